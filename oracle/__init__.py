@@ -1,0 +1,229 @@
+"""CPU oracle for the numba-cuda library kernels -- TEST INFRASTRUCTURE ONLY.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference
+legs of ``bench.py`` may import this package.  The shipped package
+(``numba_cuda_b200``) never does: it fails loudly if its CUDA library is absent.
+
+Two checkers live here:
+
+* ``libb2k_oracle.so`` -- a plain-C restatement (``b2k_oracle.c``) of the
+  reference algorithms, each function citing the reference file:line it follows.
+* ``_ref/libb2k_ref_headers.so`` -- the *reference's own* host code for the
+  fp8/bf16 arithmetic: its vendored ``cuda_fp8.hpp`` / ``cuda_bf16.hpp`` compiled
+  with g++ straight from the reference tree (``oracle/Makefile``).  It is built
+  only where the reference tree is present and travels as a binary.
+
+The wrappers below expose both through NumPy arrays.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+#: the RNG state record of numba_cuda/numba/cuda/random.py:47-49
+xoroshiro128p_dtype = np.dtype([("s0", np.uint64), ("s1", np.uint64)], align=True)
+
+F32, BF16, E4M3, E5M2 = 0, 1, 2, 3
+OPS = {"add": 0, "mul": 1, "max": 2, "min": 3}
+
+
+def build(force: bool = False) -> None:
+    """Compile the C restatement and, where the reference tree exists, the
+    reference-header checker.  Building the checker is not using it."""
+    target = os.path.join(_HERE, "libb2k_oracle.so")
+    src = os.path.join(_HERE, "b2k_oracle.c")
+    stale = (not os.path.exists(target)) or os.path.getmtime(target) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "libb2k_oracle.so", "CC=gcc"], check=True,
+                       capture_output=True)
+    ref_root = os.environ.get("B2K_REFERENCE_ROOT", "/root/reference")
+    ref_so = os.path.join(_HERE, "_ref", "libb2k_ref_headers.so")
+    if os.path.isdir(ref_root) and (force or not os.path.exists(ref_so)):
+        subprocess.run(["make", "-C", _HERE, "ref", "CXX=g++", f"REFERENCE_ROOT={ref_root}"],
+                       check=True, capture_output=True)
+
+
+@functools.lru_cache(maxsize=None)
+def lib() -> ctypes.CDLL:
+    build()
+    L = ctypes.CDLL(os.path.join(_HERE, "libb2k_oracle.so"))
+    vp, i64, u64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_uint64, ctypes.c_int
+    L.oracle_xoro_seed.argtypes = [vp, u64]
+    L.oracle_xoro_next.argtypes = [vp]
+    L.oracle_xoro_next.restype = u64
+    L.oracle_xoro_jump.argtypes = [vp]
+    L.oracle_xoro_init_states.argtypes = [vp, i64, u64, u64]
+    L.oracle_xoro_fill.argtypes = [vp, i64, i32, vp, i64]
+    L.oracle_f64_to_fp8.argtypes = [ctypes.c_double, i32, i32]
+    L.oracle_f64_to_fp8.restype = ctypes.c_uint8
+    L.oracle_f32_to_fp8.argtypes = [ctypes.c_float, i32, i32]
+    L.oracle_f32_to_fp8.restype = ctypes.c_uint8
+    L.oracle_fp8_to_f16bits.argtypes = [ctypes.c_uint8, i32]
+    L.oracle_fp8_to_f16bits.restype = ctypes.c_uint16
+    L.oracle_fp8_to_f32.argtypes = [ctypes.c_uint8, i32]
+    L.oracle_fp8_to_f32.restype = ctypes.c_float
+    L.oracle_f32_to_bf16.argtypes = [ctypes.c_float]
+    L.oracle_f32_to_bf16.restype = ctypes.c_uint16
+    L.oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
+    L.oracle_bf16_to_f32.restype = ctypes.c_float
+    L.oracle_cast.argtypes = [i32, i32, i32, vp, vp, i64]
+    L.oracle_cast.restype = i32
+    L.oracle_fold_f64.argtypes = [vp, i64, ctypes.c_double, i32]
+    L.oracle_fold_f64.restype = ctypes.c_double
+    L.oracle_fold_f32.argtypes = [vp, i64, ctypes.c_float, i32]
+    L.oracle_fold_f32.restype = ctypes.c_float
+    L.oracle_transpose2d.argtypes = [vp, vp, i64, i64, i64, i64, i64]
+    return L
+
+
+def have_ref_headers() -> bool:
+    return os.path.exists(os.path.join(_HERE, "_ref", "libb2k_ref_headers.so"))
+
+
+@functools.lru_cache(maxsize=None)
+def ref_headers() -> ctypes.CDLL:
+    """The reference's vendored fp8/bf16 headers, host path (g++-compiled)."""
+    L = ctypes.CDLL(os.path.join(_HERE, "_ref", "libb2k_ref_headers.so"))
+    vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    L.ref_cvt_float_to_fp8.argtypes = [ctypes.c_float, i32, i32]
+    L.ref_cvt_float_to_fp8.restype = ctypes.c_uint8
+    L.ref_cvt_double_to_fp8.argtypes = [ctypes.c_double, i32, i32]
+    L.ref_cvt_double_to_fp8.restype = ctypes.c_uint8
+    L.ref_cvt_fp8_to_halfraw.argtypes = [ctypes.c_uint8, i32]
+    L.ref_cvt_fp8_to_halfraw.restype = ctypes.c_uint16
+    L.ref_fp8_to_float.argtypes = [ctypes.c_uint8, i32]
+    L.ref_fp8_to_float.restype = ctypes.c_float
+    L.ref_fp8_from_float.argtypes = [ctypes.c_float, i32]
+    L.ref_fp8_from_float.restype = ctypes.c_uint8
+    L.ref_float2bfloat16_rn.argtypes = [ctypes.c_float]
+    L.ref_float2bfloat16_rn.restype = ctypes.c_uint16
+    L.ref_bfloat162float.argtypes = [ctypes.c_uint16]
+    L.ref_bfloat162float.restype = ctypes.c_float
+    L.ref_bulk_f32_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
+    L.ref_bulk_fp8_to_f32.argtypes = [vp, vp, i64, i32, i32]
+    L.ref_bulk_f32_to_bf16.argtypes = [vp, vp, i64, i32]
+    L.ref_bulk_bf16_to_f32.argtypes = [vp, vp, i64, i32]
+    return L
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+# ---------------------------------------------------------------- RNG
+def init_states(n: int, seed: int, subsequence_start: int = 0) -> np.ndarray:
+    """Serial state creation, as random.py:242-257."""
+    st = np.empty(n, dtype=xoroshiro128p_dtype)
+    lib().oracle_xoro_init_states(_ptr(st), n, seed & (2**64 - 1), subsequence_start)
+    return st
+
+
+_KIND = {("uniform", np.dtype(np.float32)): 0, ("uniform", np.dtype(np.float64)): 1,
+         ("normal", np.dtype(np.float32)): 2, ("normal", np.dtype(np.float64)): 3}
+
+
+def fill(states: np.ndarray, dist: str, dtype, count: int) -> np.ndarray:
+    """out[t, i] = i-th draw of generator t; advances ``states`` in place."""
+    dtype = np.dtype(dtype)
+    out = np.empty((states.shape[0], count), dtype=dtype)
+    assert states.flags.c_contiguous and states.dtype.itemsize == 16
+    lib().oracle_xoro_fill(_ptr(states), states.shape[0], _KIND[(dist, dtype)], _ptr(out), count)
+    return out
+
+
+def jump(state_pair):
+    st = np.array([tuple(state_pair)], dtype=xoroshiro128p_dtype)
+    lib().oracle_xoro_jump(_ptr(st))
+    return int(st[0]["s0"]), int(st[0]["s1"])
+
+
+def next_u64(state_pair):
+    st = np.array([tuple(state_pair)], dtype=xoroshiro128p_dtype)
+    r = lib().oracle_xoro_next(_ptr(st))
+    return int(r), (int(st[0]["s0"]), int(st[0]["s1"]))
+
+
+# ---------------------------------------------------------------- casts
+_CODE_DTYPE = {F32: np.float32, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8}
+
+
+def cast(x: np.ndarray, src: int, dst: int, sat: int = 1) -> np.ndarray:
+    """Bulk cast with the C restatement.  bf16 travels as uint16 bit patterns,
+    fp8 as uint8 codes."""
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    out = np.empty(x.shape, dtype=_CODE_DTYPE[dst])
+    rc = lib().oracle_cast(src, dst, sat, _ptr(x), _ptr(out), x.size)
+    if rc != 0:
+        raise ValueError(f"unsupported cast {src}->{dst}")
+    return out
+
+
+def ref_cast(x: np.ndarray, src: int, dst: int, sat: int = 1, threads: int = 0) -> np.ndarray:
+    """Bulk cast with the reference's own vendored-header host code."""
+    R = ref_headers()
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    out = np.empty(x.shape, dtype=_CODE_DTYPE[dst])
+    if src == F32 and dst == BF16:
+        R.ref_bulk_f32_to_bf16(_ptr(x), _ptr(out), x.size, threads)
+    elif src == BF16 and dst == F32:
+        R.ref_bulk_bf16_to_f32(_ptr(x), _ptr(out), x.size, threads)
+    elif src == F32 and dst in (E4M3, E5M2):
+        R.ref_bulk_f32_to_fp8(_ptr(x), _ptr(out), x.size, sat, dst - 2, threads)
+    elif src in (E4M3, E5M2) and dst == F32:
+        R.ref_bulk_fp8_to_f32(_ptr(x), _ptr(out), x.size, src - 2, threads)
+    else:
+        raise ValueError(f"unsupported cast {src}->{dst}")
+    return out
+
+
+# ---------------------------------------------------------------- reduce / transpose
+def fold(x: np.ndarray, op: str, init=0):
+    """Sequential left fold from ``init`` -- the reference's CPU path for
+    cuda.reduce (simulator/reduction.py:7-16).  Floats go through C so the
+    rounding order is exactly left-to-right; integers use NumPy's exact
+    wrap-around ufunc reductions."""
+    x = np.ascontiguousarray(x)
+    if x.dtype == np.float64:
+        return np.float64(lib().oracle_fold_f64(_ptr(x), x.size, float(init), OPS[op]))
+    if x.dtype == np.float32:
+        return np.float32(lib().oracle_fold_f32(_ptr(x), x.size, float(init), OPS[op]))
+    t = x.dtype.type
+    with np.errstate(over="ignore"):
+        if op == "add":
+            return t(np.add.reduce(x, dtype=x.dtype, initial=t(init)))
+        if op == "mul":
+            return t(np.multiply.reduce(x, dtype=x.dtype, initial=t(init)))
+        if op == "max":
+            return t(max(t(init), x.max())) if x.size else t(init)
+        if op == "min":
+            return t(min(t(init), x.min())) if x.size else t(init)
+        if op == "and":
+            return t(np.bitwise_and.reduce(x, initial=t(init)))
+        if op == "or":
+            return t(np.bitwise_or.reduce(x, initial=t(init)))
+        if op == "xor":
+            return t(np.bitwise_xor.reduce(x, initial=t(init)))
+    raise ValueError(op)
+
+
+def py_fold(fn, seq, init=0):
+    """The simulator's Reduce verbatim in behaviour: functools.reduce(fn, seq, init)
+    (simulator/reduction.py:9)."""
+    return functools.reduce(fn, seq, init)
+
+
+def transpose2d(a: np.ndarray) -> np.ndarray:
+    """b[j, i] = a[i, j] through the byte-copy loop of b2k_oracle.c (works for any
+    itemsize and any input strides)."""
+    rows, cols = a.shape
+    out = np.empty((cols, rows), dtype=a.dtype)
+    base = a
+    lib().oracle_transpose2d(base.__array_interface__["data"][0], _ptr(out), rows, cols,
+                             a.strides[0], a.strides[1], a.dtype.itemsize)
+    return out
