@@ -1,0 +1,457 @@
+#!/usr/bin/env python
+"""Benchmark of the B200-native library kernels on the reference's configurations.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline line (one JSON object on stdout, printed by rank 0):
+
+* workload = configuration 2: ``cuda.reduce(max)`` over 2^28 int32 per GPU
+  (1 GiB, far larger than the 126 MB L2, so no flush is needed between steps);
+  with N > 1 every rank reduces its own contiguous 2^28-element shard of an
+  N*2^28 array and ONE NCCL all-reduce(max) of a single int32 combines the
+  partials (weak scaling);
+* ``value``  : GB/s of input consumed by the whole job, inputs resident in HBM,
+  CUDA-event time, max over ranks;
+* ``e2e``    : the same metric through the public Python API with the input in
+  pinned HOST memory: H2D copy of the shard + kernel + D2H of the scalar are all
+  inside the timed region;
+* ``roofline``: the reduce kernel alone against the measured HBM copy rate;
+* ``cpu_baseline``: the reference's CPU path for cuda.reduce (the simulator's
+  sequential functools.reduce) timed on a bounded prefix on the host;
+* ``paths``  : the other configurations (reduce f64 2^20, transposes, RNG, casts),
+  each with its own value and roofline fraction.
+
+``--impl reference`` times only the reference's CPU path (rank 0; other ranks
+exit at once) and prints a line of the same shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_C2 = 1 << 28
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the reduce kernel at
+# 2^28 int32, from one ncu capture (profiles/reduce_max_int32_2p28.md); None until captured
+REDUCE_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- reference arm
+def reference_arm(args, rank):
+    """The reference's CPU path for cuda.reduce is the simulator's Reduce:
+    functools.reduce(functor, seq, init) (numba/cuda/simulator/reduction.py:7-16),
+    single-threaded Python.  Each step folds a bounded prefix of configuration 2."""
+    if rank != 0:
+        return
+    import oracle
+    sample_n = 1 << 22
+    x = np.random.default_rng(1).integers(-2 ** 31, 2 ** 31, size=sample_n, dtype=np.int32)
+    fn = lambda a, b: max(a, b)  # noqa: E731
+    for _ in range(args.warmup):
+        oracle.py_fold(fn, x[: 1 << 18], 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        got = oracle.py_fold(fn, x, 0)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    assert got == max(int(x.max()), 0)
+    gbs = sample_n * 4 / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "reduce_max_int32_GBps", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int32",
+        "data": "synthetic", "config": config_dict(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": f"first 2^22 of the 2^28 int32 per step, functools.reduce(max) as the "
+                                   f"simulator does; host has {os.cpu_count()} cores, the path is single-threaded"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(n_gpus):
+    return {"workload": "C2: cuda.reduce(max) over 2^28 int32 per GPU, uniform over the full int32 range "
+                        "(default_rng(seed=1+rank).integers)",
+            "elements_per_gpu": N_C2, "bytes_per_gpu": N_C2 * 4,
+            "l2": "input (1 GiB) is larger than L2 (126 MB); no flush between steps",
+            "sharding": "contiguous shard per rank + one NCCL all-reduce(max) of one int32" if n_gpus > 1
+            else "single GPU"}
+
+
+# --------------------------------------------------------------------------- our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-paths", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--only", default=None, help="run a single path (profiling aid): c1,c2,c3a,c3b,c4,c5")
+    ap.add_argument("--scale", type=int, default=0, help="shrink the --only workload by 2^scale (profiling aid)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import numba_cuda_b200 as cuda
+    from numba_cuda_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    distributed = world > 1
+    if distributed:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = _lib.lib()
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if not distributed:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn, steps, warmup):
+        """CUDA-event time per step on the launching stream, max over ranks (ms)."""
+        for _ in range(max(warmup, 3)):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = L.b2k_launch_count()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        launches = L.b2k_launch_count() - before
+        return max_over_ranks(e0.elapsed_time(e1) / steps), launches
+
+    peak, peak_kind = measured_peak()
+
+    if args.only:
+        run_single_path(args, cuda, L, torch, timed, peak, peak_kind, sptr)
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    # ---------------- headline: configuration 2 --------------------------------
+    host = cuda.pinned_array(N_C2, dtype=np.int32)
+    rng = np.random.default_rng(1 + rank)
+    chunk = 1 << 24
+    for lo in range(0, N_C2, chunk):
+        host[lo:lo + chunk] = rng.integers(-2 ** 31, 2 ** 31, size=chunk, dtype=np.int32)
+    expect_local = int(host.max())
+    x = cuda.to_device(host)
+    torch.cuda.synchronize()
+
+    scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ident = np.array([-2 ** 31], dtype=np.int32)
+
+    def kernel_only():
+        rc = L.b2k_reduce(_lib.MAX, _lib.I32, x._ptr, N_C2, ident.ctypes.data, out.data_ptr(),
+                          scratch.data_ptr(), scratch.numel(), sptr)
+        if rc:
+            raise RuntimeError(L.b2k_last_error())
+
+    def step():
+        kernel_only()
+        if distributed:
+            dist.all_reduce(out, op=dist.ReduceOp.MAX)
+
+    with ClockSampler(local_rank) as clocks:
+        ms_step, launches = timed(step, args.steps, args.warmup)
+    clock_summary = clocks.summary()
+    # correctness of what was timed
+    if distributed:
+        t = torch.tensor([expect_local], dtype=torch.int64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        expect = int(t.item())
+    else:
+        expect = expect_local
+    assert int(out.item()) == expect, (int(out.item()), expect)
+
+    # the kernel alone (roofline): same launches without the collective
+    ms_kernel, _ = timed(kernel_only, args.steps, 3)
+
+    # end to end through the public API: host shard -> device -> kernel -> host scalar
+    sharded_max = cuda.sharded.ShardedReduce(lambda a, b: max(a, b))
+    plain_max = cuda.reduce(lambda a, b: max(a, b))
+
+    def e2e_step():
+        if distributed:
+            got = sharded_max(host, init=0)
+        else:
+            got = plain_max(host, init=0)
+        assert got == max(expect, 0)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e, _ = timed(e2e_step, e2e_steps, 3)
+
+    total_bytes = N_C2 * 4 * world
+    line = {
+        "metric": "reduce_max_int32_GBps",
+        "value": total_bytes / (ms_step * 1e-3) / 1e9,
+        "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int32", "data": "synthetic",
+        "config": config_dict(world),
+        "clocks": clock_summary,
+        "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": N_C2 * 4, "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "achieved": N_C2 * 4 / (ms_kernel * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": N_C2 * 4 / (ms_kernel * 1e-3) / 1e9 / peak,
+                     "traffic": REDUCE_TRAFFIC_BYTES, "peak_kind": peak_kind,
+                     "kernel": "reduce_kernel<int, OpMax>", "us_per_launch": ms_kernel * 1e3,
+                     "algorithmic_bytes_per_launch": N_C2 * 4},
+    }
+
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(host)
+    del x, host
+
+    if not args.no_paths:
+        line["paths"] = secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr)
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if distributed:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(host):
+    """The reference's CPU path for this workload on a bounded prefix."""
+    import oracle
+    sample = 1 << 24
+    x = np.array(host[:sample])
+    fn = lambda a, b: max(a, b)  # noqa: E731
+    t0 = time.perf_counter()
+    got = oracle.py_fold(fn, x, 0)
+    dt = time.perf_counter() - t0
+    assert got == max(int(x.max()), 0)
+    t1 = time.perf_counter()
+    np_max = int(np.array(host).max())
+    dt_np = time.perf_counter() - t1
+    return {"value": sample * 4 / dt / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": "first 2^24 of the 2^28 int32, functools.reduce(max, seq, 0) as the simulator's Reduce "
+                      f"does (single Python thread; host has {os.cpu_count()} cores)",
+            "seconds": dt,
+            "numpy_max_full_GBps": N_C2 * 4 / dt_np / 1e9, "numpy_max_value": np_max}
+
+
+# --------------------------------------------------------------------------- other configurations
+def _roof(bytes_per_launch, ms, peak):
+    ach = bytes_per_launch / (ms * 1e-3) / 1e9
+    return {"GBps": ach, "frac_of_measured_copy": ach / peak, "frac_of_8000": ach / 8000.0, "ms": ms}
+
+
+def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, scale=0):
+    """Configurations 1, 3a, 3b, 4, 5: per-rank work is fixed (weak scaling);
+    times are CUDA-event, max over ranks; GB/s are per GPU."""
+    from numba_cuda_b200 import _lib
+    res = {}
+    iters, warm = 10, 3
+
+    def want(name):
+        return only is None or only == name
+
+    def check(rc):
+        if rc:
+            raise RuntimeError(L.b2k_last_error())
+
+    if want("c1"):
+        n = 1 << 20
+        x = cuda.to_device(np.random.default_rng(0).random(n))
+        scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+        out = torch.zeros(1, dtype=torch.float64, device="cuda")
+        zero = np.zeros(1, dtype=np.float64)
+        ms, _ = timed(lambda: check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
+                                                 scratch.data_ptr(), scratch.numel(), sptr)), 200, 10)
+        res["c1_reduce_sum_f64_2p20"] = dict(_roof(n * 8, ms, peak), us_per_call=ms * 1e3,
+                                             note="8 MiB: launch-latency bound, L2 resident")
+        n2 = 1 << (28 - scale)
+        y = torch.rand(n2, dtype=torch.float64, device="cuda")
+        ms, _ = timed(lambda: check(L.b2k_reduce(_lib.ADD, _lib.F64, y.data_ptr(), n2, zero.ctypes.data,
+                                                 out.data_ptr(), scratch.data_ptr(), scratch.numel(), sptr)),
+                      iters, warm)
+        res["reduce_sum_f64_2p28"] = _roof(n2 * 8, ms, peak)
+        del x, y
+
+    for name, rows, cols, tdt, item in (("c3a_transpose_f32_32768x32768", 32768, 32768, torch.float32, 4),
+                                        ("c3b_transpose_bf16_16384x65536", 16384, 65536, torch.bfloat16, 2)):
+        key = name[:3]
+        if not want(key):
+            continue
+        rows >>= scale
+        a = torch.randn(rows, cols, device="cuda", dtype=torch.float32).to(tdt)
+        b = torch.empty(cols, rows, device="cuda", dtype=tdt)
+        ms, _ = timed(lambda: check(L.b2k_transpose2d(a.data_ptr(), b.data_ptr(), rows, cols, cols * item, item,
+                                                      rows * item, item, item, sptr)), iters, warm)
+        ok = bool(torch.equal(b[:256], a[:, :256].t()))
+        res[name] = dict(_roof(2 * rows * cols * item, ms, peak), spot_check=ok,
+                         scope="replicas" if world > 1 else "single GPU")
+        del a, b
+
+    if want("c4"):
+        n = 1 << (24 - scale)
+        states = cuda.device_array(n, dtype=cuda.random.xoroshiro128p_dtype)
+        ms_init, _ = timed(lambda: cuda.random.init_xoroshiro128p_states(states, 42, rank * n), iters, warm)
+        u = torch.empty(n, 64, dtype=torch.float32, device="cuda")
+        z = torch.empty(n, 16, dtype=torch.float64, device="cuda")
+        ms, _ = timed(lambda: check(L.b2k_xoroshiro128p_fill(states._ptr, n, _lib.UNIFORM_F32, u.data_ptr(), 64,
+                                                             _lib.NORMAL_F64, z.data_ptr(), 16, sptr)), iters, warm)
+        res["c4_rng_init_2p24_states"] = dict(_roof(n * 16, ms_init, peak), Mstates_per_s=n / ms_init / 1e3)
+        res["c4_rng_generate_64u32_16n64"] = dict(_roof(n * 416, ms, peak), Gsamples_per_s=n * 80 / ms / 1e6)
+        ms_u, _ = timed(lambda: check(L.b2k_xoroshiro128p_fill(states._ptr, n, _lib.UNIFORM_F32, u.data_ptr(), 64,
+                                                               0, None, 0, sptr)), iters, warm)
+        res["rng_uniform_f32_only_64"] = dict(_roof(n * (32 + 256), ms_u, peak), Gsamples_per_s=n * 64 / ms_u / 1e6)
+        del u, z, states
+
+    if want("c5"):
+        n = 1 << (30 - scale)
+        x = torch.randn(n, device="cuda") * 4
+        idx = torch.randint(0, n, (n // 100,), device="cuda")
+        specials = torch.tensor([float("inf"), float("-inf"), float("nan"), 1e6, -1e6], device="cuda")
+        x[idx] = specials[torch.arange(idx.numel(), device="cuda") % 5]
+        del idx
+        e = torch.empty(n, dtype=torch.uint8, device="cuda")
+        h = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        back = torch.empty(n, dtype=torch.float32, device="cuda")
+        for label, s, d, src, dst, bpe in (
+                ("c5_cast_f32_to_e4m3", _lib.FMT_F32, _lib.FMT_E4M3, x, e, 5),
+                ("c5_cast_e4m3_to_f32", _lib.FMT_E4M3, _lib.FMT_F32, e, back, 5),
+                ("c5_cast_f32_to_e5m2", _lib.FMT_F32, _lib.FMT_E5M2, x, e, 5),
+                ("c5_cast_f32_to_bf16", _lib.FMT_F32, _lib.FMT_BF16, x, h, 6),
+                ("c5_cast_bf16_to_f32", _lib.FMT_BF16, _lib.FMT_F32, h, back, 6)):
+            ms, _ = timed(lambda: check(L.b2k_cast(s, d, 1, src.data_ptr(), dst.data_ptr(), n, sptr)), iters, warm)
+            res[label] = _roof(n * bpe, ms, peak)
+        res["c5_cast_f32_to_bf16"]["matches_torch_on_finite"] = bool(
+            torch.equal(h[:1 << 20].view(torch.int16)[torch.isfinite(x[:1 << 20])],
+                        x[:1 << 20].to(torch.bfloat16).view(torch.int16)[torch.isfinite(x[:1 << 20])]))
+        del x, e, h, back
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_single_path(args, cuda, L, torch, timed, peak, peak_kind, sptr):
+    """Profiling aid: run one configuration, optionally shrunk, and print its numbers."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.only == "c2":
+        from numba_cuda_b200 import _lib
+        n = N_C2 >> args.scale
+        x = torch.randint(-2 ** 31, 2 ** 31 - 1, (n,), dtype=torch.int32, device="cuda")
+        scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+        out = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ident = np.array([-2 ** 31], dtype=np.int32)
+
+        def k():
+            rc = L.b2k_reduce(_lib.MAX, _lib.I32, x.data_ptr(), n, ident.ctypes.data, out.data_ptr(),
+                              scratch.data_ptr(), scratch.numel(), sptr)
+            if rc:
+                raise RuntimeError(L.b2k_last_error())
+        ms, _ = timed(k, args.steps, args.warmup)
+        assert int(out.item()) == int(x.max().item())
+        res = {"c2_reduce_max_int32": _roof(n * 4, ms, peak)}
+    else:
+        res = secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=args.only, scale=args.scale)
+    if rank == 0:
+        print(json.dumps({"only": args.only, "scale": args.scale, "peak": peak, "peak_kind": peak_kind,
+                          "paths": res}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,135 @@
+/*
+ * b2k.h -- C ABI of libb2k.so: sm_100a kernels behind numba-cuda's built-in
+ * library kernels (cuda.reduce, device-array transpose, xoroshiro128p RNG,
+ * bf16 / fp8 conversion).
+ *
+ * The reference has no FFI for this path: its library kernels are Python that is
+ * JIT-compiled on first use.  Each entry point below names the reference code
+ * whose device work it replaces (paths relative to the numba-cuda project root).
+ *
+ * Conventions
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void*
+ *     (NULL = the legacy default stream);
+ *   - every pointer named *_dev is device memory of the CURRENT device;
+ *   - every call returns an int status: 0 = ok, negative = argument error found
+ *     on the host before any launch (B2K_ERR_*), positive = a cudaError_t;
+ *   - calls are asynchronous on `stream` and never synchronise;
+ *   - the library allocates no device memory; scratch is passed in by the caller
+ *     (sizes from the *_scratch_bytes functions);
+ *   - b2k_last_error() gives a thread-local message for the last failure.
+ */
+#ifndef B2K_H_
+#define B2K_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B2K_API __attribute__((visibility("default")))
+#else
+#define B2K_API
+#endif
+
+#define B2K_OK 0
+#define B2K_ERR_INVALID_ARG (-1)   /* null pointer, negative size, bad enum        */
+#define B2K_ERR_UNSUPPORTED (-2)   /* op/dtype pair or cast pair not implemented   */
+#define B2K_ERR_ALIGNMENT (-3)     /* pointer not aligned to the element size      */
+#define B2K_ERR_SCRATCH (-4)       /* scratch buffer missing or too small          */
+#define B2K_ERR_TOO_LARGE (-5)     /* size beyond a stated maximum                 */
+
+/* element types (reduce) */
+enum b2k_dtype {
+    B2K_I8 = 0, B2K_I16 = 1, B2K_I32 = 2, B2K_I64 = 3,
+    B2K_U8 = 4, B2K_U16 = 5, B2K_U32 = 6, B2K_U64 = 7,
+    B2K_F32 = 8, B2K_F64 = 9
+};
+
+/* binary ops (reduce): the table a user's Python functor is classified into */
+enum b2k_op {
+    B2K_ADD = 0, B2K_MUL = 1, B2K_MAX = 2, B2K_MIN = 3,
+    B2K_AND = 4, B2K_OR = 5, B2K_XOR = 6
+};
+
+/* storage formats (cast) */
+enum b2k_format { B2K_FMT_F32 = 0, B2K_FMT_BF16 = 1, B2K_FMT_E4M3 = 2, B2K_FMT_E5M2 = 3 };
+
+/* draws (RNG fill) */
+enum b2k_draw {
+    B2K_UNIFORM_F32 = 0, B2K_UNIFORM_F64 = 1, B2K_NORMAL_F32 = 2, B2K_NORMAL_F64 = 3
+};
+
+B2K_API int b2k_version(void);
+B2K_API const char *b2k_last_error(void);
+/* number of kernels this library has launched in the calling process */
+B2K_API int64_t b2k_launch_count(void);
+
+/* ---- reduce -------------------------------------------------------------
+ * Replaces the three launches + partials allocation of Reduce.__call__
+ * (numba/cuda/kernels/reduction.py:194-265) and the kernel bodies
+ * gpu_reduce_block_strided / device_reduce_full_block (:44-166) with ONE launch:
+ * out_dev[0] = op(fold(x_dev[0..n)), *init_host).
+ *   init_host : host pointer to one element of `dtype` (always folded in, as
+ *               reduction.py:163-164 does)
+ *   out_dev   : one element of `dtype`
+ *   scratch   : b2k_reduce_scratch_bytes() bytes, zero-filled once by the caller
+ *               before first use; the kernel leaves it reusable.  Two reductions
+ *               that may overlap on the GPU need separate scratch.
+ * n == 0 writes *init_host to out_dev. */
+B2K_API int64_t b2k_reduce_scratch_bytes(void);
+B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+               void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
+
+/* ---- transpose ----------------------------------------------------------
+ * Replaces the per-call JIT-compiled tile kernel of
+ * numba/cuda/kernels/transpose.py:42-63: out[j, i] = in[i, j] for items of
+ * `itemsize` bytes; strides are in bytes and arbitrary for both arrays. */
+B2K_API int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, int64_t cols,
+                    int64_t in_stride0, int64_t in_stride1,
+                    int64_t out_stride0, int64_t out_stride1,
+                    int64_t itemsize, void *stream);
+
+/* ---- xoroshiro128p ------------------------------------------------------
+ * b2k_xoroshiro128p_init replaces init_xoroshiro128p_states_cpu + the H2D copy
+ * (numba/cuda/random.py:242-282): states[i] = jump^(subsequence_start+i)(seed
+ * state), computed on the device in parallel.
+ *   tables_dev : b2k_xoroshiro128p_tables_bytes() bytes filled once per device
+ *                by b2k_xoroshiro128p_build_tables (seed-independent).          */
+B2K_API int64_t b2k_xoroshiro128p_tables_bytes(void);
+B2K_API int b2k_xoroshiro128p_build_tables(void *tables_dev, int64_t tables_bytes, void *stream);
+B2K_API int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed,
+                           uint64_t subsequence_start, const void *tables_dev,
+                           int64_t tables_bytes, void *stream);
+
+/* One bulk "user kernel" in the layout of the reference's test kernels
+ * (numba/cuda/tests/cudapy/test_random.py:29-53): for every generator t in
+ * [0, n): out[t*count + i] = draw(states, t), i in [0, count); states are
+ * advanced in place.  Replaces the device functions
+ * xoroshiro128p_{uniform,normal}_float{32,64} (random.py:160-238) inlined in a
+ * caller's kernel.  Up to two segments are generated back to back per
+ * generator (segment 1 may be NULL / count 0), so that e.g. 64 uniform f32
+ * followed by 16 normal f64 costs one state round trip. */
+B2K_API int b2k_xoroshiro128p_fill(void *states_dev, int64_t n,
+                           int draw0, void *out0_dev, int64_t count0,
+                           int draw1, void *out1_dev, int64_t count1, void *stream);
+
+/* ---- casts --------------------------------------------------------------
+ * Bulk elementwise conversion with the semantics of the conversion intrinsics
+ *   f32 -> e4m3/e5m2 : cvt_float_to_fp8(x, saturate, interp)
+ *                      (numba/cuda/_internal/cuda_fp8.py:3341-3374;
+ *                       include/12/cuda_fp8.hpp:245-288)
+ *   e4m3/e5m2 -> f32 : float(fp8_e4m3(code)) (cuda_fp8.py:1610-1631;
+ *                       cuda_fp8.hpp:473-545, :319-356)
+ *   f32 -> bf16      : float32_to_bfloat16 / __float2bfloat16_rn
+ *                      (numba/cuda/bf16.py:204-207; cuda_bf16.hpp:471-503)
+ *   bf16 -> f32      : bfloat16_to_float32 (bf16.py:206; cuda_bf16.hpp:582-609)
+ * saturate: 1 = SATFINITE, 0 = NOSAT (fp8 destinations only). */
+B2K_API int b2k_cast(int src_format, int dst_format, int saturate, const void *in_dev,
+             void *out_dev, int64_t n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2K_H_ */

@@ -1,0 +1,136 @@
+"""Bulk elementwise conversions f32 <-> bf16 / fp8 with the semantics of the
+reference's conversion intrinsics (numba/cuda/_internal/cuda_fp8.py:3341-3374,
+:1331-1351, :1610-1631; numba/cuda/bf16.py:204-210).
+
+The reference has no bulk cast: a user writes an elementwise ``@cuda.jit``
+kernel over the scalar intrinsics.  ``cast`` is that kernel, precompiled.
+Storage on the host side: fp8 codes are ``uint8`` (``__nv_fp8_storage_t``),
+bf16 is ``ml_dtypes.bfloat16`` (as numba/cuda/np/numpy_support.py:79-84) or
+raw ``uint16`` bits.
+"""
+from __future__ import annotations
+
+import enum
+
+import numpy as np
+
+from . import _lib
+from .api import auto_device, device_array
+from .devicearray import DeviceNDArray, bfloat16_dtype, stream_ptr
+
+
+class saturation_t(enum.IntEnum):
+    """cuda_fp8.py:223-226"""
+    NOSAT = 0
+    SATFINITE = 1
+
+
+class fp8_interpretation_t(enum.IntEnum):
+    """cuda_fp8.py:228-230"""
+    E4M3 = 0
+    E5M2 = 1
+
+
+FORMATS = {"f32": _lib.FMT_F32, "float32": _lib.FMT_F32, "bf16": _lib.FMT_BF16, "bfloat16": _lib.FMT_BF16,
+           "e4m3": _lib.FMT_E4M3, "fp8_e4m3": _lib.FMT_E4M3, "float8_e4m3fn": _lib.FMT_E4M3,
+           "e5m2": _lib.FMT_E5M2, "fp8_e5m2": _lib.FMT_E5M2, "float8_e5m2": _lib.FMT_E5M2}
+_ITEMSIZE = {_lib.FMT_F32: 4, _lib.FMT_BF16: 2, _lib.FMT_E4M3: 1, _lib.FMT_E5M2: 1}
+
+
+def _format_code(fmt) -> int:
+    if isinstance(fmt, (int, np.integer)):
+        return int(fmt)
+    key = str(getattr(fmt, "name", fmt)).lower()
+    if key not in FORMATS:
+        raise ValueError(f"unknown format {fmt!r}")
+    return FORMATS[key]
+
+
+def _storage_dtype(code: int):
+    if code == _lib.FMT_F32:
+        return np.dtype(np.float32)
+    if code == _lib.FMT_BF16:
+        return bfloat16_dtype()
+    return np.dtype(np.uint8)
+
+
+def cast(src, src_format, dst_format, out=None, saturate=saturation_t.SATFINITE, stream=0):
+    """Convert every element of ``src`` (host or device array holding
+    ``src_format`` items) to ``dst_format``; returns a device array of the same
+    shape.  Supported: f32 -> bf16 / e4m3 / e5m2 and back to f32."""
+    s, d = _format_code(src_format), _format_code(dst_format)
+    dsrc, _ = auto_device(src, stream=stream)
+    if dsrc.dtype.itemsize != _ITEMSIZE[s]:
+        raise TypeError(f"source items are {dsrc.dtype.itemsize} bytes, format needs {_ITEMSIZE[s]}")
+    if dsrc.size and not dsrc.flags["C_CONTIGUOUS"]:
+        raise ValueError("cast needs a C-contiguous source")
+    if out is None:
+        out = device_array(dsrc.shape, dtype=_storage_dtype(d), stream=stream)
+    else:
+        out, _ = auto_device(out, stream=stream, copy=False)
+        if out.dtype.itemsize != _ITEMSIZE[d] or out.size != dsrc.size or not out.flags["C_CONTIGUOUS"]:
+            raise ValueError("out must be C-contiguous with the source's size and the target's item size")
+    _lib.check(_lib.lib().b2k_cast(s, d, int(saturate), dsrc._ptr, out._ptr, dsrc.size, stream_ptr(stream)))
+    return out
+
+
+def _scalar_or_bulk(x, s, d, saturate=saturation_t.SATFINITE):
+    if isinstance(x, DeviceNDArray) or (isinstance(x, np.ndarray) and x.ndim > 0):
+        return cast(x, s, d, saturate=saturate)
+    host = np.array([x], dtype=_storage_dtype(s))
+    return cast(host, s, d, saturate=saturate).copy_to_host()[0]
+
+
+# ---- fp8 storage intrinsics (cuda_fp8.py:3341-3410) --------------------------
+def cvt_float_to_fp8(x, saturate, fp8_interpretation):
+    """float32 -> fp8 code (uint8).  A scalar gives a scalar; an array is
+    converted in bulk on the device."""
+    d = _lib.FMT_E5M2 if int(fp8_interpretation) == fp8_interpretation_t.E5M2 else _lib.FMT_E4M3
+    return _scalar_or_bulk(x, _lib.FMT_F32, d, saturate)
+
+
+def cvt_float2_to_fp8x2(x, saturate, fp8_interpretation):
+    """(float32, float32) -> uint16 holding two codes, ``x[0]`` in the low byte."""
+    codes = cvt_float_to_fp8(np.asarray(x, dtype=np.float32).reshape(2), saturate, fp8_interpretation)
+    lo, hi = (int(v) for v in codes.copy_to_host())
+    return np.uint16(lo | (hi << 8))
+
+
+# ---- fp8 value types: construct from float (SATFINITE) and convert back --------
+def fp8_e4m3(x):
+    """``fp8_e4m3(float)`` (cuda_fp8.py:1331-1351): saturating E4M3 code(s)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_E4M3, saturation_t.SATFINITE)
+
+
+def fp8_e5m2(x):
+    """``fp8_e5m2(float)``: saturating E5M2 code(s)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_E5M2, saturation_t.SATFINITE)
+
+
+def fp8_e4m3_to_float32(codes):
+    """``float32(fp8_e4m3)`` (cuda_fp8.py:1610-1631)."""
+    return _scalar_or_bulk(codes, _lib.FMT_E4M3, _lib.FMT_F32)
+
+
+def fp8_e5m2_to_float32(codes):
+    return _scalar_or_bulk(codes, _lib.FMT_E5M2, _lib.FMT_F32)
+
+
+# ---- bf16 (bf16.py:204-207) --------------------------------------------------------
+def float32_to_bfloat16(x):
+    """Round-to-nearest-even float32 -> bfloat16."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_BF16)
+
+
+float32_to_bfloat16_rn = float32_to_bfloat16
+
+
+def bfloat16_to_float32(x):
+    return _scalar_or_bulk(x, _lib.FMT_BF16, _lib.FMT_F32)
+
+
+__all__ = [
+    "cast", "saturation_t", "fp8_interpretation_t", "cvt_float_to_fp8", "cvt_float2_to_fp8x2",
+    "fp8_e4m3", "fp8_e5m2", "fp8_e4m3_to_float32", "fp8_e5m2_to_float32",
+    "float32_to_bfloat16", "float32_to_bfloat16_rn", "bfloat16_to_float32",
+]

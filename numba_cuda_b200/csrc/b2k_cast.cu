@@ -1,0 +1,242 @@
+// Bulk elementwise conversions f32 <-> bf16 and f32 <-> fp8 (E4M3 / E5M2).
+//
+// In the reference these conversions are scalar intrinsics reached through a
+// non-inlined NVRTC-compiled shim per element (numba/cuda/_internal/
+// cuda_fp8.py:166-207, :3341-3374; cuda_bf16.py:2054-2131, :2257-2295) whose
+// bodies are the vendored cuda_fp8.hpp / cuda_bf16.hpp.  Here one thread
+// converts four elements per step with the packed cvt instructions; the wide
+// side moves as one 128-bit access per lane and the narrow side as one 32- or
+// 64-bit access per lane, so every warp access is a run of whole 128-byte lines.
+// HBM roofline: 4+1 bytes per element for fp8, 4+2 for bf16.
+#include "b2k_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+
+// ---- scalar conversions ----------------------------------------------------
+
+// Packed saturating convert: the FIRST source operand lands in the HIGH byte.
+__device__ __forceinline__ uint32_t pack2_e4m3_sat(float hi, float lo) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack2_e5m2_sat(float hi, float lo) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// Round-to-nearest-even f32 -> fp8 without saturation: the integer algorithm of
+// include/12/cuda_fp8.hpp:119-229 restated on f32 bit patterns (the reference
+// widens to double first; widening is exact, so thresholds and dropped bits map
+// one to one).  Overflow gives NaN (E4M3) or Inf (E5M2); every NaN gives 0x7F.
+template <bool E5M2>
+__device__ __forceinline__ uint32_t f32_to_fp8_nosat(float x) {
+    constexpr uint32_t kMant = E5M2 ? 2u : 3u;             // stored mantissa bits
+    constexpr int kBias = E5M2 ? 15 : 7;
+    constexpr uint32_t kHalfMinDenorm = E5M2 ? 0x37000000u : 0x3A800000u;  // 2^-17 / 2^-10
+    constexpr uint32_t kMinNorm = E5M2 ? 0x38800000u : 0x3C800000u;        // 2^-14 / 2^-6
+    // first magnitude that no longer rounds to the largest finite value
+    constexpr uint32_t kOverflowFrom = E5M2 ? 0x47700000u : 0x43E80001u;   // 61440 / >464
+    constexpr uint32_t kHalf = 1u << (22u - kMant);
+
+    const uint32_t bits = __float_as_uint(x);
+    const uint32_t mag = bits & 0x7FFFFFFFu;
+    const uint32_t sign = (bits >> 24) & 0x80u;
+    if (mag > 0x7F800000u) return 0x7Fu;                   // NaN: canonical, sign dropped
+    if (mag <= kHalfMinDenorm) return sign;
+    if (mag >= kOverflowFrom) return sign | (E5M2 ? 0x7Cu : 0x7Fu);
+    const int e8 = static_cast<int>(mag >> 23) - 127 + kBias;
+    uint32_t mant = (bits >> (23u - kMant)) & ((1u << kMant) - 1u);
+    uint32_t code;
+    if (mag >= kMinNorm) {
+        code = (static_cast<uint32_t>(e8) << kMant) | mant;
+        const uint32_t dropped = bits & ((kHalf << 1) - 1u);
+        if (dropped > kHalf || (dropped == kHalf && (mant & 1u))) ++code;
+    } else {
+        const uint32_t shift = static_cast<uint32_t>(1 - e8);
+        mant |= 1u << kMant;
+        code = mant >> shift;
+        const uint32_t dropped = (bits | (1u << 23)) & ((kHalf << (shift + 1u)) - 1u);
+        const uint32_t mid = kHalf << shift;
+        if (dropped > mid || (dropped == mid && (code & 1u))) ++code;
+    }
+    return code | sign;
+}
+
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2_e4m3(uint32_t two_codes) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(two_codes)));
+    return r;
+}
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2_e5m2(uint32_t two_codes) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(two_codes)));
+    return r;
+}
+__device__ __forceinline__ float f16bits_to_f32(uint32_t h) {
+    float f;
+    asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(static_cast<uint16_t>(h)));
+    return f;
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float hi, float lo) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float bf16bits_to_f32(uint32_t h) {
+    float f;
+    asm("cvt.f32.bf16 %0, %1;" : "=f"(f) : "h"(static_cast<uint16_t>(h)));
+    return f;
+}
+
+// ---- four-element converters ------------------------------------------------
+// Each converter names its wide and narrow vector types and converts one item
+// of four consecutive elements; `one` converts a single element for ragged ends.
+
+template <bool E5M2, bool SAT>
+struct F32ToFp8 {
+    using In = float4; using Out = uint32_t; using InS = float; using OutS = uint8_t;
+    __device__ static Out four(const In &v) {
+        if constexpr (SAT) {
+            if constexpr (E5M2) return pack2_e5m2_sat(v.y, v.x) | (pack2_e5m2_sat(v.w, v.z) << 16);
+            else return pack2_e4m3_sat(v.y, v.x) | (pack2_e4m3_sat(v.w, v.z) << 16);
+        } else {
+            return f32_to_fp8_nosat<E5M2>(v.x) | (f32_to_fp8_nosat<E5M2>(v.y) << 8) |
+                   (f32_to_fp8_nosat<E5M2>(v.z) << 16) | (f32_to_fp8_nosat<E5M2>(v.w) << 24);
+        }
+    }
+    __device__ static OutS one(InS x) {
+        if constexpr (SAT) {
+            return static_cast<OutS>(E5M2 ? pack2_e5m2_sat(0.0f, x) : pack2_e4m3_sat(0.0f, x));
+        } else {
+            return static_cast<OutS>(f32_to_fp8_nosat<E5M2>(x));
+        }
+    }
+};
+
+template <bool E5M2>
+struct Fp8ToF32 {
+    using In = uint32_t; using Out = float4; using InS = uint8_t; using OutS = float;
+    __device__ static Out four(const In &codes) {
+        const uint32_t lo = E5M2 ? fp8x2_to_f16x2_e5m2(codes & 0xFFFFu) : fp8x2_to_f16x2_e4m3(codes & 0xFFFFu);
+        const uint32_t hi = E5M2 ? fp8x2_to_f16x2_e5m2(codes >> 16) : fp8x2_to_f16x2_e4m3(codes >> 16);
+        return make_float4(f16bits_to_f32(lo & 0xFFFFu), f16bits_to_f32(lo >> 16),
+                           f16bits_to_f32(hi & 0xFFFFu), f16bits_to_f32(hi >> 16));
+    }
+    __device__ static OutS one(InS c) {
+        const uint32_t h = E5M2 ? fp8x2_to_f16x2_e5m2(c) : fp8x2_to_f16x2_e4m3(c);
+        return f16bits_to_f32(h & 0xFFFFu);
+    }
+};
+
+struct F32ToBf16 {
+    using In = float4; using Out = uint2; using InS = float; using OutS = uint16_t;
+    __device__ static Out four(const In &v) {
+        return make_uint2(pack2_bf16(v.y, v.x), pack2_bf16(v.w, v.z));
+    }
+    __device__ static OutS one(InS x) { return static_cast<OutS>(pack2_bf16(0.0f, x) & 0xFFFFu); }
+};
+
+struct Bf16ToF32 {
+    using In = uint2; using Out = float4; using InS = uint16_t; using OutS = float;
+    __device__ static Out four(const In &v) {
+        return make_float4(bf16bits_to_f32(v.x & 0xFFFFu), bf16bits_to_f32(v.x >> 16),
+                           bf16bits_to_f32(v.y & 0xFFFFu), bf16bits_to_f32(v.y >> 16));
+    }
+    __device__ static OutS one(InS h) { return bf16bits_to_f32(h); }
+};
+
+// ---- kernels ------------------------------------------------------------------
+
+template <typename V>
+__device__ __forceinline__ V load_stream(const V *p) {
+    return __ldcs(p);  // read once: evict-first
+}
+template <typename V>
+__device__ __forceinline__ void store_stream(V *p, const V &v) {
+    __stcs(p, v);      // written once, not re-read by this kernel
+}
+
+template <typename C, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+cast_items_kernel(const typename C::In *__restrict__ in, typename C::Out *__restrict__ out,
+                  int64_t items, int64_t n) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    int64_t i = tid;
+    for (; i + (UNROLL - 1) * stride < items; i += UNROLL * stride) {
+        typename C::In raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream(in + i + u * stride);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) store_stream(out + i + u * stride, C::four(raw[u]));
+    }
+    for (; i < items; i += stride) store_stream(out + i, C::four(load_stream(in + i)));
+    // ragged end: fewer than four elements
+    const int64_t t = items * 4 + tid;
+    if (t < n) {
+        const auto *in_s = reinterpret_cast<const typename C::InS *>(in);
+        auto *out_s = reinterpret_cast<typename C::OutS *>(out);
+        out_s[t] = C::one(in_s[t]);
+    }
+}
+
+// Any alignment: one element per thread step.
+template <typename C>
+__global__ void __launch_bounds__(kThreads)
+cast_scalar_kernel(const typename C::InS *__restrict__ in, typename C::OutS *__restrict__ out, int64_t n) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride)
+        out[i] = C::one(in[i]);
+}
+
+template <typename C>
+int launch(const void *in, void *out, int64_t n, cudaStream_t stream) {
+    if (n == 0) return B2K_OK;
+    if (!b2k::aligned_to<void>(in, sizeof(typename C::InS)) || !b2k::aligned_to<void>(out, sizeof(typename C::OutS)))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_cast: pointers must be aligned to the element size");
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_CAST_CTAS_PER_SM", 8);
+    const bool vector_ok = b2k::aligned_to<void>(in, sizeof(typename C::In)) &&
+                           b2k::aligned_to<void>(out, sizeof(typename C::Out));
+    if (vector_ok) {
+        const int64_t items = n / 4;
+        int64_t grid = (items + kThreads * kUnroll - 1) / (kThreads * kUnroll);
+        if (grid < 1) grid = 1;
+        if (grid > cap) grid = cap;
+        cast_items_kernel<C, kUnroll><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename C::In *>(in), static_cast<typename C::Out *>(out), items, n);
+    } else {
+        int64_t grid = (n + kThreads - 1) / kThreads;
+        if (grid > cap) grid = cap;
+        cast_scalar_kernel<C><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename C::InS *>(in), static_cast<typename C::OutS *>(out), n);
+    }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_cast launch");
+    return B2K_OK;
+}
+
+}  // namespace
+
+extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void *out_dev,
+                        int64_t n, void *stream) {
+    if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast: negative length %lld", (long long)n);
+    if (n > 0 && (!in_dev || !out_dev)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast: null pointer");
+    cudaStream_t s = b2k::as_stream(stream);
+    const bool sat = saturate != 0;
+    if (src == B2K_FMT_F32 && dst == B2K_FMT_BF16) return launch<F32ToBf16>(in_dev, out_dev, n, s);
+    if (src == B2K_FMT_BF16 && dst == B2K_FMT_F32) return launch<Bf16ToF32>(in_dev, out_dev, n, s);
+    if (src == B2K_FMT_F32 && dst == B2K_FMT_E4M3)
+        return sat ? launch<F32ToFp8<false, true>>(in_dev, out_dev, n, s)
+                   : launch<F32ToFp8<false, false>>(in_dev, out_dev, n, s);
+    if (src == B2K_FMT_F32 && dst == B2K_FMT_E5M2)
+        return sat ? launch<F32ToFp8<true, true>>(in_dev, out_dev, n, s)
+                   : launch<F32ToFp8<true, false>>(in_dev, out_dev, n, s);
+    if (src == B2K_FMT_E4M3 && dst == B2K_FMT_F32) return launch<Fp8ToF32<false>>(in_dev, out_dev, n, s);
+    if (src == B2K_FMT_E5M2 && dst == B2K_FMT_F32) return launch<Fp8ToF32<true>>(in_dev, out_dev, n, s);
+    return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_cast: no conversion from format %d to %d", src, dst);
+}

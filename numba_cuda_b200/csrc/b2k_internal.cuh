@@ -1,0 +1,35 @@
+// Shared host/device helpers for libb2k.so (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b2k.h"
+
+namespace b2k {
+
+// Records a thread-local message and returns `code` (see b2k_last_error()).
+int fail(int code, const char *fmt, ...);
+// Converts a cudaError_t of a launch/API call into the ABI's positive status.
+int check_cuda(cudaError_t e, const char *what);
+// Counts kernels launched by this library (reported by b2k_launch_count()).
+void note_launch(int n = 1);
+// Streaming multiprocessors of the current device (cached per device).
+int sm_count();
+// Integer knob from the environment, read once per name (development aid).
+int env_int(const char *name, int fallback);
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+template <typename T>
+inline bool aligned_to(const void *p, size_t a) {
+    return (reinterpret_cast<uintptr_t>(p) % a) == 0;
+}
+
+}  // namespace b2k
+
+#define B2K_RETURN_IF_LAUNCH_FAILED(what)                      \
+    do {                                                       \
+        cudaError_t e__ = cudaGetLastError();                  \
+        if (e__ != cudaSuccess) return b2k::check_cuda(e__, what); \
+    } while (0)

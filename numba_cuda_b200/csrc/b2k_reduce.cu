@@ -1,0 +1,294 @@
+// Single-launch full reduction of a 1-D array with a table op.
+//
+// Replaces the reference's three-launch schedule (numba/cuda/kernels/
+// reduction.py:233-258: full blocks -> tail block -> fold of <=65 partials, with
+// only 64x128 threads and scalar loads) by one persistent-grid kernel:
+//
+//   * every thread walks the array with a grid stride of 16-byte vectors,
+//     UNROLL independent 128-bit loads in flight, one accumulator per slot;
+//   * lanes combine with a shuffle butterfly, warps through shared memory;
+//   * each block publishes its partial, then takes a ticket (atomicInc that
+//     wraps to zero by itself); the block that draws the last ticket folds all
+//     partials in index order, folds `init` in and writes the result.
+//
+// The fold order depends only on (n, grid size), so floating-point results are
+// reproducible run to run.  HBM roofline: sizeof(T) bytes read per element.
+#include <cstring>
+#include <type_traits>
+
+#include "b2k_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kUnroll = 4;
+constexpr int kMaxGrid = 4096;
+constexpr int kTicketBytes = 256;  // ticket word padded so partials stay 256-B aligned
+
+// ---- ops -----------------------------------------------------------------
+// Integer add/mul run in the unsigned type of the same width: numba evaluates
+// the functor in int64 and truncates when storing to the dtype's partials
+// array, which is the same as wrap-around at the dtype's width.
+template <typename T> struct UnsignedOf { using type = T; };
+template <> struct UnsignedOf<int8_t> { using type = uint8_t; };
+template <> struct UnsignedOf<int16_t> { using type = uint16_t; };
+template <> struct UnsignedOf<int32_t> { using type = uint32_t; };
+template <> struct UnsignedOf<int64_t> { using type = uint64_t; };
+
+template <typename T> struct Limits;
+#define B2K_LIMITS(T, LO, HI)                                   \
+    template <> struct Limits<T> {                              \
+        __host__ __device__ static T lowest() { return LO; }    \
+        __host__ __device__ static T highest() { return HI; }   \
+    };
+B2K_LIMITS(int8_t, INT8_MIN, INT8_MAX)
+B2K_LIMITS(int16_t, INT16_MIN, INT16_MAX)
+B2K_LIMITS(int32_t, INT32_MIN, INT32_MAX)
+B2K_LIMITS(int64_t, INT64_MIN, INT64_MAX)
+B2K_LIMITS(uint8_t, 0, UINT8_MAX)
+B2K_LIMITS(uint16_t, 0, UINT16_MAX)
+B2K_LIMITS(uint32_t, 0u, UINT32_MAX)
+B2K_LIMITS(uint64_t, 0ull, UINT64_MAX)
+B2K_LIMITS(float, -__builtin_huge_valf(), __builtin_huge_valf())
+B2K_LIMITS(double, -__builtin_huge_val(), __builtin_huge_val())
+#undef B2K_LIMITS
+
+struct OpAdd {
+    template <typename T> __device__ static T identity() { return T(0); }
+    template <typename T> __device__ static T apply(T a, T b) {
+        using U = typename UnsignedOf<T>::type;
+        return static_cast<T>(static_cast<U>(a) + static_cast<U>(b));
+    }
+};
+struct OpMul {
+    template <typename T> __device__ static T identity() { return T(1); }
+    template <typename T> __device__ static T apply(T a, T b) {
+        using U = typename UnsignedOf<T>::type;
+        return static_cast<T>(static_cast<U>(a) * static_cast<U>(b));
+    }
+};
+struct OpMax {
+    template <typename T> __device__ static T identity() { return Limits<T>::lowest(); }
+    template <typename T> __device__ static T apply(T a, T b) { return (b > a) ? b : a; }
+};
+struct OpMin {
+    template <typename T> __device__ static T identity() { return Limits<T>::highest(); }
+    template <typename T> __device__ static T apply(T a, T b) { return (b < a) ? b : a; }
+};
+struct OpAnd {
+    template <typename T> __device__ static T identity() { return static_cast<T>(~T(0)); }
+    template <typename T> __device__ static T apply(T a, T b) { return static_cast<T>(a & b); }
+};
+struct OpOr {
+    template <typename T> __device__ static T identity() { return T(0); }
+    template <typename T> __device__ static T apply(T a, T b) { return static_cast<T>(a | b); }
+};
+struct OpXor {
+    template <typename T> __device__ static T identity() { return T(0); }
+    template <typename T> __device__ static T apply(T a, T b) { return static_cast<T>(a ^ b); }
+};
+
+// ---- helpers -------------------------------------------------------------
+// Read-once data: non-coherent path, no L1 allocation.
+__device__ __forceinline__ uint4 load_stream16(const uint4 *p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+template <typename T, typename Op>
+__device__ __forceinline__ T fold_vector(T acc, const uint4 &raw) {
+    constexpr int N = 16 / sizeof(T);
+    union { uint4 v; T e[N]; } u;
+    u.v = raw;
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc = Op::template apply<T>(acc, u.e[i]);
+    return acc;
+}
+
+template <typename T>
+__device__ __forceinline__ T shuffle_xor(T v, int mask) {
+    if constexpr (sizeof(T) < 4) {
+        return static_cast<T>(__shfl_xor_sync(0xffffffffu, static_cast<int>(v), mask));
+    } else {
+        return __shfl_xor_sync(0xffffffffu, v, mask);
+    }
+}
+__device__ __forceinline__ int64_t shuffle_xor(int64_t v, int mask) {
+    return static_cast<int64_t>(__shfl_xor_sync(0xffffffffu, static_cast<long long>(v), mask));
+}
+__device__ __forceinline__ uint64_t shuffle_xor(uint64_t v, int mask) {
+    return static_cast<uint64_t>(
+        __shfl_xor_sync(0xffffffffu, static_cast<unsigned long long>(v), mask));
+}
+
+// Block-wide fold; the result is valid in thread 0.  `slots` holds one T per warp.
+template <typename T, typename Op, int THREADS>
+__device__ __forceinline__ T block_fold(T v, T *slots) {
+    constexpr int WARPS = THREADS / 32;
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = Op::template apply<T>(v, shuffle_xor(v, m));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) slots[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = (lane < WARPS) ? slots[lane] : Op::template identity<T>();
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) v = Op::template apply<T>(v, shuffle_xor(v, m));
+    }
+    __syncthreads();
+    return v;
+}
+
+template <typename T, typename Op, int THREADS, int UNROLL>
+__global__ void __launch_bounds__(THREADS)
+reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
+              T *partials, unsigned int *ticket) {
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ T slots[THREADS / 32];
+    __shared__ bool is_last;
+
+    // elements before the first 16-byte boundary, then whole vectors, then a tail
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
+    int64_t head = static_cast<int64_t>(((16u - (addr & 15u)) & 15u) / sizeof(T));
+    if (head > n) head = n;
+    const uint4 *xv = reinterpret_cast<const uint4 *>(x + head);
+    const int64_t nvec = (n - head) / VEC;
+    const int64_t tail_begin = head + nvec * VEC;
+
+    T acc[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) acc[u] = Op::template identity<T>();
+
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * THREADS;
+    int64_t v = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+    for (; v + (UNROLL - 1) * stride < nvec; v += UNROLL * stride) {
+        uint4 raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream16(xv + v + u * stride);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) acc[u] = fold_vector<T, Op>(acc[u], raw[u]);
+    }
+    for (; v < nvec; v += stride) acc[0] = fold_vector<T, Op>(acc[0], load_stream16(xv + v));
+
+    if (blockIdx.x == 0) {  // fewer than 16 scalars on each side
+        if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);
+        const int64_t t = tail_begin + threadIdx.x;
+        if (t < n) acc[0] = Op::template apply<T>(acc[0], x[t]);
+    }
+#pragma unroll
+    for (int u = 1; u < UNROLL; ++u) acc[0] = Op::template apply<T>(acc[0], acc[u]);
+
+    T total = block_fold<T, Op, THREADS>(acc[0], slots);
+
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = total;
+        __threadfence();
+        // wraps to 0 after gridDim.x tickets: the scratch is reusable as is
+        const unsigned int t = atomicInc(ticket, gridDim.x - 1);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    T mine = Op::template identity<T>();
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
+        mine = Op::template apply<T>(mine, __ldcg(partials + i));
+    total = block_fold<T, Op, THREADS>(mine, slots);
+    if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
+}
+
+template <typename T, typename Op>
+int launch(const void *x, int64_t n, const void *init_host, void *out, void *scratch,
+           cudaStream_t stream) {
+    constexpr int VEC = 16 / sizeof(T);
+    T init;
+    memcpy(&init, init_host, sizeof(T));
+    const int per_sm = b2k::env_int("B2K_REDUCE_CTAS_PER_SM", 4);
+    int64_t max_grid = static_cast<int64_t>(b2k::sm_count()) * per_sm;
+    if (max_grid > kMaxGrid) max_grid = kMaxGrid;
+    const int64_t nvec = n / VEC + 1;
+    int64_t grid = (nvec + static_cast<int64_t>(kThreads) * kUnroll - 1) /
+                   (static_cast<int64_t>(kThreads) * kUnroll);
+    if (grid < 1) grid = 1;
+    if (grid > max_grid) grid = max_grid;
+    auto *ticket = static_cast<unsigned int *>(scratch);
+    auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
+    reduce_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+        static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_reduce launch");
+    return B2K_OK;
+}
+
+template <typename T>
+int dispatch_op(int op, const void *x, int64_t n, const void *init_host, void *out,
+                void *scratch, cudaStream_t stream) {
+    switch (op) {
+    case B2K_ADD: return launch<T, OpAdd>(x, n, init_host, out, scratch, stream);
+    case B2K_MUL: return launch<T, OpMul>(x, n, init_host, out, scratch, stream);
+    case B2K_MAX: return launch<T, OpMax>(x, n, init_host, out, scratch, stream);
+    case B2K_MIN: return launch<T, OpMin>(x, n, init_host, out, scratch, stream);
+    default: break;
+    }
+    if constexpr (!(std::is_same<T, float>::value || std::is_same<T, double>::value)) {
+        switch (op) {
+        case B2K_AND: return launch<T, OpAnd>(x, n, init_host, out, scratch, stream);
+        case B2K_OR: return launch<T, OpOr>(x, n, init_host, out, scratch, stream);
+        case B2K_XOR: return launch<T, OpXor>(x, n, init_host, out, scratch, stream);
+        default: break;
+        }
+    }
+    return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce: op %d is not defined for dtype", op);
+}
+
+size_t dtype_size(int dtype) {
+    switch (dtype) {
+    case B2K_I8: case B2K_U8: return 1;
+    case B2K_I16: case B2K_U16: return 2;
+    case B2K_I32: case B2K_U32: case B2K_F32: return 4;
+    case B2K_I64: case B2K_U64: case B2K_F64: return 8;
+    default: return 0;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b2k_reduce_scratch_bytes(void) { return kTicketBytes + 8 * static_cast<int64_t>(kMaxGrid); }
+
+int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+               void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    const size_t size = dtype_size(dtype);
+    if (size == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown dtype %d", dtype);
+    if (op < B2K_ADD || op > B2K_XOR) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown op %d", op);
+    if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: negative length %lld", (long long)n);
+    if (!init_host || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: null init or out");
+    if (n > 0 && !x_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: null input with n > 0");
+    if (!scratch_dev || scratch_bytes < b2k_reduce_scratch_bytes())
+        return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce: scratch of %lld bytes required",
+                         (long long)b2k_reduce_scratch_bytes());
+    if (!b2k::aligned_to<void>(x_dev, size) || !b2k::aligned_to<void>(out_dev, size))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce: pointers must be aligned to the element size");
+    if (!b2k::aligned_to<void>(scratch_dev, 256))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce: scratch must be 256-byte aligned");
+    cudaStream_t s = b2k::as_stream(stream);
+    switch (dtype) {
+    case B2K_I8: return dispatch_op<int8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_I16: return dispatch_op<int16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_I32: return dispatch_op<int32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_I64: return dispatch_op<int64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_U8: return dispatch_op<uint8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_U16: return dispatch_op<uint16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_U32: return dispatch_op<uint32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_U64: return dispatch_op<uint64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    }
+}
+
+}  // extern "C"

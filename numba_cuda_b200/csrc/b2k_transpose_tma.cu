@@ -1,0 +1,291 @@
+// TMA tile transpose for items of 1, 2, 4, 8 or 16 bytes (sm_100a).
+//
+// Replaces the one-element-per-thread tile kernel of
+// numba/cuda/kernels/transpose.py:42-57 for arrays whose rows are contiguous
+// and 16-byte aligned on both sides.
+//
+// Data path of one input tile of R rows x 128 bytes (128/ES columns):
+//
+//   global --cp.async.bulk.tensor (tiled, 128-byte swizzle)--> stage A[s]
+//   A[s]   --ld.shared.v4 per (row, 16-byte chunk); lanes walk rows, and the
+//            swizzle puts chunk q of row r at chunk (q ^ (r & 7)), so a
+//            quarter-warp always touches eight different bank groups----------.
+//   B[b]   <-st.shared of single items, lanes walk the contiguous direction <-'
+//   B[b]   --cp.async.bulk.tensor store (tiled, no swizzle)--> global
+//
+// B holds the transposed tile as (128/ES) output rows of R items.  Edge tiles
+// need no code: out-of-range parts of a load read as zero and out-of-range
+// parts of a store are dropped by the tensor-map bounds.
+//
+// Persistent CTAs walk tiles in input row-major order so that CTAs running at
+// the same time read neighbouring lines; a ring of NSTAGE loads per CTA stays in
+// flight and B is double buffered against the asynchronous store.
+//
+// HBM roofline: 2*ES bytes per item (one read, one write).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "b2k_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr uint32_t kWaitLimit = 1u << 22;  // mbarrier polls before giving up
+
+__device__ unsigned int g_wait_timeouts = 0;  // bumped when a bounded wait runs out
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait: false when the phase did not complete within kWaitLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, const void *src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(smem_addr(src))
+                 : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void tma_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int ES> struct Item;
+template <> struct Item<1> { using type = uint8_t; };
+template <> struct Item<2> { using type = uint16_t; };
+template <> struct Item<4> { using type = uint32_t; };
+template <> struct Item<8> { using type = uint2; };
+template <> struct Item<16> { using type = uint4; };
+
+// Transpose one staged tile: A is R rows x 128 B (swizzled), B is (128/ES) rows
+// of R items (linear).
+template <int ES, int R>
+__device__ __forceinline__ void transpose_tile(const unsigned char *A, unsigned char *B) {
+    using T = typename Item<ES>::type;
+    constexpr int EPC = 16 / ES;  // items per 16-byte chunk
+    constexpr int ITEMS = R * 8;  // (row, chunk) pairs
+    static_assert(ITEMS % kThreads == 0, "tile must split evenly over the block");
+#pragma unroll
+    for (int w = threadIdx.x; w < ITEMS; w += kThreads) {
+        const int r = w % R;
+        const int q = w / R;
+        const uint4 v = *reinterpret_cast<const uint4 *>(A + r * 128 + ((q ^ (r & 7)) << 4));
+        union { uint4 raw; T e[EPC]; } u;
+        u.raw = v;
+        T *dst = reinterpret_cast<T *>(B) + static_cast<size_t>(q * EPC) * R + r;
+#pragma unroll
+        for (int k = 0; k < EPC; ++k) dst[k * R] = u.e[k];
+    }
+}
+
+template <int ES, int R, int NSTAGE>
+__global__ void __launch_bounds__(kThreads)
+transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
+                     int tiles_x, long long tiles) {
+    constexpr int TILE_BYTES = R * 128;
+    constexpr int TCOLS = 128 / ES;
+    extern __shared__ unsigned char smem_raw[];
+    // the 128-byte swizzle pattern is a function of address bits 7..9
+    unsigned char *base = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char *A = base;
+    unsigned char *B = base + NSTAGE * TILE_BYTES;
+    uint64_t *full = reinterpret_cast<uint64_t *>(B + 2 * TILE_BYTES);
+
+    const long long first = blockIdx.x;
+    const long long step = gridDim.x;
+
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+        // fill the ring
+#pragma unroll
+        for (int s = 0; s < NSTAGE; ++s) {
+            const long long id = first + s * step;
+            if (id < tiles) {
+                mbar_expect_tx(&full[s], TILE_BYTES);
+                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(id % tiles_x) * TCOLS,
+                            static_cast<int>(id / tiles_x) * R, &full[s]);
+            }
+        }
+    }
+    __syncthreads();
+
+    bool ok = true;
+    int it = 0;
+    for (long long id = first; id < tiles; id += step, ++it) {
+        const int s = it % NSTAGE;
+        const int b = it & 1;
+        if (threadIdx.x == 0) tma_wait_read<1>();  // the store that last read B[b] has drained
+        ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+        // every thread polls the same barrier, so the vote only guards against skew
+        if (!__syncthreads_and(ok)) { ok = false; break; }
+
+        transpose_tile<ES, R>(A + s * TILE_BYTES, B + b * TILE_BYTES);
+        fence_async_smem();
+        __syncthreads();
+
+        if (threadIdx.x == 0) {
+            // output coordinates: x runs along input rows, y along input columns
+            tma_store_2d(&out_map, static_cast<int>(id / tiles_x) * R, static_cast<int>(id % tiles_x) * TCOLS,
+                         B + b * TILE_BYTES);
+            tma_commit();
+            const long long next = id + NSTAGE * step;
+            if (next < tiles) {
+                mbar_expect_tx(&full[s], TILE_BYTES);
+                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(next % tiles_x) * TCOLS,
+                            static_cast<int>(next / tiles_x) * R, &full[s]);
+            }
+        }
+    }
+    if (threadIdx.x == 0) {
+        if (!ok) atomicAdd(&g_wait_timeouts, 1u);
+        tma_wait_all();
+    }
+}
+
+// ---- host --------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static std::mutex mu;
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A 2-D map over `rows` lines of `cols` items (ES bytes each, lines `pitch` bytes
+// apart) with a box of box_cols x box_rows items.
+template <int ES>
+bool make_map(CUtensorMap *map, const void *ptr, int64_t rows, int64_t cols, int64_t pitch, int box_cols,
+              int box_rows, bool swizzle) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    // map elements: the item itself up to 4 bytes, 32-bit words for wider items
+    constexpr int UNIT = ES >= 4 ? 4 : ES;
+    constexpr int WORDS = ES / UNIT;
+    const CUtensorMapDataType type = UNIT == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32
+                                     : UNIT == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols) * WORDS, static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols * WORDS), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return enc(map, type, 2, const_cast<void *>(ptr), dims, strides, box, elem_strides,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int ES, int R, int NSTAGE>
+int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pitch, int64_t out_pitch,
+           cudaStream_t stream) {
+    constexpr int TCOLS = 128 / ES;
+    constexpr int UNIT = ES >= 4 ? 4 : ES;
+    static_assert(R * (ES / UNIT) <= 256, "store box exceeds the tensor-map limit");
+    CUtensorMap in_map, out_map;
+    if (!make_map<ES>(&in_map, in, rows, cols, in_pitch, TCOLS, R, true) ||
+        !make_map<ES>(&out_map, out, cols, rows, out_pitch, R, TCOLS, false))
+        return B2K_ERR_UNSUPPORTED;
+    const int64_t tiles_x = (cols + TCOLS - 1) / TCOLS;
+    const int64_t tiles_y = (rows + R - 1) / R;
+    const int64_t tiles = tiles_x * tiles_y;
+    constexpr int SMEM = (NSTAGE + 2) * R * 128 + NSTAGE * 8 + 1024;
+    auto kernel = transpose_tma_kernel<ES, R, NSTAGE>;
+    static std::once_flag once;
+    static cudaError_t attr_status = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    });
+    if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
+    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 200 * 1024 / SMEM);
+    int64_t grid = static_cast<int64_t>(b2k::sm_count()) * (per_sm < 1 ? 1 : per_sm);
+    if (grid > tiles) grid = tiles;
+    kernel<<<static_cast<unsigned>(grid), kThreads, SMEM, stream>>>(in_map, out_map, static_cast<int>(tiles_x),
+                                                                    static_cast<long long>(tiles));
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_transpose2d (tma) launch");
+    return B2K_OK;
+}
+
+}  // namespace
+
+namespace b2k {
+
+int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_stride0, int64_t in_stride1,
+                  int64_t out_stride0, int64_t out_stride1, int64_t itemsize, cudaStream_t stream) {
+    if (itemsize != 1 && itemsize != 2 && itemsize != 4 && itemsize != 8 && itemsize != 16)
+        return B2K_ERR_UNSUPPORTED;
+    // tensor-map rules: contiguous lines, 16-byte aligned bases and pitches
+    if (in_stride1 != itemsize || out_stride1 != itemsize) return B2K_ERR_UNSUPPORTED;
+    if (!aligned_to<void>(in, 16) || !aligned_to<void>(out, 16)) return B2K_ERR_UNSUPPORTED;
+    if (in_stride0 % 16 != 0 || out_stride0 % 16 != 0) return B2K_ERR_UNSUPPORTED;
+    if (in_stride0 < cols * itemsize || out_stride0 < rows * itemsize) return B2K_ERR_UNSUPPORTED;
+    if (in_stride0 >= (int64_t(1) << 40) || out_stride0 >= (int64_t(1) << 40)) return B2K_ERR_UNSUPPORTED;
+    if (rows * (itemsize >= 4 ? itemsize / 4 : 1) >= (int64_t(1) << 31) ||
+        cols * (itemsize >= 4 ? itemsize / 4 : 1) >= (int64_t(1) << 31))
+        return B2K_ERR_UNSUPPORTED;
+    // small arrays: the general tile kernel has less fixed cost
+    if (rows * cols * itemsize < b2k::env_int("B2K_TRANSPOSE_TMA_MIN_BYTES", 1 << 16)) return B2K_ERR_UNSUPPORTED;
+    switch (itemsize) {
+    case 1: return launch<1, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 2: return launch<2, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 4: return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 8: return launch<8, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    default: return launch<16, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    }
+}
+
+}  // namespace b2k
+
+// Number of bounded waits that ran out in TMA transpose kernels on the current
+// device since the library was loaded (0 in a healthy run).  Synchronises.
+extern "C" B2K_API int b2k_transpose_wait_timeouts(unsigned int *count_out) {
+    if (!count_out) return b2k::fail(B2K_ERR_INVALID_ARG, "null output");
+    return b2k::check_cuda(cudaMemcpyFromSymbol(count_out, g_wait_timeouts, sizeof(unsigned int)),
+                           "b2k_transpose_wait_timeouts");
+}

@@ -1,0 +1,440 @@
+// xoroshiro128+ : parallel state creation with jump-ahead, and fused bulk draws.
+//
+// State creation.  The reference builds the states on the CPU as a serial
+// chain, state[i] = jump(state[i-1]) with 128 generator steps per jump
+// (numba/cuda/random.py:242-257), then copies them to the device.  Here every
+// thread computes its states directly:
+//
+//   * the generator step is linear over GF(2), so jump is a 128x128 bit matrix J
+//     and state[i] = J^i v (v = SplitMix64 of the seed, random.py:63-85);
+//   * J is annihilated by a degree-128 polynomial P (found once per process by
+//     solving u_128 = sum_j P_j u_j over GF(2) on a probe sequence u_j = J^j v0,
+//     then re-checked on a second probe), hence
+//         J^i v = sum_j c_j u_j   with  c(y) = y^i mod P(y),  u_j = J^j v;
+//   * the host computes the 128 seed-dependent basis states u_j with the serial
+//     recipe (16 k generator steps) and passes them as a kernel parameter;
+//   * a thread owning states [first, first+L) gets y^(start+first) mod P as a
+//     product of per-byte table entries Y[l][b] = y^(b*256^l) (seed-independent
+//     table in device memory), then alternates "combine basis states under the
+//     128-bit mask c" and "c <- c*y mod P" (one shift and one conditional xor).
+//
+// Bulk draws.  One lane owns one generator, keeps (s0, s1) in registers for all
+// its draws and writes the state back once (the reference reloads and stores
+// the state on every draw, random.py:97-115).  Each warp stages a 32-generator
+// x 32-value block in shared memory and flushes it row by row so that every
+// global store instruction covers whole 128-byte lines of the [n, count] output.
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "b2k_internal.cuh"
+
+namespace {
+
+// ---- host-side restatement of the generator (random.py:63-142) --------------
+struct State { uint64_t s0, s1; };
+
+inline uint64_t rotl_h(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
+
+inline State seed_state(uint64_t seed) {
+    uint64_t z = seed + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return State{z, z};
+}
+inline void step_h(State &s) {
+    uint64_t a = s.s0, b = s.s1 ^ s.s0;
+    s.s0 = rotl_h(a, 55) ^ b ^ (b << 14);
+    s.s1 = rotl_h(b, 36);
+}
+inline void jump_h(State &s) {
+    static const uint64_t kJump[2] = {0xBEAC0467EBA5FACBull, 0xD86B048B86AA9922ull};
+    uint64_t a0 = 0, a1 = 0;
+    for (int w = 0; w < 2; ++w)
+        for (int b = 0; b < 64; ++b) {
+            if ((kJump[w] >> b) & 1ull) { a0 ^= s.s0; a1 ^= s.s1; }
+            step_h(s);
+        }
+    s.s0 = a0;
+    s.s1 = a1;
+}
+
+// ---- GF(2)[y] / P(y) ------------------------------------------------------------
+struct Poly { uint64_t lo, hi; };  // coefficient of y^k is bit k
+
+struct RingConstants {
+    bool ready = false;
+    bool valid = false;
+    Poly p_low{};                  // P(y) = y^128 + p_low(y)
+    Poly ytab[8][256];             // ytab[l][b] = y^(b * 256^l) mod P
+};
+RingConstants g_ring;
+std::mutex g_ring_mutex;
+
+inline Poly times_y(Poly a, const Poly &p_low) {
+    const bool carry = (a.hi >> 63) != 0;
+    a.hi = (a.hi << 1) | (a.lo >> 63);
+    a.lo <<= 1;
+    if (carry) { a.lo ^= p_low.lo; a.hi ^= p_low.hi; }
+    return a;
+}
+inline Poly mulmod_h(const Poly &a, const Poly &b, const Poly &p_low) {
+    Poly r{0, 0};
+    for (int i = 127; i >= 0; --i) {
+        r = times_y(r, p_low);
+        const uint64_t bit = (i < 64) ? (a.lo >> i) & 1ull : (a.hi >> (i - 64)) & 1ull;
+        if (bit) { r.lo ^= b.lo; r.hi ^= b.hi; }
+    }
+    return r;
+}
+
+// Solve sum_j c_j u_j = u_128 over GF(2) for the coefficient mask c.
+bool solve_recurrence(const State *u /* 129 states */, Poly *out) {
+    // rows = the 128 state bits; columns 0..127 = u_j, column 128 = right-hand side
+    struct Row { uint64_t w[3]; };
+    Row rows[128];
+    for (int bit = 0; bit < 128; ++bit) {
+        Row r{{0, 0, 0}};
+        for (int j = 0; j <= 128; ++j) {
+            const uint64_t word = bit < 64 ? u[j].s0 : u[j].s1;
+            if ((word >> (bit & 63)) & 1ull) r.w[j >> 6] |= 1ull << (j & 63);
+        }
+        rows[bit] = r;
+    }
+    int pivot_row_of_col[128];
+    int next_row = 0;
+    for (int col = 0; col < 128; ++col) {
+        int found = -1;
+        for (int r = next_row; r < 128; ++r)
+            if ((rows[r].w[col >> 6] >> (col & 63)) & 1ull) { found = r; break; }
+        if (found < 0) return false;  // basis not of full rank
+        Row tmp = rows[found]; rows[found] = rows[next_row]; rows[next_row] = tmp;
+        for (int r = 0; r < 128; ++r)
+            if (r != next_row && ((rows[r].w[col >> 6] >> (col & 63)) & 1ull))
+                for (int k = 0; k < 3; ++k) rows[r].w[k] ^= rows[next_row].w[k];
+        pivot_row_of_col[col] = next_row++;
+    }
+    Poly c{0, 0};
+    for (int col = 0; col < 128; ++col)
+        if (rows[pivot_row_of_col[col]].w[2] & 1ull) {
+            if (col < 64) c.lo |= 1ull << col; else c.hi |= 1ull << (col - 64);
+        }
+    *out = c;
+    return true;
+}
+
+void basis_states(uint64_t seed, State *u, int count) {
+    u[0] = seed_state(seed);
+    for (int j = 1; j < count; ++j) { u[j] = u[j - 1]; jump_h(u[j]); }
+}
+
+const RingConstants &ring() {
+    std::lock_guard<std::mutex> lock(g_ring_mutex);
+    if (g_ring.ready) return g_ring;
+    g_ring.ready = true;
+    State u[129];
+    basis_states(0x243F6A8885A308D3ull, u, 129);
+    Poly p{};
+    if (!solve_recurrence(u, &p)) return g_ring;
+    // independent check on another sequence: u_128 must equal the masked xor
+    basis_states(0x13198A2E03707344ull, u, 129);
+    uint64_t x0 = 0, x1 = 0;
+    for (int j = 0; j < 128; ++j) {
+        const uint64_t bit = j < 64 ? (p.lo >> j) & 1ull : (p.hi >> (j - 64)) & 1ull;
+        if (bit) { x0 ^= u[j].s0; x1 ^= u[j].s1; }
+    }
+    if (x0 != u[128].s0 || x1 != u[128].s1) return g_ring;
+    g_ring.p_low = p;
+    Poly base{2, 0};  // y
+    for (int l = 0; l < 8; ++l) {
+        g_ring.ytab[l][0] = Poly{1, 0};
+        g_ring.ytab[l][1] = base;
+        for (int b = 2; b < 256; ++b) g_ring.ytab[l][b] = mulmod_h(g_ring.ytab[l][b - 1], base, p);
+        base = mulmod_h(g_ring.ytab[l][255], base, p);
+    }
+    g_ring.valid = true;
+    return g_ring;
+}
+
+constexpr int64_t kTablesBytes = 8 * 256 * 16;
+
+// ---- device: state creation -------------------------------------------------------
+struct Basis { uint32_t w[128][4]; };  // u_j as four little-endian 32-bit words
+
+struct Poly4 { uint32_t w[4]; };
+
+__device__ __forceinline__ void times_y_d(Poly4 &a, const Poly4 &p_low) {
+    const uint32_t carry = static_cast<uint32_t>(static_cast<int32_t>(a.w[3]) >> 31);  // 0 or ~0
+    a.w[3] = __funnelshift_l(a.w[2], a.w[3], 1);
+    a.w[2] = __funnelshift_l(a.w[1], a.w[2], 1);
+    a.w[1] = __funnelshift_l(a.w[0], a.w[1], 1);
+    a.w[0] <<= 1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) a.w[k] ^= carry & p_low.w[k];
+}
+
+__device__ __forceinline__ Poly4 mulmod_d(const Poly4 &a, const Poly4 &b, const Poly4 &p_low) {
+    Poly4 r{{0, 0, 0, 0}};
+    for (int word = 3; word >= 0; --word) {
+        const uint32_t aw = a.w[word];
+        for (int bit = 31; bit >= 0; --bit) {
+            times_y_d(r, p_low);
+            const uint32_t m = static_cast<uint32_t>(static_cast<int32_t>(aw << (31 - bit)) >> 31);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r.w[k] ^= m & b.w[k];
+        }
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(256)
+xoro_init_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_thread,
+                 const uint4 *__restrict__ ytab, const __grid_constant__ Basis basis,
+                 const Poly4 p_low) {
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t first = t * per_thread;
+    if (first >= n) return;
+
+    // c(y) = y^(start + first) mod P, one table entry per non-zero exponent byte
+    const uint64_t e = start + static_cast<uint64_t>(first);
+    Poly4 c{{1, 0, 0, 0}};
+    bool have = false;
+    for (int l = 0; l < 8; ++l) {
+        const uint32_t b = static_cast<uint32_t>(e >> (8 * l)) & 0xFFu;
+        if (b == 0) continue;
+        const uint4 raw = __ldg(ytab + l * 256 + b);
+        const Poly4 f{{raw.x, raw.y, raw.z, raw.w}};
+        c = have ? mulmod_d(c, f, p_low) : f;
+        have = true;
+    }
+
+    const int64_t last = (first + per_thread < n) ? first + per_thread : n;
+    for (int64_t i = first; i < last; ++i) {
+        uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+        for (int j = 0; j < 128; ++j) {
+            const uint32_t m =
+                static_cast<uint32_t>(static_cast<int32_t>(c.w[j >> 5] << (31 - (j & 31))) >> 31);
+            s0 ^= m & basis.w[j][0];
+            s1 ^= m & basis.w[j][1];
+            s2 ^= m & basis.w[j][2];
+            s3 ^= m & basis.w[j][3];
+        }
+        states[i] = make_uint4(s0, s1, s2, s3);
+        times_y_d(c, p_low);
+    }
+}
+
+// ---- device: draws ------------------------------------------------------------------
+__device__ __forceinline__ uint64_t rotl_d(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
+
+// random.py:97-115
+__device__ __forceinline__ uint64_t next_d(uint64_t &s0, uint64_t &s1) {
+    const uint64_t out = s0 + s1;
+    s1 ^= s0;
+    s0 = rotl_d(s0, 55) ^ s1 ^ (s1 << 14);
+    s1 = rotl_d(s1, 36);
+    return out;
+}
+// random.py:146-156.  The f64 value (x>>11)*2^-53 is exact, so rounding the
+// 53-bit integer to f32 first and scaling by a power of two gives the same bits
+// as rounding the f64 product.
+__device__ __forceinline__ float unit_f32(uint64_t x) { return __ull2float_rn(x >> 11) * 0x1p-53f; }
+__device__ __forceinline__ double unit_f64(uint64_t x) { return __ull2double_rn(x >> 11) * 0x1p-53; }
+
+// random.py:192-238: Box-Muller, cosine branch, from two f32 uniforms.
+__device__ __forceinline__ float normal_f32(uint64_t &s0, uint64_t &s1) {
+    const float u1 = unit_f32(next_d(s0, s1));
+    const float u2 = unit_f32(next_d(s0, s1));
+    return sqrtf(-2.0f * logf(u1)) * cosf(6.2831855f * u2);
+}
+__device__ __forceinline__ double normal_f64(uint64_t &s0, uint64_t &s1) {
+    const float u1 = unit_f32(next_d(s0, s1));
+    const float u2 = unit_f32(next_d(s0, s1));
+    return sqrt(-2.0 * static_cast<double>(logf(u1))) * cos(6.283185307179586 * static_cast<double>(u2));
+}
+
+struct Segment {
+    void *out;
+    int64_t count;
+    int draw;
+};
+
+constexpr int kFillWarps = 8;
+constexpr int kPitch32 = 33;  // words per staged row of 32 f32 values
+constexpr int kPitch64 = 17;  // doubles per staged row of 16 f64 values
+constexpr int kStageBytes = 32 * kPitch64 * 8;  // >= 32*kPitch32*4
+
+template <typename T, int DRAW>
+__device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
+    if constexpr (DRAW == B2K_UNIFORM_F32) return unit_f32(next_d(s0, s1));
+    else if constexpr (DRAW == B2K_UNIFORM_F64) return unit_f64(next_d(s0, s1));
+    else if constexpr (DRAW == B2K_NORMAL_F32) return normal_f32(s0, s1);
+    else return normal_f64(s0, s1);
+}
+
+// One segment for the 32 generators [base, base+32) of this warp.
+template <typename T, int DRAW>
+__device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
+                                             int64_t n, const Segment &seg, void *stage) {
+    constexpr int CHUNK = sizeof(T) == 4 ? 32 : 16;
+    constexpr int PITCH = sizeof(T) == 4 ? kPitch32 : kPitch64;
+    constexpr int ROWS_PER_STORE = 32 / CHUNK;
+    T *buf = static_cast<T *>(stage);
+    T *out = static_cast<T *>(seg.out);
+    const int lane = threadIdx.x & 31;
+    for (int64_t c0 = 0; c0 < seg.count; c0 += CHUNK) {
+        const int m = (seg.count - c0 < CHUNK) ? static_cast<int>(seg.count - c0) : CHUNK;
+        if (live) {
+            if (m == CHUNK) {
+#pragma unroll 4
+                for (int i = 0; i < CHUNK; ++i) buf[lane * PITCH + i] = draw_one<T, DRAW>(s0, s1);
+            } else {
+                for (int i = 0; i < m; ++i) buf[lane * PITCH + i] = draw_one<T, DRAW>(s0, s1);
+            }
+        }
+        __syncwarp();
+        const int col = lane % CHUNK;
+        const int sub = lane / CHUNK;
+#pragma unroll 4
+        for (int r = 0; r < 32; r += ROWS_PER_STORE) {
+            const int row = r + sub;
+            const int64_t g = base + row;
+            if (g < n && col < m) out[g * seg.count + c0 + col] = buf[row * PITCH + col];
+        }
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ void run_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
+                                            int64_t n, const Segment &seg, void *stage) {
+    if (seg.count <= 0) return;
+    switch (seg.draw) {  // uniform across the grid
+    case B2K_UNIFORM_F32: fill_segment<float, B2K_UNIFORM_F32>(s0, s1, live, base, n, seg, stage); break;
+    case B2K_UNIFORM_F64: fill_segment<double, B2K_UNIFORM_F64>(s0, s1, live, base, n, seg, stage); break;
+    case B2K_NORMAL_F32: fill_segment<float, B2K_NORMAL_F32>(s0, s1, live, base, n, seg, stage); break;
+    default: fill_segment<double, B2K_NORMAL_F64>(s0, s1, live, base, n, seg, stage); break;
+    }
+}
+
+__global__ void __launch_bounds__(kFillWarps * 32)
+xoro_fill_kernel(ulonglong2 *__restrict__ states, int64_t n, Segment seg0, Segment seg1) {
+    __shared__ __align__(16) unsigned char stage_all[kFillWarps][kStageBytes];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    void *stage = stage_all[warp];
+    const int64_t groups = (n + 31) / 32;
+    for (int64_t grp = static_cast<int64_t>(blockIdx.x) * kFillWarps + warp; grp < groups;
+         grp += static_cast<int64_t>(gridDim.x) * kFillWarps) {
+        const int64_t base = grp * 32;
+        const int64_t g = base + lane;
+        const bool live = g < n;
+        uint64_t s0 = 0, s1 = 0;
+        if (live) {
+            const ulonglong2 s = states[g];
+            s0 = s.x;
+            s1 = s.y;
+        }
+        run_segment(s0, s1, live, base, n, seg0, stage);
+        run_segment(s0, s1, live, base, n, seg1, stage);
+        if (live) states[g] = make_ulonglong2(s0, s1);
+    }
+}
+
+size_t draw_size(int draw) {
+    switch (draw) {
+    case B2K_UNIFORM_F32: case B2K_NORMAL_F32: return 4;
+    case B2K_UNIFORM_F64: case B2K_NORMAL_F64: return 8;
+    default: return 0;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b2k_xoroshiro128p_tables_bytes(void) { return kTablesBytes; }
+
+int b2k_xoroshiro128p_build_tables(void *tables_dev, int64_t tables_bytes, void *stream) {
+    if (!tables_dev || tables_bytes < kTablesBytes)
+        return b2k::fail(B2K_ERR_SCRATCH, "b2k_xoroshiro128p_build_tables: %lld bytes required",
+                         (long long)kTablesBytes);
+    const RingConstants &rc = ring();
+    if (!rc.valid)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "xoroshiro128p: jump recurrence self-check failed");
+    // the source is static storage that is never modified after construction
+    return b2k::check_cuda(cudaMemcpyAsync(tables_dev, rc.ytab, kTablesBytes, cudaMemcpyHostToDevice,
+                                           b2k::as_stream(stream)),
+                           "b2k_xoroshiro128p_build_tables copy");
+}
+
+int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t subsequence_start,
+                           const void *tables_dev, int64_t tables_bytes, void *stream) {
+    if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_init: negative n");
+    if (n == 0) return B2K_OK;
+    if (!states_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_init: null states");
+    if (!b2k::aligned_to<void>(states_dev, 16))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_xoroshiro128p_init: states must be 16-byte aligned");
+    if (!tables_dev || tables_bytes < kTablesBytes || !b2k::aligned_to<void>(tables_dev, 16))
+        return b2k::fail(B2K_ERR_SCRATCH, "b2k_xoroshiro128p_init: jump tables missing");
+    const RingConstants &rc = ring();
+    if (!rc.valid)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "xoroshiro128p: jump recurrence self-check failed");
+
+    State u[128];
+    basis_states(seed, u, 128);
+    Basis basis;
+    for (int j = 0; j < 128; ++j) {
+        basis.w[j][0] = static_cast<uint32_t>(u[j].s0);
+        basis.w[j][1] = static_cast<uint32_t>(u[j].s0 >> 32);
+        basis.w[j][2] = static_cast<uint32_t>(u[j].s1);
+        basis.w[j][3] = static_cast<uint32_t>(u[j].s1 >> 32);
+    }
+    Poly4 p_low{{static_cast<uint32_t>(rc.p_low.lo), static_cast<uint32_t>(rc.p_low.lo >> 32),
+                 static_cast<uint32_t>(rc.p_low.hi), static_cast<uint32_t>(rc.p_low.hi >> 32)}};
+
+    // long runs per thread amortise the table products; short arrays stay parallel
+    int per_thread = n >= (int64_t(1) << 22) ? 64 : (n >= (int64_t(1) << 16) ? 16 : 1);
+    per_thread = b2k::env_int("B2K_XORO_INIT_PER_THREAD", per_thread);
+    if (per_thread < 1) per_thread = 1;
+    const int64_t threads = (n + per_thread - 1) / per_thread;
+    const int64_t grid = (threads + 255) / 256;
+    xoro_init_kernel<<<static_cast<unsigned>(grid), 256, 0, b2k::as_stream(stream)>>>(
+        static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
+        static_cast<const uint4 *>(tables_dev), basis, p_low);
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_xoroshiro128p_init launch");
+    return B2K_OK;
+}
+
+int b2k_xoroshiro128p_fill(void *states_dev, int64_t n, int draw0, void *out0_dev, int64_t count0,
+                           int draw1, void *out1_dev, int64_t count1, void *stream) {
+    if (n < 0 || count0 < 0 || count1 < 0)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_fill: negative size");
+    if (n == 0 || (count0 == 0 && count1 == 0)) return B2K_OK;
+    if (!states_dev || !b2k::aligned_to<void>(states_dev, 16))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_xoroshiro128p_fill: states null or not 16-byte aligned");
+    const int draws[2] = {draw0, draw1};
+    void *outs[2] = {out0_dev, out1_dev};
+    const int64_t counts[2] = {count0, count1};
+    for (int k = 0; k < 2; ++k) {
+        if (counts[k] == 0) continue;
+        const size_t size = draw_size(draws[k]);
+        if (size == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_fill: unknown draw %d", draws[k]);
+        if (!outs[k]) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_fill: null output");
+        if (!b2k::aligned_to<void>(outs[k], size))
+            return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_xoroshiro128p_fill: output not aligned to its element size");
+    }
+    const int64_t groups = (n + 31) / 32;
+    int64_t grid = (groups + kFillWarps - 1) / kFillWarps;
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_FILL_CTAS_PER_SM", 6);
+    if (grid > cap) grid = cap;
+    Segment a{out0_dev, count0, draw0}, b{out1_dev, count1, draw1};
+    xoro_fill_kernel<<<static_cast<unsigned>(grid), kFillWarps * 32, 0, b2k::as_stream(stream)>>>(
+        static_cast<ulonglong2 *>(states_dev), n, a, b);
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_xoroshiro128p_fill launch");
+    return B2K_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,207 @@
+"""``cuda.reduce`` / ``Reduce``: full reduction of a 1-D array with a user's
+binary function, on one sm_100a kernel launch.
+
+Same call surface as numba/cuda/kernels/reduction.py:169-265:
+``Reduce(functor)(arr, size=None, res=None, init=0, stream=0)``.
+
+The reference JIT-compiles the Python functor into its kernel.  Here the
+functor is *classified* into the table of ops the precompiled kernels carry
+(add, mul, max, min, and, or, xor): it is evaluated on a fixed set of sample
+pairs and must agree with exactly one table op on all of them.  A functor that
+matches none raises ``NotImplementedError`` -- nothing is ever computed on the
+CPU instead.
+"""
+from __future__ import annotations
+
+import random
+import threading
+
+import numpy as np
+import torch
+
+from .. import _lib
+from ..api import auto_device
+from ..devicearray import DeviceNDArray, _torch_stream, check_array_compatibility, stream_ptr
+
+_WARPSIZE = 32
+_NUMWARPS = 4
+
+_DTYPE_CODES = {
+    np.dtype(np.int8): _lib.I8, np.dtype(np.int16): _lib.I16, np.dtype(np.int32): _lib.I32,
+    np.dtype(np.int64): _lib.I64, np.dtype(np.uint8): _lib.U8, np.dtype(np.uint16): _lib.U16,
+    np.dtype(np.uint32): _lib.U32, np.dtype(np.uint64): _lib.U64,
+    np.dtype(np.float32): _lib.F32, np.dtype(np.float64): _lib.F64,
+}
+
+_OP_TABLE = [
+    ("add", _lib.ADD, lambda a, b: a + b),
+    ("mul", _lib.MUL, lambda a, b: a * b),
+    ("max", _lib.MAX, lambda a, b: b if b > a else a),
+    ("min", _lib.MIN, lambda a, b: b if b < a else a),
+    ("and", _lib.AND, lambda a, b: a & b),
+    ("or", _lib.OR, lambda a, b: a | b),
+    ("xor", _lib.XOR, lambda a, b: a ^ b),
+]
+OP_NAMES = {code: name for name, code, _ in _OP_TABLE}
+
+
+def _sample_pairs(kind: str):
+    rng = random.Random(0xB200)
+    if kind == "f":
+        fixed = [(0.0, 0.0), (1.0, 1.0), (0.0, 3.5), (3.5, 0.0), (-2.25, 7.5), (7.5, -2.25),
+                 (-1.5, -4.0), (0.5, 0.25), (2.0, 2.0)]
+        rnd = [(rng.uniform(-50, 50), rng.uniform(-50, 50)) for _ in range(40)]
+    elif kind == "u":
+        fixed = [(0, 0), (1, 1), (0, 5), (5, 0), (12, 10), (10, 12), (255, 1), (6, 3), (7, 7)]
+        rnd = [(rng.randrange(0, 1000), rng.randrange(0, 1000)) for _ in range(40)]
+    else:
+        fixed = [(0, 0), (1, 1), (0, 5), (5, 0), (-3, 7), (7, -3), (-4, -9), (12, 10), (6, 3), (-1, -1)]
+        rnd = [(rng.randrange(-1000, 1000), rng.randrange(-1000, 1000)) for _ in range(40)]
+    return fixed + rnd
+
+
+def classify_functor(functor, dtype) -> int:
+    """Return the table op code ``functor`` computes on ``dtype`` or raise
+    ``NotImplementedError``.  Pure host logic: probes the functor on Python
+    scalars (ints for integer dtypes, floats for float dtypes)."""
+    dtype = np.dtype(dtype)
+    if dtype not in _DTYPE_CODES:
+        raise NotImplementedError(f"cuda.reduce: dtype {dtype} has no precompiled kernel")
+    kind = dtype.kind
+    pairs = _sample_pairs(kind)
+    matches = []
+    for name, code, ref in _OP_TABLE:
+        if kind == "f" and name in ("and", "or", "xor"):
+            continue
+        ok = True
+        for a, b in pairs:
+            try:
+                got = functor(a, b)
+            except Exception:
+                ok = False
+                break
+            want = ref(a, b)
+            if isinstance(got, (bool, np.bool_)) or got != want:
+                ok = False
+                break
+        if ok:
+            matches.append(code)
+    if len(matches) == 1:
+        return matches[0]
+    raise NotImplementedError(
+        "cuda.reduce: the binary function is not one of the precompiled ops "
+        "(a+b, a*b, max(a,b), min(a,b), a&b, a|b, a^b); arbitrary functors are not supported "
+        "and there is no CPU fallback")
+
+
+class _Scratch:
+    """Per-(device, stream) scratch: ticket + partials for the kernel, and one
+    result slot.  Zero-filled once; the kernel leaves it reusable."""
+
+    _lock = threading.Lock()
+    _pool: dict = {}
+
+    @classmethod
+    def get(cls, stream):
+        key = (torch.cuda.current_device(), stream_ptr(stream))
+        with cls._lock:
+            entry = cls._pool.get(key)
+            if entry is None:
+                nbytes = int(_lib.lib().b2k_reduce_scratch_bytes())
+                with torch.cuda.stream(_torch_stream(stream)):
+                    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+                    result = torch.zeros(16, dtype=torch.uint8, device="cuda")
+                entry = (scratch, result, nbytes)
+                cls._pool[key] = entry
+            return entry
+
+
+class Reduce:
+    """Create a reduction object that reduces values using a given binary
+    function.  The classification of the function is cached per
+    ``(functor, dtype)`` on the class, like the reference's kernel cache
+    (reduction.py:175-192)."""
+
+    _cache: dict = {}
+
+    def __init__(self, functor):
+        self._functor = functor
+
+    def _compile(self, dtype):
+        key = self._functor, np.dtype(dtype)
+        op = self._cache.get(key)
+        if op is None:
+            op = classify_functor(self._functor, dtype)
+            self._cache[key] = op
+        return op
+
+    def __call__(self, arr, size=None, res=None, init=0, stream=0):
+        """Performs a full reduction.
+
+        :param arr: A host or device array (1-D).
+        :param size: Optional number of leading elements to reduce.
+        :param res: Optional device array; the result is written to its first
+                    element and nothing is copied back to the host.
+        :param init: Initial value; it is always folded into the result.
+        :param stream: Optional CUDA stream (0 = default stream).
+        :return: ``None`` if ``res`` is given, else a NumPy scalar of ``arr.dtype``.
+        """
+        # reduction.py:217-228
+        if arr.ndim != 1:
+            raise TypeError("only support 1D array")
+        if size is not None:
+            arr = arr[:size]
+        init = arr.dtype.type(init)
+        if arr.size < 1:
+            return init
+
+        op = self._compile(arr.dtype)
+        darr, _ = auto_device(arr, stream=stream)
+        if darr.strides[0] != darr.dtype.itemsize:
+            darr = _gather_contiguous(darr, stream)
+
+        scratch, slot, scratch_bytes = _Scratch.get(stream)
+        if res is not None:
+            dres, _ = auto_device(res, stream=stream)
+            check_array_compatibility(dres[:1], _OneItem(arr.dtype))
+            out_ptr = dres._ptr
+        else:
+            out_ptr = slot.data_ptr()
+
+        init_host = np.array([init], dtype=arr.dtype)
+        _lib.check(_lib.lib().b2k_reduce(
+            op, _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
+            out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
+        if res is not None:
+            return None
+        host = np.empty(1, dtype=arr.dtype)
+        with torch.cuda.stream(_torch_stream(stream)):
+            torch.from_numpy(host.view(np.uint8)).copy_(slot[: arr.dtype.itemsize])
+        return host[0]
+
+
+class _OneItem:
+    """Shape/stride descriptor of ``partials[:1]`` for the compatibility check."""
+
+    def __init__(self, dtype):
+        self.dtype = np.dtype(dtype)
+        self.shape = (1,)
+        self.strides = (self.dtype.itemsize,)
+        self.size = 1
+
+
+def _gather_contiguous(darr: DeviceNDArray, stream) -> DeviceNDArray:
+    """Unit-stride copy of a strided 1-D device view (device-side gather)."""
+    step = darr.strides[0]
+    item = darr.dtype.itemsize
+    if step <= 0 or step % item:
+        raise NotImplementedError("cuda.reduce: only positive item-multiple strides are supported")
+    from ..api import device_array
+    out = device_array(darr.size, darr.dtype, stream=stream)
+    with torch.cuda.stream(_torch_stream(stream)):
+        src = torch.as_strided(darr._buf[darr._offset:], (darr.size, item), (step, 1))
+        out._bytes_view().view(darr.size, item).copy_(src)
+    return out
+
+
+reduce = Reduce

@@ -1,0 +1,84 @@
+"""The C-ABI library loads and exports every symbol include/b2k.h declares, and
+rejects bad arguments on the host before any CUDA call.  No GPU."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from numba_cuda_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b2k.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b2k_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_bound():
+    names = declared_symbols()
+    assert "b2k_reduce" in names and "b2k_cast" in names and len(names) >= 10
+    assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.lib()
+    for name in declared_symbols():
+        assert getattr(L, name) is not None
+    assert L.b2k_version() >= 100
+    assert L.b2k_reduce_scratch_bytes() >= 256 + 8 * 1024
+    assert L.b2k_xoroshiro128p_tables_bytes() == 8 * 256 * 16
+
+
+def test_argument_errors_are_reported_on_host():
+    L = _lib.lib()
+    init = np.zeros(1, dtype=np.float64)
+    # unknown dtype / op, negative length, null pointers: all before any launch
+    assert L.b2k_reduce(_lib.ADD, 99, None, 0, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_INVALID_ARG
+    assert b"dtype" in L.b2k_last_error()
+    assert L.b2k_reduce(42, _lib.F64, None, 0, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce(_lib.ADD, _lib.F64, None, -1, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce(_lib.ADD, _lib.F64, None, 4, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce(_lib.ADD, _lib.F64, 1024, 4, init.ctypes.data, 8, None, 0, None) == _lib.ERR_SCRATCH
+    assert L.b2k_reduce(_lib.ADD, _lib.F64, 1028, 4, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_reduce(_lib.AND, _lib.F32, 1024, 4, init.ctypes.data, 8, 256, 1 << 20, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast(_lib.FMT_BF16, _lib.FMT_E4M3, 1, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, 1024, 2048, -5, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, None, 2048, 16, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, 1026, 2048, 16, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_transpose2d(None, None, 4, 4, 16, 4, 16, 4, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_transpose2d(1024, 2048, -1, 4, 16, 4, 16, 4, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_xoroshiro128p_init(1024, 8, 1, 0, None, 0, None) == _lib.ERR_SCRATCH
+    assert L.b2k_xoroshiro128p_init(1028, 8, 1, 0, 4096, 1 << 20, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_xoroshiro128p_fill(1024, 8, 7, 2048, 4, 0, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_xoroshiro128p_fill(1024, -8, 0, 2048, 4, 0, None, 0, None) == _lib.ERR_INVALID_ARG
+    # empty work is a no-op that needs no device
+    assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, None, None, 0, None) == 0
+    assert L.b2k_transpose2d(None, None, 0, 4, 16, 4, 0, 4, 4, None) == 0
+    assert L.b2k_xoroshiro128p_init(None, 0, 1, 0, None, 0, None) == 0
+
+
+def test_status_maps_to_python_exceptions():
+    L = _lib.lib()
+    with pytest.raises(NotImplementedError):
+        _lib.check(L.b2k_cast(_lib.FMT_BF16, _lib.FMT_E4M3, 1, 1024, 2048, 16, None))
+    with pytest.raises(ValueError):
+        _lib.check(L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, 1024, 2048, -5, None))
+    _lib.check(0)
+
+
+def test_no_cpu_fallback_without_device():
+    """Without a GPU the public API must raise, not compute on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    import numba_cuda_b200 as cuda
+    with pytest.raises(RuntimeError):
+        cuda.to_device(np.arange(4.0))
+    with pytest.raises(RuntimeError):
+        cuda.reduce(lambda a, b: a + b)(np.arange(4.0))
+    with pytest.raises(RuntimeError):
+        cuda.random.create_xoroshiro128p_states(4, 1)

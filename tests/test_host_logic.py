@@ -1,0 +1,103 @@
+"""Host-side logic of the drop-in: functor classification, indexing math,
+shard bounds, identities.  No GPU."""
+import numpy as np
+import pytest
+
+from numba_cuda_b200 import _lib, casts, sharded
+from numba_cuda_b200.devicearray import (_basic_index, _c_strides, _extent_bytes, _f_strides,
+                                         _is_c_contig, _is_f_contig, stream_ptr)
+from numba_cuda_b200.kernels.reduction import Reduce, classify_functor
+
+
+@pytest.mark.parametrize("fn,code", [
+    (lambda a, b: a + b, _lib.ADD), (lambda a, b: b + a, _lib.ADD), (lambda a, b: a * b, _lib.MUL),
+    (lambda a, b: max(a, b), _lib.MAX), (lambda a, b: min(a, b), _lib.MIN),
+    (lambda a, b: a if a > b else b, _lib.MAX), (lambda a, b: a if a < b else b, _lib.MIN)])
+@pytest.mark.parametrize("dtype", [np.int8, np.int32, np.uint64, np.float32, np.float64])
+def test_classify_arithmetic(fn, code, dtype):
+    assert classify_functor(fn, dtype) == code
+
+
+@pytest.mark.parametrize("fn,code", [(lambda a, b: a & b, _lib.AND), (lambda a, b: a | b, _lib.OR),
+                                     (lambda a, b: a ^ b, _lib.XOR)])
+def test_classify_bitwise(fn, code):
+    assert classify_functor(fn, np.int32) == code
+    assert classify_functor(fn, np.uint8) == code
+    with pytest.raises(NotImplementedError):
+        classify_functor(fn, np.float32)
+
+
+def test_classify_rejects_what_it_cannot_run():
+    for fn in (lambda a, b: a - b, lambda a, b: a + 2 * b, lambda a, b: a > b, lambda a, b: a / (b + 1e9),
+               lambda a, b: a + b if a < 40 else a):
+        with pytest.raises(NotImplementedError):
+            classify_functor(fn, np.float64)
+    with pytest.raises(NotImplementedError):
+        classify_functor(lambda a, b: a + b, np.complex128)
+
+
+def test_reduce_argument_checks_come_first():
+    # reduction.py:217-228: ndim check, then empty -> init, all before any device work
+    r = Reduce(lambda a, b: a + b)
+    with pytest.raises(TypeError, match="only support 1D array"):
+        r(np.zeros((2, 2)))
+    assert r(np.zeros(0, dtype=np.float64)) == 0.0
+    got = r(np.zeros(0, dtype=np.int32), init=7)
+    assert got == 7 and got.dtype == np.int32
+    assert r(np.arange(10.0), size=0, init=3) == 3.0
+
+
+def test_basic_index():
+    shape, strides = (10, 12), (96, 8)
+    assert _basic_index(shape, strides, (slice(None, None, 2), slice(None, None, 2))) == ((5, 6), (192, 16), 0)
+    assert _basic_index(shape, strides, 3) == ((12,), (8,), 288)
+    assert _basic_index(shape, strides, (3, 4)) == ((), (), 288 + 32)
+    assert _basic_index(shape, strides, (-1, slice(2, 5))) == ((3,), (8,), 9 * 96 + 16)
+    assert _basic_index(shape, strides, (Ellipsis, 1)) == ((10,), (96,), 8)
+    assert _basic_index((7,), (4,), slice(5, 2)) == ((0,), (4,), 0)
+    with pytest.raises(IndexError):
+        _basic_index(shape, strides, (10, 0))
+    with pytest.raises(IndexError):
+        _basic_index(shape, strides, (0, 0, 0))
+
+
+def test_layout_helpers():
+    assert _c_strides((3, 4), 8) == (32, 8) and _f_strides((3, 4), 8) == (8, 24)
+    assert _is_c_contig((3, 4), (32, 8), 8) and not _is_c_contig((3, 4), (64, 8), 8)
+    assert _is_f_contig((3, 4), (8, 24), 8) and _is_c_contig((1, 4), (999, 8), 8)
+    assert _extent_bytes((5, 6), (192, 16), 8) == 4 * 192 + 5 * 16 + 8
+    assert _extent_bytes((0, 6), (192, 16), 8) == 0
+    assert stream_ptr(0) == 0 and stream_ptr(None) == 0 and stream_ptr(0x1234) == 0x1234
+
+
+def test_shard_bounds_partition():
+    for n in (0, 1, 7, 1 << 20, (1 << 20) + 13):
+        for world in (1, 2, 4, 8):
+            for align in (1, 16):
+                pieces = [sharded.shard_bounds(n, world, r, align) for r in range(world)]
+                assert pieces[0][0] == 0 and pieces[-1][1] == n
+                for (lo, hi), (lo2, _) in zip(pieces, pieces[1:]):
+                    assert hi == lo2 and lo % align == 0 and lo <= hi
+    with pytest.raises(ValueError):
+        sharded.shard_bounds(10, 2, 2)
+
+
+def test_identities_and_host_fold():
+    for dt in (np.int8, np.uint16, np.int32, np.uint64, np.float32, np.float64):
+        x = (np.random.default_rng(3).integers(0, 100, size=17)).astype(dt)
+        ops = [_lib.ADD, _lib.MUL, _lib.MAX, _lib.MIN] + ([] if np.dtype(dt).kind == "f" else [_lib.AND, _lib.OR, _lib.XOR])
+        for op in ops:
+            ident = sharded.op_identity(op, dt)
+            assert ident.dtype == np.dtype(dt)
+            assert sharded.host_fold(op, x[:1], ident) == x[0]
+    x = np.array([200, 100, 7], dtype=np.uint8)
+    assert sharded.host_fold(_lib.ADD, x, np.uint8(0)) == np.uint8((200 + 100 + 7) % 256)
+    assert sharded.host_fold(_lib.MAX, np.array([-5, -9], dtype=np.int32), np.int32(0)) == 0
+
+
+def test_format_names():
+    assert casts._format_code("e4m3") == _lib.FMT_E4M3 and casts._format_code("bfloat16") == _lib.FMT_BF16
+    assert casts._format_code(_lib.FMT_F32) == _lib.FMT_F32
+    assert casts.saturation_t.SATFINITE == 1 and casts.fp8_interpretation_t.E5M2 == 1
+    with pytest.raises(ValueError):
+        casts._format_code("fp4")

@@ -1,0 +1,235 @@
+"""xoroshiro128p on the GPU against the CPU oracle and the reference-generated
+fixtures.  Restates numba/cuda/tests/cudapy/test_random.py (creation,
+subsequence identity, stream, distribution moments) and adds bit-exact
+comparison of states and draws."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import numba_cuda_b200 as cuda
+from numba_cuda_b200 import _lib
+from numba_cuda_b200.random import (create_xoroshiro128p_states, init_xoroshiro128p_states,
+                                    xoroshiro128p_dtype, xoroshiro128p_fill,
+                                    xoroshiro128p_normal_float32, xoroshiro128p_normal_float64,
+                                    xoroshiro128p_uniform_float32, xoroshiro128p_uniform_float64)
+
+pytestmark = pytest.mark.gpu
+
+
+def pairs(st):
+    return np.stack([st["s0"], st["s1"]], axis=1)
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return np.load(os.path.join(golden_dir, "rng_reference.npz"))
+
+
+def test_create():
+    # test_random.py:57-60
+    states = create_xoroshiro128p_states(10, seed=1)
+    s = states.copy_to_host()
+    assert s.dtype == xoroshiro128p_dtype
+    assert len(np.unique(s)) == 10
+
+
+def test_create_subsequence_start():
+    # test_random.py:62-72
+    states = create_xoroshiro128p_states(10, seed=1)
+    s1 = states.copy_to_host()
+    states = create_xoroshiro128p_states(10, seed=1, subsequence_start=3)
+    s2 = states.copy_to_host()
+    np.testing.assert_array_equal(s1[3:], s2[:-3])
+
+
+def test_create_stream():
+    stream = cuda.stream()
+    states = create_xoroshiro128p_states(10, seed=1, stream=stream)
+    stream.synchronize()
+    s = states.copy_to_host()
+    assert len(np.unique(s)) == 10
+    np.testing.assert_array_equal(pairs(s), pairs(oracle.init_states(10, 1, 0)))
+
+
+def test_states_match_reference_fixtures(gold):
+    def dev(n, seed, start):
+        return pairs(create_xoroshiro128p_states(n, seed, start).copy_to_host())
+    assert (dev(64, 42, 0) == gold["states_seed42_n64"]).all()
+    assert (dev(4, 1, 0) == gold["states_seed1_n4"]).all()
+    assert (dev(8, 1, 2) == gold["states_seed1_start2_n8"]).all()
+    assert (dev(4, 7, 1000) == gold["states_seed7_start1000_n4"]).all()
+    big = create_xoroshiro128p_states(1 << 20, 42, 0).copy_to_host()
+    assert (pairs(big[gold["big_idx"]]) == gold["big_states_seed42"]).all()
+    assert (pairs(big[:: int(gold["big_stride"])]) == gold["big_states_seed42_strided"]).all()
+
+
+@pytest.mark.parametrize("n,seed,start", [(1, 0, 0), (2, 2 ** 64 - 1, 0), (33, 5, 1), (1000, 123456789, 77),
+                                          (65535, 9, 0), (65536 + 7, 9, 3), (1 << 18, 2, 255), (100, 3, 65535),
+                                          (300, 3, 65536), (50, 1, (1 << 24) - 25)])
+def test_states_bit_exact_vs_oracle(n, seed, start):
+    if start > 100000:
+        # the serial oracle cannot walk that far: check the chain rule from one state to the next
+        s = create_xoroshiro128p_states(n, seed, start).copy_to_host()
+        for i in (0, 1, 23, 24, 25, n - 2):
+            assert oracle.jump((int(s[i]["s0"]), int(s[i]["s1"]))) == (int(s[i + 1]["s0"]), int(s[i + 1]["s1"]))
+        return
+    got = create_xoroshiro128p_states(n, seed, start).copy_to_host()
+    assert got.tobytes() == oracle.init_states(n, seed, start).tobytes()
+
+
+def test_states_large_array_vs_oracle():
+    n = (1 << 22) + 5            # crosses into the longest per-thread runs
+    got = create_xoroshiro128p_states(n, 42, 0).copy_to_host()
+    assert got.tobytes() == oracle.init_states(n, 42, 0).tobytes()
+
+
+def test_huge_subsequence_start_chain_rule():
+    for start in (1 << 40, (1 << 63) + 12345, 2 ** 64 - 300):
+        s = create_xoroshiro128p_states(256, 11, start).copy_to_host()
+        for i in (0, 100, 254):
+            assert oracle.jump((int(s[i]["s0"]), int(s[i]["s1"]))) == (int(s[i + 1]["s0"]), int(s[i + 1]["s1"]))
+        t = create_xoroshiro128p_states(8, 11, start + 248).copy_to_host()
+        assert t.tobytes() == s[248:].tobytes()
+
+
+def test_init_in_place_and_argument_checks():
+    st = cuda.device_array(100, dtype=xoroshiro128p_dtype)
+    init_xoroshiro128p_states(st, seed=77, subsequence_start=2)
+    assert st.copy_to_host().tobytes() == oracle.init_states(100, 77, 2).tobytes()
+    with pytest.raises(TypeError):
+        init_xoroshiro128p_states(cuda.device_array(10, dtype=np.float64), 1)
+
+
+@pytest.mark.parametrize("dist,dtype", [("uniform", np.float32), ("uniform", np.float64)])
+@pytest.mark.parametrize("n,count", [(1, 1), (4, 64), (31, 7), (33, 33), (100, 70), (1000, 128), (2049, 5)])
+def test_uniform_draws_bit_exact(dist, dtype, n, count):
+    st_host = oracle.init_states(n, 42, 0)
+    st_dev = create_xoroshiro128p_states(n, 42, 0)
+    got = xoroshiro128p_fill(st_dev, dist, count=count, dtype=dtype).copy_to_host()
+    want = oracle.fill(st_host, dist, dtype, count)
+    assert got.shape == (n, count)
+    assert got.tobytes() == want.tobytes()
+    assert st_dev.copy_to_host().tobytes() == st_host.tobytes()      # states advanced identically
+
+
+def test_uniform_draws_match_reference_fixture(gold):
+    st = create_xoroshiro128p_states(4, 42, 0)
+    assert xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32).copy_to_host().tobytes() == gold["uniform_f32"].tobytes()
+    assert (pairs(st.copy_to_host()) == gold["uniform_f32_end"]).all()
+    st = create_xoroshiro128p_states(4, 42, 0)
+    assert xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float64).copy_to_host().tobytes() == gold["uniform_f64"].tobytes()
+
+
+def ulp_diff(a, b):
+    itype = np.int32 if a.dtype == np.float32 else np.int64
+    ia, ib = a.view(itype).astype(np.int64), b.view(itype).astype(np.int64)
+    ia = np.where(ia < 0, np.iinfo(itype).min - ia, ia)
+    ib = np.where(ib < 0, np.iinfo(itype).min - ib, ib)
+    return np.abs(ia - ib)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_normal_draws_vs_cpu_restatement(dtype, gold):
+    # The GPU uses libdevice's logf/cos/cosf, the CPU oracle the host libm, so this
+    # is a tolerance check (a few ulp of the result, looser where cos() is near 0);
+    # the state stream itself must be bit-exact.
+    n, count = 257, 40
+    st_host = oracle.init_states(n, 42, 0)
+    st_dev = create_xoroshiro128p_states(n, 42, 0)
+    got = xoroshiro128p_fill(st_dev, "normal", count=count, dtype=dtype).copy_to_host()
+    want = oracle.fill(st_host, "normal", dtype, count)
+    assert st_dev.copy_to_host().tobytes() == st_host.tobytes()
+    finite = np.isfinite(want)
+    assert (np.isfinite(got) == finite).all()
+    eps = np.finfo(dtype).eps
+    err = np.abs(got[finite] - want[finite])
+    # error budget: rounding of sqrt/log/cos plus the argument error of cos(2*pi*u2)
+    assert (err <= 64 * eps * np.maximum(np.abs(want[finite]), 1.0)).all(), err.max()
+    frac_exact = (ulp_diff(got[finite], want[finite]) == 0).mean()
+    print(f"normal {np.dtype(dtype).name}: {frac_exact:.4f} of draws bit-identical to host libm")
+    key = "normal_f32_hostlibm" if dtype == np.float32 else "normal_f64_hostlibm"
+    st = create_xoroshiro128p_states(4, 42, 0)
+    g = xoroshiro128p_fill(st, "normal", count=32, dtype=dtype).copy_to_host()
+    np.testing.assert_allclose(g, gold[key], rtol=64 * eps, atol=64 * eps)
+
+
+def test_fused_config4_sequence_small(gold):
+    st = create_xoroshiro128p_states(8, 42, 0)
+    u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+    assert u.copy_to_host().tobytes() == gold["c4_u"].tobytes()
+    np.testing.assert_allclose(z.copy_to_host(), gold["c4_z_hostlibm"], rtol=1e-13, atol=1e-13)
+    assert (pairs(st.copy_to_host()) == gold["c4_end"]).all()
+    # fused launch == two launches
+    st2 = create_xoroshiro128p_states(8, 42, 0)
+    u2 = xoroshiro128p_fill(st2, "uniform", count=64, dtype=np.float32)
+    z2 = xoroshiro128p_fill(st2, "normal", count=16, dtype=np.float64)
+    assert u2.copy_to_host().tobytes() == u.copy_to_host().tobytes()
+    assert z2.copy_to_host().tobytes() == z.copy_to_host().tobytes()
+    assert st2.copy_to_host().tobytes() == st.copy_to_host().tobytes()
+
+
+def test_config4_shapes_sharded_equals_single():
+    # configuration 4 at 1/64 scale: sharding by state index reproduces the single-GPU stream
+    n = 1 << 18
+    st = create_xoroshiro128p_states(n, 42, 0)
+    u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+    uh, zh, sh = u.copy_to_host(), z.copy_to_host(), st.copy_to_host()
+    host = oracle.init_states(n, 42, 0)
+    assert oracle.fill(host, "uniform", np.float32, 64).tobytes() == uh.tobytes()
+    for world in (2, 8):
+        for rank in (0, world - 1):
+            s_k, lo, hi = cuda.sharded.create_sharded_xoroshiro128p_states(n, 42, world_size=world, rank=rank)
+            u_k, z_k = xoroshiro128p_fill(s_k, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+            assert u_k.copy_to_host().tobytes() == uh[lo:hi].tobytes()
+            assert z_k.copy_to_host().tobytes() == zh[lo:hi].tobytes()
+            assert s_k.copy_to_host().tobytes() == sh[lo:hi].tobytes()
+
+
+def test_scalar_draw_functions():
+    st = create_xoroshiro128p_states(3, 42, 0)
+    host = oracle.init_states(3, 42, 0)
+    want = oracle.fill(host[1:2], "uniform", np.float32, 2)[0]
+    assert xoroshiro128p_uniform_float32(st, 1) == want[0]
+    assert xoroshiro128p_uniform_float32(st, 1) == want[1]
+    h = oracle.init_states(3, 42, 0)
+    assert xoroshiro128p_uniform_float64(st, 2) == oracle.fill(h[2:3], "uniform", np.float64, 1)[0, 0]
+    assert math.isfinite(xoroshiro128p_normal_float32(st, 0))
+    assert math.isfinite(xoroshiro128p_normal_float64(st, 0))
+    assert st.copy_to_host()[1].tobytes() == host[1].tobytes()
+    with pytest.raises(IndexError):
+        xoroshiro128p_uniform_float32(st, 3)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_uniform_moments(dtype):
+    # test_random.py:82-97: 2 blocks x 32 threads, 32 draws each
+    st = create_xoroshiro128p_states(64, seed=1)
+    out = xoroshiro128p_fill(st, "uniform", count=32, dtype=dtype).copy_to_host().ravel()
+    assert abs(out.min() - 0.0) < 1e-3 and abs(out.max() - 1.0) < 1e-3
+    assert abs(out.mean() - 0.5) < 1.5e-2
+    assert abs(out.std() - (1.0 / (2 * math.sqrt(3)))) < 6e-3
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_normal_moments(dtype):
+    # test_random.py:99-113
+    st = create_xoroshiro128p_states(64, seed=1)
+    out = xoroshiro128p_fill(st, "normal", count=32, dtype=dtype).copy_to_host().ravel()
+    assert abs(out.mean() - 0.0) < 4e-2 and abs(out.std() - 1.0) < 4e-2
+    big = xoroshiro128p_fill(create_xoroshiro128p_states(1 << 14, seed=1), "normal", count=64, dtype=dtype).copy_to_host()
+    assert abs(big.mean()) < 4e-3 and abs(big.std() - 1.0) < 2e-3
+
+
+def test_checkpoint_resume():
+    # the states array is the resumable object: saving and reloading it continues the stream
+    st = create_xoroshiro128p_states(100, 5)
+    a = xoroshiro128p_fill(st, "uniform", count=10, dtype=np.float32).copy_to_host()
+    saved = st.copy_to_host()
+    b = xoroshiro128p_fill(st, "uniform", count=10, dtype=np.float32).copy_to_host()
+    st2 = cuda.to_device(saved)
+    b2 = xoroshiro128p_fill(st2, "uniform", count=10, dtype=np.float32).copy_to_host()
+    assert b.tobytes() == b2.tobytes() and a.tobytes() != b.tobytes()

@@ -1,0 +1,146 @@
+"""Multi-rank host logic on CPU: two `gloo` ranks exercise the partition
+bounds, the one-collective combine of reduce partials and the RNG / cast
+sharding rules.  The per-shard arithmetic is done by the CPU oracle here (the
+CUDA kernels are checked against the same oracle in the gpu tests)."""
+import os
+import socket
+import sys
+import traceback
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn_name, errors):
+    try:
+        sys.path.insert(0, ROOT)
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        globals()[fn_name](rank, world)
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        errors.put((rank, traceback.format_exc()))
+
+
+def _run(fn_name, world=2):
+    ctx = mp.get_context("spawn")
+    errors = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, errors)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        if p.is_alive():
+            p.kill()
+            pytest.fail("rank did not finish")
+    if not errors.empty():
+        rank, tb = errors.get()
+        pytest.fail(f"rank {rank} failed:\n{tb}")
+    assert all(p.exitcode == 0 for p in procs)
+
+
+# ---- bodies run inside each rank ------------------------------------------------
+def _body_reduce(rank, world):
+    import oracle
+    from numba_cuda_b200 import _lib, sharded
+    cases = [("max", _lib.MAX, np.int32), ("add", _lib.ADD, np.float64), ("add", _lib.ADD, np.int16),
+             ("min", _lib.MIN, np.uint64), ("mul", _lib.MUL, np.float32), ("xor", _lib.XOR, np.uint32),
+             ("and", _lib.AND, np.int8), ("or", _lib.OR, np.uint16), ("max", _lib.MAX, np.uint64)]
+    for name, op, dt in cases:
+        rng = np.random.default_rng(1)
+        n = 10007
+        if np.dtype(dt).kind == "f":
+            x = (rng.random(n) + 0.5).astype(dt) if name == "mul" else rng.standard_normal(n).astype(dt)
+            if name == "mul":
+                x = x[:64]
+                n = 64
+        else:
+            info = np.iinfo(dt)
+            x = rng.integers(info.min, info.max, size=n, dtype=dt, endpoint=True)
+        lo, hi = sharded.shard_bounds(n, world, rank)
+        ident = sharded.op_identity(op, dt)
+        partial = oracle.fold(x[lo:hi], name, ident)       # stands in for the device kernel
+        buf = torch.from_numpy(np.array([partial], dtype=dt).view(np.uint8).copy())
+        sharded.combine_partials(buf, op, dt)
+        init = np.dtype(dt).type(3)
+        got = sharded.host_fold(op, buf.numpy().view(dt), init)
+        want = oracle.fold(x, name, init)
+        if np.dtype(dt).kind == "f":
+            assert abs(got - want) <= 1e-5 * abs(want) + 1e-12, (name, dt, got, want)
+        else:
+            assert got == want, (name, dt, got, want)
+
+
+def _body_rng(rank, world):
+    import oracle
+    from numba_cuda_b200 import sharded
+    n, seed, start = 1000, 42, 5
+    whole = oracle.init_states(n, seed, start)
+    lo, hi = sharded.shard_bounds(n, world, rank)
+    mine = oracle.init_states(hi - lo, seed, start + lo)    # the rule create_sharded_* applies
+    assert mine.tobytes() == whole[lo:hi].tobytes()
+    # gather the shards and compare the concatenation with the single-rank array
+    pieces = [None] * world
+    dist.all_gather_object(pieces, (lo, hi, mine.tobytes()))
+    cat = b"".join(p[2] for p in sorted(pieces))
+    assert cat == whole.tobytes()
+    u_whole = oracle.fill(whole.copy(), "uniform", np.float32, 8)
+    u_mine = oracle.fill(mine, "uniform", np.float32, 8)
+    assert u_mine.tobytes() == u_whole[lo:hi].tobytes()
+
+
+def _body_cast(rank, world):
+    import oracle
+    from numba_cuda_b200 import sharded
+    n = 100003
+    x = (4 * np.random.default_rng(3).standard_normal(n)).astype(np.float32)
+    lo, hi = sharded.shard_bounds(n, world, rank, align=16)
+    assert lo % 16 == 0
+    whole = oracle.cast(x, oracle.F32, oracle.E4M3)
+    assert oracle.cast(x[lo:hi], oracle.F32, oracle.E4M3).tobytes() == whole[lo:hi].tobytes()
+    sizes = [None] * world
+    dist.all_gather_object(sizes, hi - lo)
+    assert sum(sizes) == n
+
+
+def _body_world_mismatch(rank, world):
+    from numba_cuda_b200 import sharded
+    with pytest.raises(ValueError):
+        sharded.shard_bounds(10, world, world)
+
+
+# ---- tests ------------------------------------------------------------------------
+def test_combine_partials_two_ranks():
+    _run("_body_reduce")
+
+
+def test_rng_shards_concatenate_to_single_stream():
+    _run("_body_rng")
+
+
+def test_cast_shards_are_aligned_and_complete():
+    _run("_body_cast")
+
+
+def test_bad_rank_is_rejected():
+    _run("_body_world_mismatch")
+
+
+def test_single_process_is_world_of_one():
+    from numba_cuda_b200 import _lib, sharded
+    buf = torch.from_numpy(np.array([5], dtype=np.int32).view(np.uint8).copy())
+    assert sharded.combine_partials(buf, _lib.MAX, np.int32) is buf
