@@ -114,6 +114,9 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
                      int tiles_x, long long tiles) {
     constexpr int TILE_BYTES = R * 128;
     constexpr int TCOLS = 128 / ES;
+    // tensor-map elements per item along the contiguous direction (32-bit words
+    // for items wider than 4 bytes); x coordinates are counted in those elements
+    constexpr int WORDS = ES > 4 ? ES / 4 : 1;
     extern __shared__ unsigned char smem_raw[];
     // the 128-byte swizzle pattern is a function of address bits 7..9
     unsigned char *base = reinterpret_cast<unsigned char *>(
@@ -136,7 +139,7 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
             const long long id = first + s * step;
             if (id < tiles) {
                 mbar_expect_tx(&full[s], TILE_BYTES);
-                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(id % tiles_x) * TCOLS,
+                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(id % tiles_x) * (TCOLS * WORDS),
                             static_cast<int>(id / tiles_x) * R, &full[s]);
             }
         }
@@ -159,13 +162,13 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
 
         if (threadIdx.x == 0) {
             // output coordinates: x runs along input rows, y along input columns
-            tma_store_2d(&out_map, static_cast<int>(id / tiles_x) * R, static_cast<int>(id % tiles_x) * TCOLS,
-                         B + b * TILE_BYTES);
+            tma_store_2d(&out_map, static_cast<int>(id / tiles_x) * (R * WORDS),
+                         static_cast<int>(id % tiles_x) * TCOLS, B + b * TILE_BYTES);
             tma_commit();
             const long long next = id + NSTAGE * step;
             if (next < tiles) {
                 mbar_expect_tx(&full[s], TILE_BYTES);
-                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(next % tiles_x) * TCOLS,
+                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(next % tiles_x) * (TCOLS * WORDS),
                             static_cast<int>(next / tiles_x) * R, &full[s]);
             }
         }

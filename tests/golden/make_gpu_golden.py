@@ -55,7 +55,7 @@ def main():
     out_path = sys.argv[1] if len(sys.argv) > 1 else "gpu_normals_reference.npz"
     info = {"device": cuda.get_current_device().name.decode() if isinstance(cuda.get_current_device().name, bytes)
             else str(cuda.get_current_device().name), "cc": list(cuda.get_current_device().compute_capability)}
-    n = 1024
+    n = 256
     res = {}
     st = create_xoroshiro128p_states(n, seed=42)
     res["states0"] = np.stack([st.copy_to_host()["s0"], st.copy_to_host()["s1"]], axis=1)

@@ -51,9 +51,15 @@ def test_decode_all_codes(gold, fmt):
     nan = np.isnan(want)
     assert (np.isnan(got) == nan).all()
     assert got[~nan].tobytes() == want[~nan].tobytes()
-    # encode(decode(code)) is the identity on every non-NaN code
+    # encode(decode(code)) is the identity on every finite code; E5M2 infinities
+    # survive without saturation and clamp to the largest finite code with it
+    fin = np.isfinite(want)
     back = cast(got, "f32", fmt, saturate=1).copy_to_host()
-    assert (back[~nan] == codes[~nan]).all()
+    assert (back[fin] == codes[fin]).all()
+    back0 = cast(got, "f32", fmt, saturate=0).copy_to_host()
+    assert (back0[~nan] == codes[~nan]).all()
+    inf = np.isinf(want)
+    assert ((back[inf] & 0x7F) == 0x7B).all()
 
 
 def test_bf16_encode_matches_reference_headers(gold):

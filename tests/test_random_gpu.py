@@ -134,9 +134,10 @@ def ulp_diff(a, b):
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
 def test_normal_draws_vs_cpu_restatement(dtype, gold):
-    # The GPU uses libdevice's logf/cos/cosf, the CPU oracle the host libm, so this
-    # is a tolerance check (a few ulp of the result, looser where cos() is near 0);
-    # the state stream itself must be bit-exact.
+    # The GPU uses libdevice's logf/cosf/cos, the CPU oracle the host libm.  Both
+    # take the log in float32, so even the float64 normals agree only to a few
+    # float32 ulps; bit parity of normals is pinned by the GPU fixture below.
+    # The state stream itself must be bit-exact.
     n, count = 257, 40
     st_host = oracle.init_states(n, 42, 0)
     st_dev = create_xoroshiro128p_states(n, 42, 0)
@@ -145,23 +146,39 @@ def test_normal_draws_vs_cpu_restatement(dtype, gold):
     assert st_dev.copy_to_host().tobytes() == st_host.tobytes()
     finite = np.isfinite(want)
     assert (np.isfinite(got) == finite).all()
-    eps = np.finfo(dtype).eps
-    err = np.abs(got[finite] - want[finite])
-    # error budget: rounding of sqrt/log/cos plus the argument error of cos(2*pi*u2)
-    assert (err <= 64 * eps * np.maximum(np.abs(want[finite]), 1.0)).all(), err.max()
+    eps32 = float(np.finfo(np.float32).eps)
+    err = np.abs(got[finite].astype(np.float64) - want[finite].astype(np.float64))
+    assert (err <= 16 * eps32 * np.maximum(np.abs(want[finite]), 1.0)).all(), err.max()
     frac_exact = (ulp_diff(got[finite], want[finite]) == 0).mean()
     print(f"normal {np.dtype(dtype).name}: {frac_exact:.4f} of draws bit-identical to host libm")
     key = "normal_f32_hostlibm" if dtype == np.float32 else "normal_f64_hostlibm"
     st = create_xoroshiro128p_states(4, 42, 0)
     g = xoroshiro128p_fill(st, "normal", count=32, dtype=dtype).copy_to_host()
-    np.testing.assert_allclose(g, gold[key], rtol=64 * eps, atol=64 * eps)
+    np.testing.assert_allclose(g, gold[key], rtol=16 * eps32, atol=16 * eps32)
+
+
+def test_normals_bit_exact_vs_gpu_reference(golden_dir):
+    """Normals produced on a B200 by the reference's kernel source (fixture from
+    tests/golden/make_gpu_golden.py): same libdevice, so every bit must agree."""
+    g = np.load(os.path.join(golden_dir, "gpu_normals_reference.npz"))
+    n = g["states0"].shape[0]
+    st = create_xoroshiro128p_states(n, 42, 0)
+    assert (pairs(st.copy_to_host()) == g["states0"]).all()
+    u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+    assert u.copy_to_host().tobytes() == g["c4_u"].tobytes()
+    assert z.copy_to_host().tobytes() == g["c4_z"].tobytes()
+    assert (pairs(st.copy_to_host()) == g["c4_end"]).all()
+    st = create_xoroshiro128p_states(n, 42, 0)
+    assert xoroshiro128p_fill(st, "normal", count=32, dtype=np.float32).copy_to_host().tobytes() == g["normal_f32"].tobytes()
+    st = create_xoroshiro128p_states(n, 42, 0)
+    assert xoroshiro128p_fill(st, "normal", count=32, dtype=np.float64).copy_to_host().tobytes() == g["normal_f64"].tobytes()
 
 
 def test_fused_config4_sequence_small(gold):
     st = create_xoroshiro128p_states(8, 42, 0)
     u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
     assert u.copy_to_host().tobytes() == gold["c4_u"].tobytes()
-    np.testing.assert_allclose(z.copy_to_host(), gold["c4_z_hostlibm"], rtol=1e-13, atol=1e-13)
+    np.testing.assert_allclose(z.copy_to_host(), gold["c4_z_hostlibm"], rtol=2e-6, atol=2e-6)
     assert (pairs(st.copy_to_host()) == gold["c4_end"]).all()
     # fused launch == two launches
     st2 = create_xoroshiro128p_states(8, 42, 0)
