@@ -82,6 +82,29 @@ B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* The same reduction for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.  Meant for hosts whose device memory belongs to
+ * someone else at the time of the call (a numba-cuda process running under an
+ * external memory-manager plugin whose pool is already handed out), for plain C
+ * callers that hold only an input and an output buffer, and for loops that
+ * cannot afford the device-wide synchronisation an allocation or free may cause.
+ * The ticket and the block partials live in an array that is compiled into the
+ * library (33,024 bytes, held by every GPU that loads the library until the
+ * process exits); the call itself performs no cudaMalloc / cudaFree and calls no
+ * allocating routine.
+ *   - n may be at most b2k_reduce_noalloc_max_elements() (2^32); larger inputs
+ *     are refused with B2K_ERR_TOO_LARGE -- use b2k_reduce with your own scratch.
+ *   - The first call on each device looks up the array's device address (that
+ *     device must be current); make that first call before starting any stream
+ *     capture.
+ *   - All calls on a device share the one array: two calls that may run on the
+ *     GPU at the same time (different streams, different threads) race and give
+ *     wrong results.  Calls ordered on one stream are fine; each call clears the
+ *     part of the array that must start at zero. */
+B2K_API int64_t b2k_reduce_noalloc_max_elements(void);
+B2K_API int b2k_reduce_noalloc(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+                               void *out_dev, void *stream);
+
 /* ---- transpose ----------------------------------------------------------
  * Replaces the per-call JIT-compiled tile kernel of
  * numba/cuda/kernels/transpose.py:42-63: out[j, i] = in[i, j] for items of

@@ -28,6 +28,8 @@ SIGNATURES = {
     "b2k_launch_count": (_i64, []),
     "b2k_reduce_scratch_bytes": (_i64, []),
     "b2k_reduce": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "b2k_reduce_noalloc_max_elements": (_i64, []),
+    "b2k_reduce_noalloc": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "b2k_transpose2d": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "b2k_xoroshiro128p_tables_bytes": (_i64, []),
     "b2k_xoroshiro128p_build_tables": (_i32, [_vp, _i64, _vp]),

@@ -14,6 +14,7 @@
 // The fold order depends only on (n, grid size), so floating-point results are
 // reproducible run to run.  HBM roofline: sizeof(T) bytes read per element.
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 
 #include "b2k_internal.cuh"
@@ -289,6 +290,73 @@ int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init
     case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
     default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
     }
+}
+
+}  // extern "C"
+
+// ---- entry point that allocates nothing ------------------------------------------
+//
+// Some hosts may not allocate device memory at the point where they need a
+// reduction: a numba-cuda process whose device memory is owned by an external
+// memory-manager plugin (every byte has to come from that pool, and the pool may
+// already be fully handed out), a C caller that holds nothing but its input and
+// output buffers, or a latency-critical loop that cannot take the device-wide
+// synchronisation an allocation or a free can imply.  For them the ticket and
+// the block partials live in the fixed array below instead of caller scratch.
+//
+// In host code the array's name stands for the symbol, not for an address the
+// GPU understands; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[kTicketBytes + 8 * kMaxGrid];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void *g_static_address[kMaxDevices];  // device address of the array, per device ordinal
+
+int static_scratch_of_current_device(void **address) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_reduce_noalloc: cudaGetDevice");
+    if (device < 0 || device >= kMaxDevices)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_noalloc: device ordinal %d not supported", device);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_address[device] == nullptr) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_reduce_static_scratch);
+        if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_reduce_noalloc: cudaGetSymbolAddress");
+        if (p == nullptr) return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_noalloc: no device address for the scratch array");
+        g_static_address[device] = p;
+    }
+    *address = g_static_address[device];
+    return B2K_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b2k_reduce_noalloc_max_elements(void) { return int64_t(1) << 32; }
+
+int b2k_reduce_noalloc(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+                       void *out_dev, void *stream) {
+    if (n > b2k_reduce_noalloc_max_elements())
+        return b2k::fail(B2K_ERR_TOO_LARGE,
+                         "b2k_reduce_noalloc: %lld elements exceed the limit of %lld for the built-in scratch; "
+                         "use b2k_reduce with caller-provided scratch",
+                         (long long)n, (long long)b2k_reduce_noalloc_max_elements());
+    if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_noalloc: negative length %lld", (long long)n);
+    void *scratch = nullptr;
+    const int rc = static_scratch_of_current_device(&scratch);
+    if (rc != B2K_OK) return rc;
+    // The array keeps whatever the previous call left.  Only the ticket word has
+    // to start at zero (the kernel returns it to zero when it completes, but a
+    // launch that failed half-way would not); partial slots are written before
+    // they are read.
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, kTicketBytes, b2k::as_stream(stream));
+    if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_reduce_noalloc: clearing the ticket");
+    return b2k_reduce(op, dtype, x_dev, n, init_host, out_dev, scratch, b2k_reduce_scratch_bytes(), stream);
 }
 
 }  // extern "C"
