@@ -49,15 +49,18 @@ int sm_count() {
 }
 
 int env_int(const char *name, int fallback) {
+    // The environment is read once per name; callers may pass different
+    // fallbacks for the same name, so only the parsed variable is cached.
     static std::mutex mu;
-    static std::unordered_map<std::string, int> seen;
+    static std::unordered_map<std::string, std::pair<bool, int>> seen;
     std::lock_guard<std::mutex> lock(mu);
     auto it = seen.find(name);
-    if (it != seen.end()) return it->second;
-    const char *v = getenv(name);
-    int val = (v && *v) ? atoi(v) : fallback;
-    seen.emplace(name, val);
-    return val;
+    if (it == seen.end()) {
+        const char *v = getenv(name);
+        const bool set = v && *v;
+        it = seen.emplace(name, std::make_pair(set, set ? atoi(v) : 0)).first;
+    }
+    return it->second.first ? it->second.second : fallback;
 }
 
 }  // namespace b2k

@@ -202,6 +202,85 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
 }
 
+// 256-bit variant: every CTA step folds one contiguous chunk of THREADS*UNROLL
+// 32-byte vectors (sm_100 has 256-bit global loads), so the CTAs in flight sweep
+// one contiguous window of the array.  Same tail handling and same single-pass
+// combine as above.
+struct alignas(32) Bits256 { uint4 lo, hi; };
+
+__device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
+    Bits256 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.lo.x), "=r"(r.lo.y), "=r"(r.lo.z), "=r"(r.lo.w), "=r"(r.hi.x), "=r"(r.hi.y),
+                   "=r"(r.hi.z), "=r"(r.hi.w)
+                 : "l"(p));
+    return r;
+}
+
+template <typename T, typename Op, int THREADS, int UNROLL>
+__global__ void __launch_bounds__(THREADS)
+reduce_wide_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
+                   T *partials, unsigned int *ticket) {
+    constexpr int VEC = 32 / sizeof(T);
+    __shared__ T slots[THREADS / 32];
+    __shared__ bool is_last;
+
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
+    int64_t head = static_cast<int64_t>(((32u - (addr & 31u)) & 31u) / sizeof(T));
+    if (head > n) head = n;
+    const Bits256 *xv = reinterpret_cast<const Bits256 *>(x + head);
+    const int64_t nvec = (n - head) / VEC;
+    const int64_t tail_begin = head + nvec * VEC;
+    constexpr int64_t CHUNK = static_cast<int64_t>(THREADS) * UNROLL;
+    const int64_t nchunks = nvec / CHUNK;
+
+    T acc[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) acc[u] = Op::template identity<T>();
+
+    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+        const Bits256 *p = xv + c * CHUNK + threadIdx.x;
+        Bits256 raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(p + u * THREADS);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            acc[u] = fold_vector<T, Op>(acc[u], raw[u].lo);
+            acc[u] = fold_vector<T, Op>(acc[u], raw[u].hi);
+        }
+    }
+    // vectors past the last whole chunk, spread over the grid
+    for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
+         v += static_cast<int64_t>(gridDim.x) * THREADS) {
+        const Bits256 raw = load_stream32(xv + v);
+        acc[0] = fold_vector<T, Op>(acc[0], raw.lo);
+        acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
+    }
+    if (blockIdx.x == 0) {  // fewer than 32 scalars on each side
+        if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);
+        const int64_t t = tail_begin + threadIdx.x;
+        if (t < n) acc[0] = Op::template apply<T>(acc[0], x[t]);
+    }
+#pragma unroll
+    for (int u = 1; u < UNROLL; ++u) acc[0] = Op::template apply<T>(acc[0], acc[u]);
+
+    T total = block_fold<T, Op, THREADS>(acc[0], slots);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = total;
+        __threadfence();
+        const unsigned int t = atomicInc(ticket, gridDim.x - 1);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    T mine = Op::template identity<T>();
+    for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
+        mine = Op::template apply<T>(mine, __ldcg(partials + i));
+    total = block_fold<T, Op, THREADS>(mine, slots);
+    if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
+}
+
 template <typename T, typename Op>
 int launch(const void *x, int64_t n, const void *init_host, void *out, void *scratch,
            cudaStream_t stream) {
@@ -218,6 +297,14 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
     if (grid > max_grid) grid = max_grid;
     auto *ticket = static_cast<unsigned int *>(scratch);
     auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
+    if (b2k::env_int("B2K_REDUCE_WIDE", 1) != 0) {
+        // one CTA step covers kThreads*kUnroll 32-byte vectors
+        int64_t wgrid = (n * static_cast<int64_t>(sizeof(T)) / 32 + kThreads * kUnroll - 1) / (kThreads * kUnroll);
+        if (wgrid < 1) wgrid = 1;
+        if (wgrid > max_grid) wgrid = max_grid;
+        reduce_wide_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(wgrid), kThreads, 0, stream>>>(
+            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
+    } else
     reduce_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
         static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
     b2k::note_launch();

@@ -108,10 +108,29 @@ __device__ __forceinline__ void transpose_tile(const unsigned char *A, unsigned 
     }
 }
 
+// Tile order.  Tiles are numbered panel by panel: a panel is `panel_w` tiles wide
+// (along input columns) and spans all tile rows; inside a panel the tile column
+// varies fastest.  CTAs that run at the same time therefore cover a 2-D patch of
+// the matrix, which keeps both the 128-byte-wide reads and the R-item-wide
+// writes of neighbouring CTAs next to each other in memory instead of lining
+// one of the two sides up at a power-of-two pitch.
+struct TileOrder {
+    int tiles_x, tiles_y, panel_w;
+    __device__ __forceinline__ void coords(long long id, int &tx, int &ty) const {
+        const long long per_panel = static_cast<long long>(panel_w) * tiles_y;
+        const int panel = static_cast<int>(id / per_panel);
+        const int within = static_cast<int>(id - panel * per_panel);
+        const int tx0 = panel * panel_w;
+        const int w = min(panel_w, tiles_x - tx0);
+        ty = within / w;
+        tx = tx0 + within - ty * w;
+    }
+};
+
 template <int ES, int R, int NSTAGE>
 __global__ void __launch_bounds__(kThreads)
 transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
-                     int tiles_x, long long tiles) {
+                     const TileOrder order, long long tiles) {
     constexpr int TILE_BYTES = R * 128;
     constexpr int TCOLS = 128 / ES;
     // tensor-map elements per item along the contiguous direction (32-bit words
@@ -138,9 +157,10 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
         for (int s = 0; s < NSTAGE; ++s) {
             const long long id = first + s * step;
             if (id < tiles) {
+                int tx, ty;
+                order.coords(id, tx, ty);
                 mbar_expect_tx(&full[s], TILE_BYTES);
-                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(id % tiles_x) * (TCOLS * WORDS),
-                            static_cast<int>(id / tiles_x) * R, &full[s]);
+                tma_load_2d(A + s * TILE_BYTES, &in_map, tx * (TCOLS * WORDS), ty * R, &full[s]);
             }
         }
     }
@@ -162,14 +182,15 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
 
         if (threadIdx.x == 0) {
             // output coordinates: x runs along input rows, y along input columns
-            tma_store_2d(&out_map, static_cast<int>(id / tiles_x) * (R * WORDS),
-                         static_cast<int>(id % tiles_x) * TCOLS, B + b * TILE_BYTES);
+            int tx, ty;
+            order.coords(id, tx, ty);
+            tma_store_2d(&out_map, ty * (R * WORDS), tx * TCOLS, B + b * TILE_BYTES);
             tma_commit();
             const long long next = id + NSTAGE * step;
             if (next < tiles) {
+                order.coords(next, tx, ty);
                 mbar_expect_tx(&full[s], TILE_BYTES);
-                tma_load_2d(A + s * TILE_BYTES, &in_map, static_cast<int>(next % tiles_x) * (TCOLS * WORDS),
-                            static_cast<int>(next / tiles_x) * R, &full[s]);
+                tma_load_2d(A + s * TILE_BYTES, &in_map, tx * (TCOLS * WORDS), ty * R, &full[s]);
             }
         }
     }
@@ -245,10 +266,14 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
         attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     });
     if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
-    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 200 * 1024 / SMEM);
+    // two resident CTAs per SM measured best (more CTAs only add DRAM page conflicts)
+    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 2);
     int64_t grid = static_cast<int64_t>(b2k::sm_count()) * (per_sm < 1 ? 1 : per_sm);
     if (grid > tiles) grid = tiles;
-    kernel<<<static_cast<unsigned>(grid), kThreads, SMEM, stream>>>(in_map, out_map, static_cast<int>(tiles_x),
+    int panel_w = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
+    if (panel_w < 1 || panel_w > tiles_x) panel_w = static_cast<int>(tiles_x);
+    const TileOrder order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), panel_w};
+    kernel<<<static_cast<unsigned>(grid), kThreads, SMEM, stream>>>(in_map, out_map, order,
                                                                     static_cast<long long>(tiles));
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_transpose2d (tma) launch");
@@ -274,10 +299,15 @@ int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t
         return B2K_ERR_UNSUPPORTED;
     // small arrays: the general tile kernel has less fixed cost
     if (rows * cols * itemsize < b2k::env_int("B2K_TRANSPOSE_TMA_MIN_BYTES", 1 << 16)) return B2K_ERR_UNSUPPORTED;
+    const int tall = b2k::env_int("B2K_TRANSPOSE_ROWS", 0);  // development knob: tile height
     switch (itemsize) {
     case 1: return launch<1, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
-    case 2: return launch<2, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
-    case 4: return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 2:
+        if (tall == 64) return launch<2, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+        return launch<2, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 4:
+        if (tall == 128) return launch<4, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+        return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 8: return launch<8, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     default: return launch<16, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     }

@@ -275,33 +275,72 @@ __device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
 }
 
 // One segment for the 32 generators [base, base+32) of this warp.
+//
+// Every lane draws CHUNK values into its own padded row of the warp's staging
+// tile (row pitch of an odd number of banks: conflict-free), then the warp
+// writes the tile out row-wise.  Full tiles whose output rows are 16-byte
+// aligned leave as 128-bit stores, four rows of 128 bytes per instruction;
+// ragged tiles (last generators, last columns, odd counts) leave one row of
+// scalars per instruction.
 template <typename T, int DRAW>
 __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
                                              int64_t n, const Segment &seg, void *stage) {
     constexpr int CHUNK = sizeof(T) == 4 ? 32 : 16;
     constexpr int PITCH = sizeof(T) == 4 ? kPitch32 : kPitch64;
     constexpr int ROWS_PER_STORE = 32 / CHUNK;
+    constexpr int PER_LANE = 16 / sizeof(T);        // items in one 128-bit store
     T *buf = static_cast<T *>(stage);
     T *out = static_cast<T *>(seg.out);
     const int lane = threadIdx.x & 31;
+    const bool rows_full = base + 32 <= n;
+    const bool vector_ok = rows_full && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0) &&
+                           ((seg.count * sizeof(T)) % 16 == 0);
     for (int64_t c0 = 0; c0 < seg.count; c0 += CHUNK) {
         const int m = (seg.count - c0 < CHUNK) ? static_cast<int>(seg.count - c0) : CHUNK;
         if (live) {
+            T *row = buf + lane * PITCH;
             if (m == CHUNK) {
-#pragma unroll 4
-                for (int i = 0; i < CHUNK; ++i) buf[lane * PITCH + i] = draw_one<T, DRAW>(s0, s1);
+#pragma unroll 8
+                for (int i = 0; i < CHUNK; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
             } else {
-                for (int i = 0; i < m; ++i) buf[lane * PITCH + i] = draw_one<T, DRAW>(s0, s1);
+                for (int i = 0; i < m; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
             }
         }
         __syncwarp();
-        const int col = lane % CHUNK;
-        const int sub = lane / CHUNK;
-#pragma unroll 4
-        for (int r = 0; r < 32; r += ROWS_PER_STORE) {
-            const int row = r + sub;
-            const int64_t g = base + row;
-            if (g < n && col < m) out[g * seg.count + c0 + col] = buf[row * PITCH + col];
+        if (vector_ok && m == CHUNK) {
+            // lane -> (row within a group of four, 16-byte piece of that row)
+            const int sub = lane >> 3, piece = lane & 7;
+            const T *src = buf + sub * PITCH + piece * PER_LANE;
+            T *dst = out + (base + sub) * seg.count + c0 + piece * PER_LANE;
+            const int64_t dst_step = 4 * seg.count;
+#pragma unroll
+            for (int r = 0; r < 32; r += 4) {
+                if constexpr (sizeof(T) == 4) {
+                    float4 v;
+                    v.x = src[0]; v.y = src[1]; v.z = src[2]; v.w = src[3];
+                    __stcs(reinterpret_cast<float4 *>(dst), v);
+                } else {
+                    double2 v;
+                    v.x = src[0]; v.y = src[1];
+                    __stcs(reinterpret_cast<double2 *>(dst), v);
+                }
+                src += 4 * PITCH;
+                dst += dst_step;
+            }
+        } else {
+            const int col = lane % CHUNK;
+            const int sub = lane / CHUNK;
+            if (col < m) {
+                const T *src = buf + sub * PITCH + col;
+                T *dst = out + (base + sub) * seg.count + c0 + col;
+                const int64_t dst_step = static_cast<int64_t>(ROWS_PER_STORE) * seg.count;
+                const int64_t rows_here = n - base - sub;  // rows this lane may still write
+                for (int r = 0; r < 32 && r < rows_here; r += ROWS_PER_STORE) {
+                    *dst = *src;
+                    src += ROWS_PER_STORE * PITCH;
+                    dst += dst_step;
+                }
+            }
         }
         __syncwarp();
     }
