@@ -98,12 +98,9 @@ __device__ __forceinline__ float bf16bits_to_f32(uint32_t h) {
 // Each converter names its wide and narrow vector types and converts one item
 // of four consecutive elements; `one` converts a single element for ragged ends.
 
-// kUnroll / kCtasPerSm: launch shape measured best for each direction (the
-// write-heavy directions want more, smaller steps in flight).
 template <bool E5M2, bool SAT>
 struct F32ToFp8 {
     using In = float4; using Out = uint32_t; using InS = float; using OutS = uint8_t;
-    static constexpr int kUnroll = 4, kCtasPerSm = 4;
     __device__ static Out four(const In &v) {
         if constexpr (SAT) {
             if constexpr (E5M2) return pack2_e5m2_sat(v.y, v.x) | (pack2_e5m2_sat(v.w, v.z) << 16);
@@ -125,7 +122,6 @@ struct F32ToFp8 {
 template <bool E5M2>
 struct Fp8ToF32 {
     using In = uint32_t; using Out = float4; using InS = uint8_t; using OutS = float;
-    static constexpr int kUnroll = 4, kCtasPerSm = 16;
     __device__ static Out four(const In &codes) {
         const uint32_t lo = E5M2 ? fp8x2_to_f16x2_e5m2(codes & 0xFFFFu) : fp8x2_to_f16x2_e4m3(codes & 0xFFFFu);
         const uint32_t hi = E5M2 ? fp8x2_to_f16x2_e5m2(codes >> 16) : fp8x2_to_f16x2_e4m3(codes >> 16);
@@ -140,7 +136,6 @@ struct Fp8ToF32 {
 
 struct F32ToBf16 {
     using In = float4; using Out = uint2; using InS = float; using OutS = uint16_t;
-    static constexpr int kUnroll = 8, kCtasPerSm = 16;
     __device__ static Out four(const In &v) {
         return make_uint2(pack2_bf16(v.y, v.x), pack2_bf16(v.w, v.z));
     }
@@ -149,7 +144,6 @@ struct F32ToBf16 {
 
 struct Bf16ToF32 {
     using In = uint2; using Out = float4; using InS = uint16_t; using OutS = float;
-    static constexpr int kUnroll = 8, kCtasPerSm = 16;
     __device__ static Out four(const In &v) {
         return make_float4(bf16bits_to_f32(v.x & 0xFFFFu), bf16bits_to_f32(v.x >> 16),
                            bf16bits_to_f32(v.y & 0xFFFFu), bf16bits_to_f32(v.y >> 16));
@@ -168,7 +162,9 @@ __device__ __forceinline__ void store_stream(V *p, const V &v) {
     __stcs(p, v);      // written once, not re-read by this kernel
 }
 
-template <typename C, int UNROLL, bool STREAM_STORE>
+// 128-bit path for arrays that are 16- but not 32-byte aligned: four elements per
+// thread step, grid-stride.
+template <typename C, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 cast_items_kernel(const typename C::In *__restrict__ in, typename C::Out *__restrict__ out,
                   int64_t items, int64_t n) {
@@ -180,10 +176,7 @@ cast_items_kernel(const typename C::In *__restrict__ in, typename C::Out *__rest
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream(in + i + u * stride);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if constexpr (STREAM_STORE) store_stream(out + i + u * stride, C::four(raw[u]));
-            else out[i + u * stride] = C::four(raw[u]);
-        }
+        for (int u = 0; u < UNROLL; ++u) store_stream(out + i + u * stride, C::four(raw[u]));
     }
     for (; i < items; i += stride) store_stream(out + i, C::four(load_stream(in + i)));
     // ragged end: fewer than four elements
@@ -199,8 +192,8 @@ cast_items_kernel(const typename C::In *__restrict__ in, typename C::Out *__rest
 // ---- 256-bit path -------------------------------------------------------------
 // Eight elements per thread step.  The wide side moves as one 256-bit access per
 // lane (sm_100 has 256-bit global loads and stores), the narrow side as 64 or 128
-// bits.  Every CTA owns one contiguous chunk of kThreads*UNROLL items, so the
-// CTAs in flight cover one contiguous window of each array.
+// bits.  Every CTA owns one contiguous run of kThreads items, so the CTAs in
+// flight cover one contiguous window of each array.
 struct alignas(32) Bits256 { uint32_t w[8]; };
 
 template <typename V> struct Mover;
@@ -247,25 +240,15 @@ struct Eight {
     }
 };
 
-template <typename C, int UNROLL>
+template <typename C>
 __global__ void __launch_bounds__(kThreads)
 cast_wide_kernel(const typename Eight<C>::In *__restrict__ in, typename Eight<C>::Out *__restrict__ out,
                  int64_t items /* of eight elements */, int64_t n) {
     using E = Eight<C>;
-    const int64_t base = static_cast<int64_t>(blockIdx.x) * (kThreads * UNROLL) + threadIdx.x;
-    typename E::In raw[UNROLL];
-    if (base + (UNROLL - 1) * kThreads < items) {
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) raw[u] = Mover<typename E::In>::load(in + base + u * kThreads);
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) Mover<typename E::Out>::store(out + base + u * kThreads, E::convert(raw[u]));
-    } else {
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int64_t i = base + u * kThreads;
-            if (i < items) Mover<typename E::Out>::store(out + i, E::convert(Mover<typename E::In>::load(in + i)));
-        }
-    }
+    // one item per thread and one CTA per 256 items measured best: the hardware
+    // keeps enough CTAs in flight, and they sweep both arrays front to back
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    if (i < items) Mover<typename E::Out>::store(out + i, E::convert(Mover<typename E::In>::load(in + i)));
     // ragged end: fewer than eight elements, done by the last CTA
     if (blockIdx.x == gridDim.x - 1) {
         const int64_t t = items * 8 + threadIdx.x;
@@ -291,7 +274,7 @@ int launch(const void *in, void *out, int64_t n, cudaStream_t stream) {
     if (n == 0) return B2K_OK;
     if (!b2k::aligned_to<void>(in, sizeof(typename C::InS)) || !b2k::aligned_to<void>(out, sizeof(typename C::OutS)))
         return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_cast: pointers must be aligned to the element size");
-    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_CAST_CTAS_PER_SM", C::kCtasPerSm);
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * 8;
     const bool vector_ok = b2k::aligned_to<void>(in, sizeof(typename C::In)) &&
                            b2k::aligned_to<void>(out, sizeof(typename C::Out));
     const bool wide_ok = b2k::aligned_to<void>(in, sizeof(typename Eight<C>::In)) &&
@@ -299,39 +282,18 @@ int launch(const void *in, void *out, int64_t n, cudaStream_t stream) {
                          b2k::env_int("B2K_CAST_WIDE", 1) != 0;
     if (wide_ok) {
         const int64_t items = n / 8;
-        const int unroll = b2k::env_int("B2K_CAST_WIDE_UNROLL", 4);
-        const int64_t per_cta = static_cast<int64_t>(kThreads) * unroll;
-        int64_t grid = (items + per_cta - 1) / per_cta;
+        int64_t grid = (items + kThreads - 1) / kThreads;
         if (grid < 1) grid = 1;
         if (grid > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_cast: array too large");
-        auto *pin = static_cast<const typename Eight<C>::In *>(in);
-        auto *pout = static_cast<typename Eight<C>::Out *>(out);
-        const unsigned g = static_cast<unsigned>(grid);
-        if (unroll == 1) cast_wide_kernel<C, 1><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        else if (unroll == 2) cast_wide_kernel<C, 2><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        else if (unroll == 8) cast_wide_kernel<C, 8><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        else cast_wide_kernel<C, 4><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
+        cast_wide_kernel<C><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename Eight<C>::In *>(in), static_cast<typename Eight<C>::Out *>(out), items, n);
     } else if (vector_ok) {
         const int64_t items = n / 4;
-        int64_t grid;
-        const int unroll = b2k::env_int("B2K_CAST_UNROLL", C::kUnroll);
-        const bool stream_store = b2k::env_int("B2K_CAST_STREAM_STORE", 1) != 0;
-        grid = (items + kThreads * unroll - 1) / (kThreads * unroll);
+        int64_t grid = (items + kThreads * 4 - 1) / (kThreads * 4);
         if (grid < 1) grid = 1;
         if (grid > cap) grid = cap;
-        auto *pin = static_cast<const typename C::In *>(in);
-        auto *pout = static_cast<typename C::Out *>(out);
-        const unsigned g = static_cast<unsigned>(grid);
-        if (unroll == 8) {
-            if (stream_store) cast_items_kernel<C, 8, true><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-            else cast_items_kernel<C, 8, false><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        } else if (unroll == 2) {
-            if (stream_store) cast_items_kernel<C, 2, true><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-            else cast_items_kernel<C, 2, false><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        } else {
-            if (stream_store) cast_items_kernel<C, 4, true><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-            else cast_items_kernel<C, 4, false><<<g, kThreads, 0, stream>>>(pin, pout, items, n);
-        }
+        cast_items_kernel<C, 4><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename C::In *>(in), static_cast<typename C::Out *>(out), items, n);
     } else {
         int64_t grid = (n + kThreads - 1) / kThreads;
         if (grid > cap) grid = cap;

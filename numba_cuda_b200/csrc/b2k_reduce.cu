@@ -4,8 +4,9 @@
 // reduction.py:233-258: full blocks -> tail block -> fold of <=65 partials, with
 // only 64x128 threads and scalar loads) by one persistent-grid kernel:
 //
-//   * every thread walks the array with a grid stride of 16-byte vectors,
-//     UNROLL independent 128-bit loads in flight, one accumulator per slot;
+//   * every CTA step folds one contiguous chunk of 32-byte vectors (256-bit
+//     loads), UNROLL independent loads in flight per thread, one accumulator
+//     per slot; CTAs stride over chunks;
 //   * lanes combine with a shuffle butterfly, warps through shared memory;
 //   * each block publishes its partial, then takes a ticket (atomicInc that
 //     wraps to zero by itself); the block that draws the last ticket folds all
@@ -90,15 +91,6 @@ struct OpXor {
 };
 
 // ---- helpers -------------------------------------------------------------
-// Read-once data: non-coherent path, no L1 allocation.
-__device__ __forceinline__ uint4 load_stream16(const uint4 *p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
-    return r;
-}
-
 template <typename T, typename Op>
 __device__ __forceinline__ T fold_vector(T acc, const uint4 &raw) {
     constexpr int N = 16 / sizeof(T);
@@ -143,69 +135,9 @@ __device__ __forceinline__ T block_fold(T v, T *slots) {
     return v;
 }
 
-template <typename T, typename Op, int THREADS, int UNROLL>
-__global__ void __launch_bounds__(THREADS)
-reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
-              T *partials, unsigned int *ticket) {
-    constexpr int VEC = 16 / sizeof(T);
-    __shared__ T slots[THREADS / 32];
-    __shared__ bool is_last;
-
-    // elements before the first 16-byte boundary, then whole vectors, then a tail
-    const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
-    int64_t head = static_cast<int64_t>(((16u - (addr & 15u)) & 15u) / sizeof(T));
-    if (head > n) head = n;
-    const uint4 *xv = reinterpret_cast<const uint4 *>(x + head);
-    const int64_t nvec = (n - head) / VEC;
-    const int64_t tail_begin = head + nvec * VEC;
-
-    T acc[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u) acc[u] = Op::template identity<T>();
-
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * THREADS;
-    int64_t v = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
-    for (; v + (UNROLL - 1) * stride < nvec; v += UNROLL * stride) {
-        uint4 raw[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream16(xv + v + u * stride);
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) acc[u] = fold_vector<T, Op>(acc[u], raw[u]);
-    }
-    for (; v < nvec; v += stride) acc[0] = fold_vector<T, Op>(acc[0], load_stream16(xv + v));
-
-    if (blockIdx.x == 0) {  // fewer than 16 scalars on each side
-        if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);
-        const int64_t t = tail_begin + threadIdx.x;
-        if (t < n) acc[0] = Op::template apply<T>(acc[0], x[t]);
-    }
-#pragma unroll
-    for (int u = 1; u < UNROLL; ++u) acc[0] = Op::template apply<T>(acc[0], acc[u]);
-
-    T total = block_fold<T, Op, THREADS>(acc[0], slots);
-
-    if (threadIdx.x == 0) {
-        partials[blockIdx.x] = total;
-        __threadfence();
-        // wraps to 0 after gridDim.x tickets: the scratch is reusable as is
-        const unsigned int t = atomicInc(ticket, gridDim.x - 1);
-        is_last = (t == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-
-    T mine = Op::template identity<T>();
-    for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
-        mine = Op::template apply<T>(mine, __ldcg(partials + i));
-    total = block_fold<T, Op, THREADS>(mine, slots);
-    if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
-}
-
-// 256-bit variant: every CTA step folds one contiguous chunk of THREADS*UNROLL
-// 32-byte vectors (sm_100 has 256-bit global loads), so the CTAs in flight sweep
-// one contiguous window of the array.  Same tail handling and same single-pass
-// combine as above.
+// Every CTA step folds one contiguous chunk of THREADS*UNROLL 32-byte vectors
+// (sm_100 has 256-bit global loads), so the CTAs in flight sweep one contiguous
+// window of the array.
 struct alignas(32) Bits256 { uint4 lo, hi; };
 
 __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
@@ -219,7 +151,7 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
 
 template <typename T, typename Op, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)
-reduce_wide_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
+reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
                    T *partials, unsigned int *ticket) {
     constexpr int VEC = 32 / sizeof(T);
     __shared__ T slots[THREADS / 32];
@@ -284,27 +216,18 @@ reduce_wide_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ o
 template <typename T, typename Op>
 int launch(const void *x, int64_t n, const void *init_host, void *out, void *scratch,
            cudaStream_t stream) {
-    constexpr int VEC = 16 / sizeof(T);
     T init;
     memcpy(&init, init_host, sizeof(T));
-    const int per_sm = b2k::env_int("B2K_REDUCE_CTAS_PER_SM", 4);
+    // two persistent CTAs per SM measured best on B200; short inputs get one CTA per chunk
+    const int per_sm = b2k::env_int("B2K_REDUCE_CTAS_PER_SM", 2);
     int64_t max_grid = static_cast<int64_t>(b2k::sm_count()) * per_sm;
     if (max_grid > kMaxGrid) max_grid = kMaxGrid;
-    const int64_t nvec = n / VEC + 1;
-    int64_t grid = (nvec + static_cast<int64_t>(kThreads) * kUnroll - 1) /
-                   (static_cast<int64_t>(kThreads) * kUnroll);
+    const int64_t chunk_bytes = static_cast<int64_t>(kThreads) * kUnroll * 32;
+    int64_t grid = (n * static_cast<int64_t>(sizeof(T)) + chunk_bytes - 1) / chunk_bytes;
     if (grid < 1) grid = 1;
     if (grid > max_grid) grid = max_grid;
     auto *ticket = static_cast<unsigned int *>(scratch);
     auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
-    if (b2k::env_int("B2K_REDUCE_WIDE", 1) != 0) {
-        // one CTA step covers kThreads*kUnroll 32-byte vectors
-        int64_t wgrid = (n * static_cast<int64_t>(sizeof(T)) / 32 + kThreads * kUnroll - 1) / (kThreads * kUnroll);
-        if (wgrid < 1) wgrid = 1;
-        if (wgrid > max_grid) wgrid = max_grid;
-        reduce_wide_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(wgrid), kThreads, 0, stream>>>(
-            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
-    } else
     reduce_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
         static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
     b2k::note_launch();

@@ -155,15 +155,27 @@ def test_against_reference_headers_on_random_bits():
 def test_unaligned_views_use_the_scalar_kernel():
     x = config5_chunk(10007)
     d = cuda.to_device(x)
-    for off in (1, 2, 3, 5):
+    for off in (1, 2, 3, 4, 5, 8, 12):          # 4 and 12: 16- but not 32-byte aligned (128-bit path)
         got = cast(d[off:], "f32", "e4m3").copy_to_host()
         assert got.tobytes() == oracle.cast(x[off:], oracle.F32, oracle.E4M3, 1).tobytes()
     codes = cuda.to_device(oracle.cast(x, oracle.F32, oracle.E4M3, 1))
     want = oracle.cast(oracle.cast(x, oracle.F32, oracle.E4M3, 1), oracle.E4M3, oracle.F32)
-    for off in (1, 2, 3):
+    for off in (1, 2, 3, 4, 8, 12):
         got = cast(codes[off:], "e4m3", "f32").copy_to_host()
         nan = np.isnan(want[off:])
         assert got[~nan].tobytes() == want[off:][~nan].tobytes()
+
+
+def test_bf16_paths_by_alignment():
+    x = config5_chunk(20011)
+    d = cuda.to_device(x)
+    want = oracle.cast(x, oracle.F32, oracle.BF16)
+    hb = cuda.to_device(want)
+    for off in (0, 1, 4, 8, 16):
+        got = cast(d[off:], "f32", "bf16").copy_to_host().view(np.uint16)
+        assert got.tobytes() == want[off:].tobytes(), off
+        back = cast(hb[off:], "bf16", "f32").copy_to_host()
+        assert back.tobytes() == oracle.cast(want[off:], oracle.BF16, oracle.F32).tobytes(), off
 
 
 def test_out_argument_shapes_and_errors():
