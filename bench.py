@@ -42,8 +42,8 @@ sys.path.insert(0, ROOT)
 N_C2 = 1 << 28
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the reduce kernel at
-# 2^28 int32, from one ncu capture (profiles/reduce_max_int32_2p28.md); None until captured
-REDUCE_TRAFFIC_BYTES = None
+# 2^28 int32, from one ncu capture (profiles/reduce_max_int32_2p28.md)
+REDUCE_TRAFFIC_BYTES = 1081083744
 
 
 def measured_peak():
@@ -305,6 +305,8 @@ def main():
 
     if not args.no_paths:
         line["paths"] = secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr)
+        if rank == 0 and world == 1:
+            line["paths_cpu"] = secondary_cpu_baselines()
 
     if rank == 0:
         print(json.dumps(line), flush=True)
@@ -330,6 +332,62 @@ def cpu_baseline(host):
                       f"does (single Python thread; host has {os.cpu_count()} cores)",
             "seconds": dt,
             "numpy_max_full_GBps": N_C2 * 4 / dt_np / 1e9, "numpy_max_value": np_max}
+
+
+def secondary_cpu_baselines():
+    """The reference's CPU path for the other configurations, each on a bounded
+    sample (a few seconds in total).  kind "reference" = the reference's own code
+    (its vendored conversion headers compiled with g++); kind "port" = the oracle's
+    restatement of the reference algorithm."""
+    import oracle
+    out = {"host_cores": os.cpu_count()}
+
+    def clock(fn):
+        t0 = time.perf_counter()
+        r = fn()
+        return time.perf_counter() - t0, r
+
+    # C1: the simulator's Reduce is functools.reduce over the sequence
+    x = np.random.default_rng(0).random(1 << 20)
+    dt, got = clock(lambda: oracle.py_fold(lambda a, b: a + b, x, 0))
+    out["c1_reduce_sum_f64_2p20"] = {"GBps": x.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                     "sample": "full 2^20 float64, functools.reduce as the simulator does"}
+    # C3: the simulator's transpose is np.transpose; the copy is the honest cost
+    a = np.random.default_rng(2).standard_normal((4096, 4096), dtype=np.float32)
+    dt, _ = clock(lambda: np.ascontiguousarray(a.T))
+    out["c3a_transpose_f32"] = {"GBps": 2 * a.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                "sample": "4096x4096 float32 block, np.ascontiguousarray(a.T)"}
+    # C4: serial state chain (random.py:242-257) and the draw loop, C restatement
+    n = 1 << 16
+    dt, st = clock(lambda: oracle.init_states(n, 42, 0))
+    out["c4_rng_init"] = {"Mstates_per_s": n / dt / 1e6, "seconds": dt, "cores": 1, "kind": "port",
+                          "sample": "2^16 of the 2^24 states, serial jump chain in C"}
+
+    def draws():
+        oracle.fill(st, "uniform", np.float32, 64)
+        oracle.fill(st, "normal", np.float64, 16)
+    dt, _ = clock(draws)
+    out["c4_rng_generate_64u32_16n64"] = {"Gsamples_per_s": n * 80 / dt / 1e9, "GBps": n * 416 / dt / 1e9,
+                                          "seconds": dt, "cores": 1, "kind": "port",
+                                          "sample": "2^16 generators x (64 uniform f32 + 16 normal f64), C restatement"}
+    # C5: the reference's vendored cuda_fp8.hpp / cuda_bf16.hpp host paths on all cores
+    m = 1 << 24
+    v = (4 * np.random.default_rng(3).standard_normal(m)).astype(np.float32)
+    if oracle.have_ref_headers():
+        for label, src, dst, bpe in (("c5_cast_f32_to_e4m3", oracle.F32, oracle.E4M3, 5),
+                                     ("c5_cast_f32_to_bf16", oracle.F32, oracle.BF16, 6)):
+            dt, codes = clock(lambda: oracle.ref_cast(v, src, dst, 1, threads=0))
+            out[label] = {"GBps": m * bpe / dt / 1e9, "seconds": dt, "cores": os.cpu_count(), "kind": "reference",
+                          "sample": "2^24 of the 2^30 elements, vendored header host path, std::thread over all cores"}
+        e = oracle.ref_cast(v, oracle.F32, oracle.E4M3, 1)
+        dt, _ = clock(lambda: oracle.ref_cast(e, oracle.E4M3, oracle.F32, 1, threads=0))
+        out["c5_cast_e4m3_to_f32"] = {"GBps": m * 5 / dt / 1e9, "seconds": dt, "cores": os.cpu_count(),
+                                      "kind": "reference", "sample": "2^24 codes, vendored header host path"}
+    else:
+        dt, _ = clock(lambda: oracle.cast(v, oracle.F32, oracle.E4M3, 1))
+        out["c5_cast_f32_to_e4m3"] = {"GBps": m * 5 / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                      "sample": "2^24 of the 2^30 elements, C restatement"}
+    return out
 
 
 # --------------------------------------------------------------------------- other configurations

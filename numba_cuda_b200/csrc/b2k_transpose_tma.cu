@@ -13,13 +13,15 @@
 //   B[b]   <-st.shared of single items, lanes walk the contiguous direction <-'
 //   B[b]   --cp.async.bulk.tensor store (tiled, no swizzle)--> global
 //
-// B holds the transposed tile as (128/ES) output rows of R items.  Edge tiles
+// B holds the transposed tile as (128/ES) output rows of R items.  R = 64 (8 KB
+// tiles, four load stages) for items of 2 bytes and more, 128 for single bytes.  Edge tiles
 // need no code: out-of-range parts of a load read as zero and out-of-range
 // parts of a store are dropped by the tensor-map bounds.
 //
-// Persistent CTAs walk tiles in input row-major order so that CTAs running at
-// the same time read neighbouring lines; a ring of NSTAGE loads per CTA stays in
-// flight and B is double buffered against the asynchronous store.
+// Two persistent CTAs per SM walk the tiles panel by panel (see TileOrder); a
+// ring of NSTAGE loads per CTA stays in flight and B is double buffered against
+// the asynchronous store.  Two CTAs per SM is a sharp optimum on B200: one cannot
+// hide its own transpose step, three or more only add DRAM page conflicts.
 //
 // HBM roofline: 2*ES bytes per item (one read, one write).
 #include <cuda.h>
@@ -303,8 +305,8 @@ int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t
     switch (itemsize) {
     case 1: return launch<1, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 2:
-        if (tall == 64) return launch<2, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
-        return launch<2, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+        if (tall == 128) return launch<2, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+        return launch<2, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 4:
         if (tall == 128) return launch<4, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
         return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
