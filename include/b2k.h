@@ -54,7 +54,15 @@ enum b2k_op {
 };
 
 /* storage formats (cast) */
-enum b2k_format { B2K_FMT_F32 = 0, B2K_FMT_BF16 = 1, B2K_FMT_E4M3 = 2, B2K_FMT_E5M2 = 3 };
+enum b2k_format {
+    B2K_FMT_F32 = 0, B2K_FMT_BF16 = 1, B2K_FMT_E4M3 = 2, B2K_FMT_E5M2 = 3,
+    B2K_FMT_F64 = 4, B2K_FMT_F16 = 5, B2K_FMT_E8M0 = 6   /* b2k_cast_ex only */
+};
+
+/* rounding modes (b2k_cast_ex), numbered like cudaRoundMode */
+enum b2k_rounding {
+    B2K_ROUND_NEAREST = 0, B2K_ROUND_ZERO = 1, B2K_ROUND_POS_INF = 2, B2K_ROUND_MIN_INF = 3
+};
 
 /* draws (RNG fill) */
 enum b2k_draw {
@@ -151,6 +159,21 @@ B2K_API int b2k_xoroshiro128p_fill(void *states_dev, int64_t n,
  * saturate: 1 = SATFINITE, 0 = NOSAT (fp8 destinations only). */
 B2K_API int b2k_cast(int src_format, int dst_format, int saturate, const void *in_dev,
              void *out_dev, int64_t n, void *stream);
+
+/* The remaining conversion intrinsics as bulk casts.  Everything b2k_cast does
+ * (rounding = B2K_ROUND_NEAREST), plus
+ *   f32 -> bf16 toward zero / +inf / -inf : float32_to_bfloat16_rz/_ru/_rd
+ *                      (numba/cuda/bf16.py:208-210; cuda_bf16.hpp:505-553)
+ *   f64 -> bf16      : float64_to_bfloat16 (bf16.py:205; cuda_bf16.hpp:444-470)
+ *   f32 -> e8m0, bf16 -> e8m0 (toward zero or +inf, with or without saturation)
+ *                    : cvt_float_to_e8m0 / cvt_bfloat16raw_to_e8m0
+ *                      (numba/cuda/_internal/cuda_fp8.py:3449-3654;
+ *                       include/12/cuda_fp8.hpp:546-589, :689-740)
+ *   e8m0 -> bf16, e8m0 -> f32 : cvt_e8m0_to_bf16raw, float(fp8_e8m0)
+ *                      (cuda_fp8.hpp:817-851)
+ *   f32 <-> f16      : round to nearest even */
+B2K_API int b2k_cast_ex(int src_format, int dst_format, int saturate, int rounding, const void *in_dev,
+                        void *out_dev, int64_t n, void *stream);
 
 #ifdef __cplusplus
 }

@@ -43,6 +43,7 @@ def _nvcc() -> str:
 def _deps(src: str) -> list[str]:
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     hdrs.append(os.path.join(os.path.dirname(HERE), "include", "b2k.h"))
+    hdrs.append(os.path.join(os.path.dirname(HERE), "include", "b2k_xoroshiro128p.cuh"))
     return [src] + hdrs
 
 
@@ -89,5 +90,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+EXAMPLES_LIB = os.path.join(CSRC, "examples", "libb2k_examples.so")
+
+
+def build_examples(force: bool = False) -> str:
+    """Compile the example user kernels (``csrc/examples``) that are written
+    against ``include/b2k_xoroshiro128p.cuh``; the tests load the result."""
+    src = os.path.join(CSRC, "examples", "rng_user_kernels.cu")
+    hdr = os.path.join(os.path.dirname(HERE), "include", "b2k_xoroshiro128p.cuh")
+    if force or _stale(EXAMPLES_LIB, [src, hdr]):
+        cmd = [_nvcc(), *NVCC_FLAGS, "-shared", "-o", EXAMPLES_LIB, src, "-cudart", "static"]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            sys.stderr.write(p.stdout + p.stderr)
+            raise RuntimeError("building libb2k_examples.so failed")
+    return EXAMPLES_LIB
+
+
 if __name__ == "__main__":
+    build_examples(force="--force" in sys.argv)
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(_HERE, "csrc", "libb2k.so")
 # enums of include/b2k.h
 I8, I16, I32, I64, U8, U16, U32, U64, F32, F64 = range(10)
 ADD, MUL, MAX, MIN, AND, OR, XOR = range(7)
-FMT_F32, FMT_BF16, FMT_E4M3, FMT_E5M2 = range(4)
+FMT_F32, FMT_BF16, FMT_E4M3, FMT_E5M2, FMT_F64, FMT_F16, FMT_E8M0 = range(7)
+ROUND_NEAREST, ROUND_ZERO, ROUND_POS_INF, ROUND_MIN_INF = range(4)
 UNIFORM_F32, UNIFORM_F64, NORMAL_F32, NORMAL_F64 = range(4)
 
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_TOO_LARGE = -1, -2, -3, -4, -5
@@ -36,6 +37,7 @@ SIGNATURES = {
     "b2k_xoroshiro128p_init": (_i32, [_vp, _i64, _u64, _u64, _vp, _i64, _vp]),
     "b2k_xoroshiro128p_fill": (_i32, [_vp, _i64, _i32, _vp, _i64, _i32, _vp, _i64, _vp]),
     "b2k_cast": (_i32, [_i32, _i32, _i32, _vp, _vp, _i64, _vp]),
+    "b2k_cast_ex": (_i32, [_i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
 }
 #: diagnostics that are exported but not part of the public header
 _EXTRA = {

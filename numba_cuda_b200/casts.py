@@ -31,10 +31,21 @@ class fp8_interpretation_t(enum.IntEnum):
     E5M2 = 1
 
 
-FORMATS = {"f32": _lib.FMT_F32, "float32": _lib.FMT_F32, "bf16": _lib.FMT_BF16, "bfloat16": _lib.FMT_BF16,
+class cudaRoundMode(enum.IntEnum):
+    """Rounding modes of the conversion intrinsics (cuda_fp8.py / driver_types.h order)."""
+    cudaRoundNearest = 0
+    cudaRoundZero = 1
+    cudaRoundPosInf = 2
+    cudaRoundMinInf = 3
+
+
+FORMATS = {"f64": _lib.FMT_F64, "float64": _lib.FMT_F64, "f16": _lib.FMT_F16, "float16": _lib.FMT_F16,
+           "e8m0": _lib.FMT_E8M0, "fp8_e8m0": _lib.FMT_E8M0, "float8_e8m0fnu": _lib.FMT_E8M0,
+           "f32": _lib.FMT_F32, "float32": _lib.FMT_F32, "bf16": _lib.FMT_BF16, "bfloat16": _lib.FMT_BF16,
            "e4m3": _lib.FMT_E4M3, "fp8_e4m3": _lib.FMT_E4M3, "float8_e4m3fn": _lib.FMT_E4M3,
            "e5m2": _lib.FMT_E5M2, "fp8_e5m2": _lib.FMT_E5M2, "float8_e5m2": _lib.FMT_E5M2}
-_ITEMSIZE = {_lib.FMT_F32: 4, _lib.FMT_BF16: 2, _lib.FMT_E4M3: 1, _lib.FMT_E5M2: 1}
+_ITEMSIZE = {_lib.FMT_F32: 4, _lib.FMT_BF16: 2, _lib.FMT_E4M3: 1, _lib.FMT_E5M2: 1,
+             _lib.FMT_F64: 8, _lib.FMT_F16: 2, _lib.FMT_E8M0: 1}
 
 
 def _format_code(fmt) -> int:
@@ -51,13 +62,20 @@ def _storage_dtype(code: int):
         return np.dtype(np.float32)
     if code == _lib.FMT_BF16:
         return bfloat16_dtype()
+    if code == _lib.FMT_F64:
+        return np.dtype(np.float64)
+    if code == _lib.FMT_F16:
+        return np.dtype(np.float16)
     return np.dtype(np.uint8)
 
 
-def cast(src, src_format, dst_format, out=None, saturate=saturation_t.SATFINITE, stream=0):
+def cast(src, src_format, dst_format, out=None, saturate=saturation_t.SATFINITE, stream=0,
+         rounding=cudaRoundMode.cudaRoundNearest):
     """Convert every element of ``src`` (host or device array holding
     ``src_format`` items) to ``dst_format``; returns a device array of the same
-    shape.  Supported: f32 -> bf16 / e4m3 / e5m2 and back to f32."""
+    shape.  Round-to-nearest-even pairs: f32 <-> bf16 / e4m3 / e5m2 / f16,
+    f64 -> bf16, e8m0 -> bf16 / f32.  With ``rounding``: f32 -> bf16 toward zero,
+    +inf or -inf; f32 / bf16 -> e8m0 toward zero or +inf."""
     s, d = _format_code(src_format), _format_code(dst_format)
     dsrc, _ = auto_device(src, stream=stream)
     if dsrc.dtype.itemsize != _ITEMSIZE[s]:
@@ -70,15 +88,16 @@ def cast(src, src_format, dst_format, out=None, saturate=saturation_t.SATFINITE,
         out, _ = auto_device(out, stream=stream, copy=False)
         if out.dtype.itemsize != _ITEMSIZE[d] or out.size != dsrc.size or not out.flags["C_CONTIGUOUS"]:
             raise ValueError("out must be C-contiguous with the source's size and the target's item size")
-    _lib.check(_lib.lib().b2k_cast(s, d, int(saturate), dsrc._ptr, out._ptr, dsrc.size, stream_ptr(stream)))
+    _lib.check(_lib.lib().b2k_cast_ex(s, d, int(saturate), int(rounding), dsrc._ptr, out._ptr, dsrc.size,
+                                      stream_ptr(stream)))
     return out
 
 
-def _scalar_or_bulk(x, s, d, saturate=saturation_t.SATFINITE):
+def _scalar_or_bulk(x, s, d, saturate=saturation_t.SATFINITE, rounding=cudaRoundMode.cudaRoundNearest):
     if isinstance(x, DeviceNDArray) or (isinstance(x, np.ndarray) and x.ndim > 0):
-        return cast(x, s, d, saturate=saturate)
+        return cast(x, s, d, saturate=saturate, rounding=rounding)
     host = np.array([x], dtype=_storage_dtype(s))
-    return cast(host, s, d, saturate=saturate).copy_to_host()[0]
+    return cast(host, s, d, saturate=saturate, rounding=rounding).copy_to_host()[0]
 
 
 # ---- fp8 storage intrinsics (cuda_fp8.py:3341-3410) --------------------------
@@ -129,8 +148,67 @@ def bfloat16_to_float32(x):
     return _scalar_or_bulk(x, _lib.FMT_BF16, _lib.FMT_F32)
 
 
+def float32_to_bfloat16_rz(x):
+    """float32 -> bfloat16, rounding toward zero (bf16.py:208)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_BF16, rounding=cudaRoundMode.cudaRoundZero)
+
+
+def float32_to_bfloat16_rd(x):
+    """float32 -> bfloat16, rounding toward -inf (bf16.py:209)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_BF16, rounding=cudaRoundMode.cudaRoundMinInf)
+
+
+def float32_to_bfloat16_ru(x):
+    """float32 -> bfloat16, rounding toward +inf (bf16.py:210)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_BF16, rounding=cudaRoundMode.cudaRoundPosInf)
+
+
+def float64_to_bfloat16(x):
+    """float64 -> bfloat16, round to nearest even in one step (bf16.py:205)."""
+    return _scalar_or_bulk(x, _lib.FMT_F64, _lib.FMT_BF16)
+
+
+# ---- E8M0: the 8-bit power-of-two scale type (cuda_fp8.py:3449-3654) -----------------
+def _e8m0_rounding(rounding):
+    rounding = cudaRoundMode(int(rounding))
+    if rounding not in (cudaRoundMode.cudaRoundZero, cudaRoundMode.cudaRoundPosInf):
+        raise ValueError("e8m0 conversions round toward zero or toward +inf")
+    return rounding
+
+
+def cvt_float_to_e8m0(x, saturate, rounding):
+    """float32 -> E8M0 code (uint8; 0xFF is NaN)."""
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_E8M0, saturate, _e8m0_rounding(rounding))
+
+
+def cvt_bfloat16raw_to_e8m0(x, saturate, rounding):
+    """bfloat16 (raw bits or ml_dtypes values) -> E8M0 code."""
+    return _scalar_or_bulk(x, _lib.FMT_BF16, _lib.FMT_E8M0, saturate, _e8m0_rounding(rounding))
+
+
+def cvt_e8m0_to_bf16raw(codes):
+    """E8M0 code -> bfloat16 (``2**(code-127)``; code 0 is the bf16 denormal 2**-127)."""
+    return _scalar_or_bulk(codes, _lib.FMT_E8M0, _lib.FMT_BF16)
+
+
+def fp8_e8m0_to_float32(codes):
+    """``float32(fp8_e8m0)``."""
+    return _scalar_or_bulk(codes, _lib.FMT_E8M0, _lib.FMT_F32)
+
+
+def float32_to_float16(x):
+    return _scalar_or_bulk(x, _lib.FMT_F32, _lib.FMT_F16)
+
+
+def float16_to_float32(x):
+    return _scalar_or_bulk(x, _lib.FMT_F16, _lib.FMT_F32)
+
+
 __all__ = [
     "cast", "saturation_t", "fp8_interpretation_t", "cvt_float_to_fp8", "cvt_float2_to_fp8x2",
     "fp8_e4m3", "fp8_e5m2", "fp8_e4m3_to_float32", "fp8_e5m2_to_float32",
     "float32_to_bfloat16", "float32_to_bfloat16_rn", "bfloat16_to_float32",
+    "cudaRoundMode", "float32_to_bfloat16_rz", "float32_to_bfloat16_rd", "float32_to_bfloat16_ru",
+    "float64_to_bfloat16", "cvt_float_to_e8m0", "cvt_bfloat16raw_to_e8m0", "cvt_e8m0_to_bf16raw",
+    "fp8_e8m0_to_float32", "float32_to_float16", "float16_to_float32",
 ]

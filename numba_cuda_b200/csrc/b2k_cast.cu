@@ -305,6 +305,148 @@ int launch(const void *in, void *out, int64_t n, cudaStream_t stream) {
     return B2K_OK;
 }
 
+// ---- further conversions: directed rounding, f64, E8M0, f16 --------------------
+// Element-wise converters (`one`) run through a generic wide kernel: eight
+// elements per thread (four when an 8-byte type is involved), each side moving as
+// one vector access per lane.
+
+template <int MODE>  // cudaRoundMode order: 0 nearest, 1 zero, 2 +inf, 3 -inf
+struct F32ToBf16Mode {
+    using InS = float; using OutS = uint16_t;
+    __device__ static OutS one(InS x) {
+        uint16_t r;
+        if constexpr (MODE == 1) asm("cvt.rz.bf16.f32 %0, %1;" : "=h"(r) : "f"(x));
+        else if constexpr (MODE == 2) asm("cvt.rp.bf16.f32 %0, %1;" : "=h"(r) : "f"(x));
+        else if constexpr (MODE == 3) asm("cvt.rm.bf16.f32 %0, %1;" : "=h"(r) : "f"(x));
+        else asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(x));
+        return r;
+    }
+};
+struct F64ToBf16 {  // __double2bfloat16 (cuda_bf16.hpp:444-470)
+    using InS = double; using OutS = uint16_t;
+    __device__ static OutS one(InS x) {
+        uint16_t r;
+        asm("cvt.rn.bf16.f64 %0, %1;" : "=h"(r) : "d"(x));
+        return r;
+    }
+};
+template <bool UP, bool SAT>  // __nv_cvt_float_to_e8m0 (cuda_fp8.hpp:689-740)
+struct F32ToE8m0 {
+    using InS = float; using OutS = uint8_t;
+    __device__ static OutS one(InS x) {
+        uint16_t r;
+        if constexpr (UP && SAT) asm("cvt.rp.satfinite.ue8m0x2.f32 %0, %2, %1;" : "=h"(r) : "f"(x), "f"(0.0f));
+        else if constexpr (UP) asm("cvt.rp.ue8m0x2.f32 %0, %2, %1;" : "=h"(r) : "f"(x), "f"(0.0f));
+        else if constexpr (SAT) asm("cvt.rz.satfinite.ue8m0x2.f32 %0, %2, %1;" : "=h"(r) : "f"(x), "f"(0.0f));
+        else asm("cvt.rz.ue8m0x2.f32 %0, %2, %1;" : "=h"(r) : "f"(x), "f"(0.0f));
+        return static_cast<OutS>(r);
+    }
+};
+template <bool UP, bool SAT>  // __nv_cvt_bfloat16raw_to_e8m0 (cuda_fp8.hpp:546-589)
+struct Bf16ToE8m0 {
+    using InS = uint16_t; using OutS = uint8_t;
+    __device__ static OutS one(InS h) {
+        uint16_t r;
+        const uint32_t in = h;
+        if constexpr (UP && SAT) asm("cvt.rp.satfinite.ue8m0x2.bf16x2 %0, %1;" : "=h"(r) : "r"(in));
+        else if constexpr (UP) asm("cvt.rp.ue8m0x2.bf16x2 %0, %1;" : "=h"(r) : "r"(in));
+        else if constexpr (SAT) asm("cvt.rz.satfinite.ue8m0x2.bf16x2 %0, %1;" : "=h"(r) : "r"(in));
+        else asm("cvt.rz.ue8m0x2.bf16x2 %0, %1;" : "=h"(r) : "r"(in));
+        return static_cast<OutS>(r);
+    }
+};
+struct E8m0ToBf16 {  // __nv_cvt_e8m0_to_bf16raw (cuda_fp8.hpp:833-851)
+    using InS = uint8_t; using OutS = uint16_t;
+    __device__ static OutS one(InS e) {
+        uint32_t r;
+        asm("cvt.rn.bf16x2.ue8m0x2 %0, %1;" : "=r"(r) : "h"(static_cast<uint16_t>(e)));
+        return static_cast<OutS>(r);
+    }
+};
+struct E8m0ToF32 {  // float(fp8_e8m0): E8M0 -> bf16 -> f32
+    using InS = uint8_t; using OutS = float;
+    __device__ static OutS one(InS e) { return bf16bits_to_f32(E8m0ToBf16::one(e)); }
+};
+struct F32ToF16 {
+    using InS = float; using OutS = uint16_t;
+    __device__ static OutS one(InS x) {
+        uint16_t r;
+        asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(x));
+        return r;
+    }
+};
+struct F16ToF32 {
+    using InS = uint16_t; using OutS = float;
+    __device__ static OutS one(InS h) { return f16bits_to_f32(h); }
+};
+
+template <int BYTES> struct VecOf;
+template <> struct VecOf<4> { using type = uint32_t; };
+template <> struct VecOf<8> { using type = uint2; };
+template <> struct VecOf<16> { using type = uint4; };
+template <> struct VecOf<32> { using type = Bits256; };
+template <> struct Mover<uint32_t> {
+    __device__ static uint32_t load(const uint32_t *p) { return __ldcs(p); }
+    __device__ static void store(uint32_t *p, const uint32_t &v) { __stcs(p, v); }
+};
+
+template <typename C>
+struct WideOf {
+    static constexpr int ELEMS = (sizeof(typename C::InS) == 8 || sizeof(typename C::OutS) == 8) ? 4 : 8;
+    using In = typename VecOf<ELEMS * sizeof(typename C::InS)>::type;
+    using Out = typename VecOf<ELEMS * sizeof(typename C::OutS)>::type;
+    __device__ static Out convert(const In &v) {
+        union { In raw; typename C::InS e[ELEMS]; } src;
+        union { Out raw; typename C::OutS e[ELEMS]; } dst;
+        src.raw = v;
+#pragma unroll
+        for (int k = 0; k < ELEMS; ++k) dst.e[k] = C::one(src.e[k]);
+        return dst.raw;
+    }
+};
+
+template <typename C>
+__global__ void __launch_bounds__(kThreads)
+cast_generic_wide_kernel(const typename WideOf<C>::In *__restrict__ in, typename WideOf<C>::Out *__restrict__ out,
+                         int64_t items, int64_t n) {
+    using W = WideOf<C>;
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    if (i < items) Mover<typename W::Out>::store(out + i, W::convert(Mover<typename W::In>::load(in + i)));
+    if (blockIdx.x == gridDim.x - 1) {  // ragged end
+        const int64_t t = items * W::ELEMS + threadIdx.x;
+        if (t < n) {
+            const auto *in_s = reinterpret_cast<const typename C::InS *>(in);
+            auto *out_s = reinterpret_cast<typename C::OutS *>(out);
+            out_s[t] = C::one(in_s[t]);
+        }
+    }
+}
+
+template <typename C>
+int launch_generic(const void *in, void *out, int64_t n, cudaStream_t stream) {
+    if (n == 0) return B2K_OK;
+    if (!b2k::aligned_to<void>(in, sizeof(typename C::InS)) || !b2k::aligned_to<void>(out, sizeof(typename C::OutS)))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_cast_ex: pointers must be aligned to the element size");
+    using W = WideOf<C>;
+    if (b2k::aligned_to<void>(in, sizeof(typename W::In)) && b2k::aligned_to<void>(out, sizeof(typename W::Out))) {
+        const int64_t items = n / W::ELEMS;
+        int64_t grid = (items + kThreads - 1) / kThreads;
+        if (grid < 1) grid = 1;
+        if (grid > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_cast_ex: array too large");
+        cast_generic_wide_kernel<C><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename W::In *>(in), static_cast<typename W::Out *>(out), items, n);
+    } else {
+        int64_t grid = (n + kThreads - 1) / kThreads;
+        const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * 8;
+        if (grid > cap) grid = cap;
+        cast_scalar_kernel<C><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const typename C::InS *>(in), static_cast<typename C::OutS *>(out), n);
+    }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_cast_ex launch");
+    return B2K_OK;
+}
+
 }  // namespace
 
 extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void *out_dev,
@@ -324,4 +466,46 @@ extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void
     if (src == B2K_FMT_E4M3 && dst == B2K_FMT_F32) return launch<Fp8ToF32<false>>(in_dev, out_dev, n, s);
     if (src == B2K_FMT_E5M2 && dst == B2K_FMT_F32) return launch<Fp8ToF32<true>>(in_dev, out_dev, n, s);
     return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_cast: no conversion from format %d to %d", src, dst);
+}
+
+extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const void *in_dev, void *out_dev,
+                           int64_t n, void *stream) {
+    if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast_ex: negative length %lld", (long long)n);
+    if (n > 0 && (!in_dev || !out_dev)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast_ex: null pointer");
+    if (rounding < B2K_ROUND_NEAREST || rounding > B2K_ROUND_MIN_INF)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast_ex: unknown rounding mode %d", rounding);
+    cudaStream_t s = b2k::as_stream(stream);
+    const bool sat = saturate != 0;
+    // the nearest-even pairs of b2k_cast
+    if (rounding == B2K_ROUND_NEAREST && src <= B2K_FMT_E5M2 && dst <= B2K_FMT_E5M2)
+        return b2k_cast(src, dst, saturate, in_dev, out_dev, n, stream);
+    if (src == B2K_FMT_F32 && dst == B2K_FMT_BF16) {
+        if (rounding == B2K_ROUND_ZERO) return launch_generic<F32ToBf16Mode<1>>(in_dev, out_dev, n, s);
+        if (rounding == B2K_ROUND_POS_INF) return launch_generic<F32ToBf16Mode<2>>(in_dev, out_dev, n, s);
+        return launch_generic<F32ToBf16Mode<3>>(in_dev, out_dev, n, s);
+    }
+    if (src == B2K_FMT_F64 && dst == B2K_FMT_BF16 && rounding == B2K_ROUND_NEAREST)
+        return launch_generic<F64ToBf16>(in_dev, out_dev, n, s);
+    const bool e8_mode = rounding == B2K_ROUND_ZERO || rounding == B2K_ROUND_POS_INF;
+    const bool up = rounding == B2K_ROUND_POS_INF;
+    if (src == B2K_FMT_F32 && dst == B2K_FMT_E8M0 && e8_mode) {
+        if (up) return sat ? launch_generic<F32ToE8m0<true, true>>(in_dev, out_dev, n, s)
+                           : launch_generic<F32ToE8m0<true, false>>(in_dev, out_dev, n, s);
+        return sat ? launch_generic<F32ToE8m0<false, true>>(in_dev, out_dev, n, s)
+                   : launch_generic<F32ToE8m0<false, false>>(in_dev, out_dev, n, s);
+    }
+    if (src == B2K_FMT_BF16 && dst == B2K_FMT_E8M0 && e8_mode) {
+        if (up) return sat ? launch_generic<Bf16ToE8m0<true, true>>(in_dev, out_dev, n, s)
+                           : launch_generic<Bf16ToE8m0<true, false>>(in_dev, out_dev, n, s);
+        return sat ? launch_generic<Bf16ToE8m0<false, true>>(in_dev, out_dev, n, s)
+                   : launch_generic<Bf16ToE8m0<false, false>>(in_dev, out_dev, n, s);
+    }
+    if (rounding == B2K_ROUND_NEAREST) {
+        if (src == B2K_FMT_E8M0 && dst == B2K_FMT_BF16) return launch_generic<E8m0ToBf16>(in_dev, out_dev, n, s);
+        if (src == B2K_FMT_E8M0 && dst == B2K_FMT_F32) return launch_generic<E8m0ToF32>(in_dev, out_dev, n, s);
+        if (src == B2K_FMT_F32 && dst == B2K_FMT_F16) return launch_generic<F32ToF16>(in_dev, out_dev, n, s);
+        if (src == B2K_FMT_F16 && dst == B2K_FMT_F32) return launch_generic<F16ToF32>(in_dev, out_dev, n, s);
+    }
+    return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_cast_ex: no conversion from format %d to %d with rounding %d", src,
+                     dst, rounding);
 }

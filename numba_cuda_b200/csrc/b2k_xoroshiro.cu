@@ -27,6 +27,7 @@
 #include <cstring>
 #include <mutex>
 
+#include "../../include/b2k_xoroshiro128p.cuh"
 #include "b2k_internal.cuh"
 
 namespace {
@@ -227,33 +228,8 @@ xoro_init_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_
 }
 
 // ---- device: draws ------------------------------------------------------------------
-__device__ __forceinline__ uint64_t rotl_d(uint64_t x, int k) { return (x << k) | (x >> (64 - k)); }
-
-// random.py:97-115
-__device__ __forceinline__ uint64_t next_d(uint64_t &s0, uint64_t &s1) {
-    const uint64_t out = s0 + s1;
-    s1 ^= s0;
-    s0 = rotl_d(s0, 55) ^ s1 ^ (s1 << 14);
-    s1 = rotl_d(s1, 36);
-    return out;
-}
-// random.py:146-156.  The f64 value (x>>11)*2^-53 is exact, so rounding the
-// 53-bit integer to f32 first and scaling by a power of two gives the same bits
-// as rounding the f64 product.
-__device__ __forceinline__ float unit_f32(uint64_t x) { return __ull2float_rn(x >> 11) * 0x1p-53f; }
-__device__ __forceinline__ double unit_f64(uint64_t x) { return __ull2double_rn(x >> 11) * 0x1p-53; }
-
-// random.py:192-238: Box-Muller, cosine branch, from two f32 uniforms.
-__device__ __forceinline__ float normal_f32(uint64_t &s0, uint64_t &s1) {
-    const float u1 = unit_f32(next_d(s0, s1));
-    const float u2 = unit_f32(next_d(s0, s1));
-    return sqrtf(-2.0f * logf(u1)) * cosf(6.2831855f * u2);
-}
-__device__ __forceinline__ double normal_f64(uint64_t &s0, uint64_t &s1) {
-    const float u1 = unit_f32(next_d(s0, s1));
-    const float u2 = unit_f32(next_d(s0, s1));
-    return sqrt(-2.0 * static_cast<double>(logf(u1))) * cos(6.283185307179586 * static_cast<double>(u2));
-}
+// The generator arithmetic lives in include/b2k_xoroshiro128p.cuh so that user
+// CUDA C++ kernels and this library draw from the same code.
 
 struct Segment {
     void *out;
@@ -268,10 +244,15 @@ constexpr int kStageBytes = 32 * kPitch64 * 8;  // >= 32*kPitch32*4
 
 template <typename T, int DRAW>
 __device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
-    if constexpr (DRAW == B2K_UNIFORM_F32) return unit_f32(next_d(s0, s1));
-    else if constexpr (DRAW == B2K_UNIFORM_F64) return unit_f64(next_d(s0, s1));
-    else if constexpr (DRAW == B2K_NORMAL_F32) return normal_f32(s0, s1);
-    else return normal_f64(s0, s1);
+    xoroshiro128p_generator g(s0, s1);
+    T r;
+    if constexpr (DRAW == B2K_UNIFORM_F32) r = g.uniform_float32();
+    else if constexpr (DRAW == B2K_UNIFORM_F64) r = g.uniform_float64();
+    else if constexpr (DRAW == B2K_NORMAL_F32) r = g.normal_float32();
+    else r = g.normal_float64();
+    s0 = g.s0;
+    s1 = g.s1;
+    return r;
 }
 
 // One segment for the 32 generators [base, base+32) of this warp.

@@ -29,7 +29,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 #: the RNG state record of numba_cuda/numba/cuda/random.py:47-49
 xoroshiro128p_dtype = np.dtype([("s0", np.uint64), ("s1", np.uint64)], align=True)
 
-F32, BF16, E4M3, E5M2 = 0, 1, 2, 3
+F32, BF16, E4M3, E5M2, F64, F16, E8M0 = 0, 1, 2, 3, 4, 5, 6
+RN, RZ, RU, RD = 0, 1, 2, 3   # cudaRoundMode order: nearest, zero, +inf, -inf
 OPS = {"add": 0, "mul": 1, "max": 2, "min": 3}
 
 
@@ -74,6 +75,18 @@ def lib() -> ctypes.CDLL:
     L.oracle_bf16_to_f32.restype = ctypes.c_float
     L.oracle_cast.argtypes = [i32, i32, i32, vp, vp, i64]
     L.oracle_cast.restype = i32
+    L.oracle_f32_to_bf16_mode.argtypes = [ctypes.c_float, i32]
+    L.oracle_f32_to_bf16_mode.restype = ctypes.c_uint16
+    L.oracle_f64_to_bf16.argtypes = [ctypes.c_double]
+    L.oracle_f64_to_bf16.restype = ctypes.c_uint16
+    L.oracle_bf16_to_e8m0.argtypes = [ctypes.c_uint16, i32, i32]
+    L.oracle_bf16_to_e8m0.restype = ctypes.c_uint8
+    L.oracle_f32_to_e8m0.argtypes = [ctypes.c_float, i32, i32]
+    L.oracle_f32_to_e8m0.restype = ctypes.c_uint8
+    L.oracle_e8m0_to_bf16.argtypes = [ctypes.c_uint8]
+    L.oracle_e8m0_to_bf16.restype = ctypes.c_uint16
+    L.oracle_cast_ex.argtypes = [i32, i32, i32, i32, vp, vp, i64]
+    L.oracle_cast_ex.restype = i32
     L.oracle_fold_f64.argtypes = [vp, i64, ctypes.c_double, i32]
     L.oracle_fold_f64.restype = ctypes.c_double
     L.oracle_fold_f32.argtypes = [vp, i64, ctypes.c_float, i32]
@@ -105,6 +118,16 @@ def ref_headers() -> ctypes.CDLL:
     L.ref_float2bfloat16_rn.restype = ctypes.c_uint16
     L.ref_bfloat162float.argtypes = [ctypes.c_uint16]
     L.ref_bfloat162float.restype = ctypes.c_float
+    L.ref_float2bfloat16_mode.argtypes = [ctypes.c_float, i32]
+    L.ref_float2bfloat16_mode.restype = ctypes.c_uint16
+    L.ref_double2bfloat16.argtypes = [ctypes.c_double]
+    L.ref_double2bfloat16.restype = ctypes.c_uint16
+    L.ref_cvt_float_to_e8m0.argtypes = [ctypes.c_float, i32, i32]
+    L.ref_cvt_float_to_e8m0.restype = ctypes.c_uint8
+    L.ref_cvt_bfloat16raw_to_e8m0.argtypes = [ctypes.c_uint16, i32, i32]
+    L.ref_cvt_bfloat16raw_to_e8m0.restype = ctypes.c_uint8
+    L.ref_cvt_e8m0_to_bf16raw.argtypes = [ctypes.c_uint8]
+    L.ref_cvt_e8m0_to_bf16raw.restype = ctypes.c_uint16
     L.ref_bulk_f32_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
     L.ref_bulk_fp8_to_f32.argtypes = [vp, vp, i64, i32, i32]
     L.ref_bulk_f32_to_bf16.argtypes = [vp, vp, i64, i32]
@@ -150,7 +173,8 @@ def next_u64(state_pair):
 
 
 # ---------------------------------------------------------------- casts
-_CODE_DTYPE = {F32: np.float32, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8}
+_CODE_DTYPE = {F32: np.float32, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8, F64: np.float64,
+               F16: np.float16, E8M0: np.uint8}
 
 
 def cast(x: np.ndarray, src: int, dst: int, sat: int = 1) -> np.ndarray:
@@ -159,6 +183,21 @@ def cast(x: np.ndarray, src: int, dst: int, sat: int = 1) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
     out = np.empty(x.shape, dtype=_CODE_DTYPE[dst])
     rc = lib().oracle_cast(src, dst, sat, _ptr(x), _ptr(out), x.size)
+    if rc != 0:
+        raise ValueError(f"unsupported cast {src}->{dst}")
+    return out
+
+
+def cast_ex(x: np.ndarray, src: int, dst: int, sat: int = 1, mode: int = RN) -> np.ndarray:
+    """Bulk cast for the rounding-mode / f64 / E8M0 / f16 conversions (C restatement;
+    f16 uses NumPy's IEEE round-to-nearest-even conversion)."""
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    if (src, dst) == (F32, F16):
+        return x.astype(np.float16)
+    if (src, dst) == (F16, F32):
+        return x.astype(np.float32)
+    out = np.empty(x.shape, dtype=_CODE_DTYPE[dst])
+    rc = lib().oracle_cast_ex(src, dst, sat, mode, _ptr(x), _ptr(out), x.size)
     if rc != 0:
         raise ValueError(f"unsupported cast {src}->{dst}")
     return out

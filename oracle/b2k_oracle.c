@@ -305,6 +305,98 @@ ORACLE_API int oracle_cast(int src, int dst, int sat, const void *in, void *out,
     return 0;
 }
 
+/* ---- further conversions (rounding modes, f64, E8M0, f16) -------------------- */
+
+/* cuda_bf16.hpp:505-553 (host branches): f32 -> bf16 with directed rounding.
+ * mode: 1 = toward zero, 2 = toward +inf, 3 = toward -inf (cudaRoundMode order);
+ * 0 = nearest even.  NaN gives 0x7FFF in every mode. */
+ORACLE_API uint16_t oracle_f32_to_bf16_mode(float x, int mode) {
+    if (mode == 0) return oracle_f32_to_bf16(x);
+    uint32_t b;
+    memcpy(&b, &x, sizeof b);
+    if ((b & 0x7FFFFFFFu) > 0x7F800000u) return 0x7FFFu;
+    uint16_t hi = (uint16_t)(b >> 16);
+    uint32_t rest = b << 16;
+    uint32_t negative = b >> 31;
+    if (mode == 3 && rest != 0 && negative) ++hi;   /* more negative */
+    if (mode == 2 && rest != 0 && !negative) ++hi;  /* more positive */
+    return hi;
+}
+
+/* cuda_bf16.hpp:452-470 (host branch): f64 -> bf16, nearest even.  The double is
+ * first rounded to float "to odd" (sticky bit kept in the last place) so that the
+ * second rounding to bf16 sees every discarded bit. */
+ORACLE_API uint16_t oracle_f64_to_bf16(double x) {
+    float f = (float)x;
+    double back = (double)f;
+    uint32_t u;
+    memcpy(&u, &f, sizeof u);
+    int not_nan = ((u << 1) <= 0xFF000000u);
+    if (x > 0.0 && back > x) u--;
+    if (x < 0.0 && back < x) u--;
+    if (back != x && not_nan) u |= 1u;
+    memcpy(&f, &u, sizeof f);
+    return oracle_f32_to_bf16(f);
+}
+
+/* cuda_fp8.hpp:546-589 (host branch): bf16 bits -> E8M0 (an 8-bit biased exponent,
+ * 0xFF = NaN).  mode: 1 = toward zero, 2 = toward +inf. */
+ORACLE_API uint8_t oracle_bf16_to_e8m0(uint16_t h, int sat, int mode) {
+    uint8_t res = (uint8_t)(h >> 7);
+    if (mode == 2) {
+        if ((h & 0x007Fu) && ((h & 0x7FFFu) > 0x0040u) && ((h & 0x7FFFu) < 0x7F80u)) res++;
+    }
+    if (sat) {
+        if (((h & 0x7FFFu) <= 0x7F80u) && res == 0xFFu) res--;
+    }
+    return res;
+}
+
+/* cuda_fp8.hpp:652-687 (host branches of the bf16 helpers) and :689-740:
+ * f32 -> E8M0 goes through bf16 with the same directed rounding (of |x| for
+ * the upward mode). */
+ORACLE_API uint8_t oracle_f32_to_e8m0(float x, int sat, int mode) {
+    uint32_t b;
+    memcpy(&b, &x, sizeof b);
+    uint16_t h;
+    if (mode == 1) {
+        h = ((b & 0x7FFFFFFFu) > 0x7F800000u) ? 0x7FFFu : (uint16_t)(b >> 16);
+    } else {
+        uint32_t a = (b << 1) >> 1;                      /* |x| */
+        if (a > 0x7F800000u) h = 0x7FFFu;
+        else if (a < 0x7F800000u && (a & 0xFFFFu) != 0) h = (uint16_t)((a >> 16) + 1u);
+        else h = (uint16_t)(a >> 16);
+    }
+    return oracle_bf16_to_e8m0(h, sat, mode);
+}
+
+/* cuda_fp8.hpp:817-831: E8M0 -> bf16 bits (2^-127 is the bf16 denormal 0x0040). */
+ORACLE_API uint16_t oracle_e8m0_to_bf16(uint8_t e) {
+    if (e == 0xFFu) return 0x7FFFu;
+    if (e == 0u) return 0x0040u;
+    return (uint16_t)((uint16_t)e << 7);
+}
+
+/* Bulk form of the above.  Formats: 0 f32, 1 bf16, 4 f64, 6 e8m0. */
+ORACLE_API int oracle_cast_ex(int src, int dst, int sat, int mode, const void *in, void *out, int64_t n) {
+    if (src == 0 && dst == 1) {
+        for (int64_t i = 0; i < n; ++i) ((uint16_t *)out)[i] = oracle_f32_to_bf16_mode(((const float *)in)[i], mode);
+    } else if (src == 4 && dst == 1) {
+        for (int64_t i = 0; i < n; ++i) ((uint16_t *)out)[i] = oracle_f64_to_bf16(((const double *)in)[i]);
+    } else if (src == 0 && dst == 6) {
+        for (int64_t i = 0; i < n; ++i) ((uint8_t *)out)[i] = oracle_f32_to_e8m0(((const float *)in)[i], sat, mode);
+    } else if (src == 1 && dst == 6) {
+        for (int64_t i = 0; i < n; ++i) ((uint8_t *)out)[i] = oracle_bf16_to_e8m0(((const uint16_t *)in)[i], sat, mode);
+    } else if (src == 6 && dst == 1) {
+        for (int64_t i = 0; i < n; ++i) ((uint16_t *)out)[i] = oracle_e8m0_to_bf16(((const uint8_t *)in)[i]);
+    } else if (src == 6 && dst == 0) {
+        for (int64_t i = 0; i < n; ++i) ((float *)out)[i] = oracle_bf16_to_f32(oracle_e8m0_to_bf16(((const uint8_t *)in)[i]));
+    } else {
+        return -1;
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------ */
 /* reduce and transpose                                                */
 /* ------------------------------------------------------------------ */

@@ -50,6 +50,27 @@ float ref_bfloat162float(uint16_t bits) {
     return __bfloat162float((__nv_bfloat16)r);
 }
 
+// __float2bfloat16_rz / _ru / _rd (cuda_bf16.hpp:505-553); mode as cudaRoundMode
+uint16_t ref_float2bfloat16_mode(float x, int mode) {
+    __nv_bfloat16 v = mode == 1 ? __float2bfloat16_rz(x) : mode == 2 ? __float2bfloat16_ru(x)
+                    : mode == 3 ? __float2bfloat16_rd(x) : __float2bfloat16_rn(x);
+    return ((__nv_bfloat16_raw)v).x;
+}
+// __double2bfloat16 (cuda_bf16.hpp:444-470)
+uint16_t ref_double2bfloat16(double x) { return ((__nv_bfloat16_raw)__double2bfloat16(x)).x; }
+// __nv_cvt_float_to_e8m0 (cuda_fp8.hpp:689-740), __nv_cvt_bfloat16raw_to_e8m0 (:546-589),
+// __nv_cvt_e8m0_to_bf16raw (:833-851)
+uint8_t ref_cvt_float_to_e8m0(float x, int sat, int mode) {
+    return (uint8_t)__nv_cvt_float_to_e8m0(x, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                           mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
+uint8_t ref_cvt_bfloat16raw_to_e8m0(uint16_t bits, int sat, int mode) {
+    __nv_bfloat16_raw r; r.x = bits;
+    return (uint8_t)__nv_cvt_bfloat16raw_to_e8m0(r, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                                 mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
+uint16_t ref_cvt_e8m0_to_bf16raw(uint8_t e) { return __nv_cvt_e8m0_to_bf16raw((__nv_fp8_storage_t)e).x; }
+
 }  // extern "C"
 
 // Bulk loops split over `threads` host threads (std::thread; <=0 means all cores).

@@ -203,6 +203,23 @@ def main() -> None:
         out[f"{name}_ctor"] = np.array(
             [R.ref_fp8_from_float(float(v), dst - 2) for v in (1.0, 2.0, 4.0, 1e20, -1e20)], dtype=np.uint8)
     out["bf16_rn"] = oracle.ref_cast(x, oracle.F32, oracle.BF16)
+    # directed rounding, f64 -> bf16 and the E8M0 scale type (vendored headers, host path)
+    for mode, tag in ((1, "rz"), (2, "ru"), (3, "rd")):
+        out[f"bf16_{tag}"] = np.array([R.ref_float2bfloat16_mode(float(v), mode) for v in x], dtype=np.uint16)
+    for sat, stag in ((0, "nosat"), (1, "satfinite")):
+        for mode, mtag in ((1, "rz"), (2, "rp")):
+            out[f"e8m0_from_f32_{stag}_{mtag}"] = np.array(
+                [R.ref_cvt_float_to_e8m0(float(v), sat, mode) for v in x], dtype=np.uint8)
+            out[f"e8m0_from_bf16_{stag}_{mtag}"] = np.array(
+                [R.ref_cvt_bfloat16raw_to_e8m0(h, sat, mode) for h in range(65536)], dtype=np.uint8)
+    out["e8m0_to_bf16"] = np.array([R.ref_cvt_e8m0_to_bf16raw(e) for e in range(256)], dtype=np.uint16)
+    rng = np.random.default_rng(12)
+    d = np.concatenate([rng.standard_normal(4000) * 10.0 ** rng.integers(-42, 40, size=4000),
+                        x[::11].astype(np.float64) * (1 + 2.0 ** -30),
+                        np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e300, -1e300, 1e-300, 1.00390625,
+                                  1.0039062500000002, 1.0039062499999998])])
+    out["f64_inputs"] = d
+    out["bf16_from_f64"] = np.array([R.ref_double2bfloat16(float(v)) for v in d], dtype=np.uint16)
     np.savez_compressed(os.path.join(HERE, "cast_reference.npz"), **out)
     print("wrote cast_reference.npz", bits.size, "probe inputs")
 

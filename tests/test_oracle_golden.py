@@ -163,3 +163,23 @@ def test_transpose_restatement():
     rec = np.zeros((3, 5), dtype=np.dtype([("i", np.int32), ("j", np.float32, (3, 2))], align=True))
     rec["i"] = rng.integers(0, 100, size=(3, 5))
     assert (oracle.transpose2d(rec) == rec.T).all()
+
+
+def test_directed_rounding_f64_and_e8m0_match_reference_headers(cast_gold):
+    x = cast_gold["f32_bits"].view(np.float32)
+    for mode, tag in ((oracle.RZ, "rz"), (oracle.RU, "ru"), (oracle.RD, "rd")):
+        assert (oracle.cast_ex(x, oracle.F32, oracle.BF16, mode=mode) == cast_gold[f"bf16_{tag}"]).all(), tag
+    h = np.arange(65536, dtype=np.uint16)
+    for sat, stag in ((0, "nosat"), (1, "satfinite")):
+        for mode, mtag in ((oracle.RZ, "rz"), (oracle.RU, "rp")):
+            assert (oracle.cast_ex(x, oracle.F32, oracle.E8M0, sat, mode) == cast_gold[f"e8m0_from_f32_{stag}_{mtag}"]).all()
+            assert (oracle.cast_ex(h, oracle.BF16, oracle.E8M0, sat, mode) == cast_gold[f"e8m0_from_bf16_{stag}_{mtag}"]).all()
+    assert (oracle.cast_ex(np.arange(256, dtype=np.uint8), oracle.E8M0, oracle.BF16) == cast_gold["e8m0_to_bf16"]).all()
+    assert (oracle.cast_ex(cast_gold["f64_inputs"], oracle.F64, oracle.BF16) == cast_gold["bf16_from_f64"]).all()
+    # known answers of tests/cudapy/test_fp8_bindings.py:449-560
+    L = oracle.lib()
+    assert L.oracle_e8m0_to_bf16(127) == 0x3F80
+    over = float(np.nextafter(np.float32(2.0 ** 127), np.float32(np.inf)))
+    assert L.oracle_f32_to_e8m0(over, 0, oracle.RU) == 0xFF and L.oracle_f32_to_e8m0(over, 1, oracle.RU) == 0xFE
+    half = L.oracle_e8m0_to_bf16(126)
+    assert L.oracle_bf16_to_e8m0(half, 0, oracle.RZ) == 126 and L.oracle_bf16_to_e8m0(half, 0, oracle.RU) == 126
