@@ -149,7 +149,7 @@ def config_dict(n_gpus):
                         "(default_rng(seed=1+rank).integers)",
             "elements_per_gpu": N_C2, "bytes_per_gpu": N_C2 * 4,
             "l2": "input (1 GiB) is larger than L2 (126 MB); no flush between steps",
-            "sharding": "contiguous shard per rank + one NCCL all-reduce(max) of one int32" if n_gpus > 1
+            "sharding": "contiguous shard per rank, partials combined once per step" if n_gpus > 1
             else "single GPU"}
 
 
@@ -244,10 +244,25 @@ def main():
         if rc:
             raise RuntimeError(L.b2k_last_error())
 
+    # N > 1: the combine runs inside the reduce kernel over NVLink peer memory (one
+    # launch per rank per step); B2K_BENCH_NCCL=1 selects kernel + NCCL all-reduce instead
+    boxes = None
+    if distributed and os.environ.get("B2K_BENCH_NCCL", "0") != "1":
+        try:
+            boxes = cuda.sharded.PeerMailboxes()
+        except Exception as exc:  # e.g. no peer access between the GPUs
+            if rank == 0:
+                print(f"peer mailboxes unavailable ({exc}); using NCCL", file=sys.stderr)
+            boxes = None
+    zero = np.array([0], dtype=np.int32)
+
     def step():
-        kernel_only()
-        if distributed:
-            dist.all_reduce(out, op=dist.ReduceOp.MAX)
+        if boxes is not None:
+            boxes.reduce(_lib.MAX, _lib.I32, x._ptr, N_C2, ident, out.data_ptr(), sptr)
+        else:
+            kernel_only()
+            if distributed:
+                dist.all_reduce(out, op=dist.ReduceOp.MAX)
 
     with ClockSampler(local_rank) as clocks:
         ms_step, launches = timed(step, args.steps, args.warmup)
@@ -260,12 +275,14 @@ def main():
     else:
         expect = expect_local
     assert int(out.item()) == expect, (int(out.item()), expect)
+    if boxes is not None:
+        boxes.check()
 
     # the kernel alone (roofline): same launches without the collective
     ms_kernel, _ = timed(kernel_only, args.steps, 3)
 
     # end to end through the public API: host shard -> device -> kernel -> host scalar
-    sharded_max = cuda.sharded.ShardedReduce(lambda a, b: max(a, b))
+    sharded_max = cuda.sharded.ShardedReduce(lambda a, b: max(a, b), peer=boxes)
     plain_max = cuda.reduce(lambda a, b: max(a, b))
 
     def e2e_step():
@@ -286,7 +303,10 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int32", "data": "synthetic",
-        "config": config_dict(world),
+        "config": dict(config_dict(world), combine=(
+            "single GPU" if not distributed else
+            "inside the reduce kernel: peer-memory mailboxes over NVLink (b2k_reduce_peer)" if boxes is not None
+            else "reduce kernel + one NCCL all-reduce(max) of one int32")),
         "clocks": clock_summary,
         "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": N_C2 * 4, "d2h_bytes_per_step": 4, "steps": e2e_steps,

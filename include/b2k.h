@@ -90,6 +90,35 @@ B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* Reduce + cross-GPU combine in ONE kernel per GPU (no counterpart in the
+ * reference, which has no distributed layer).  For an array sharded over up to
+ * b2k_peer_max_world() GPUs of one NVLink domain: every rank calls
+ * b2k_reduce_peer on its shard with the same `epoch` (1, 2, 3, ... per call of a
+ * communicator); the block that finishes the local fold stores the rank's value
+ * into a mailbox in every peer's memory, waits (at most timeout_ns, 0 = 2 s)
+ * for the peers' values of this epoch in its own mailbox, folds them in rank
+ * order, folds *init_host in and writes out_dev[0] -- the same result on every
+ * rank.  If a peer's value does not arrive in time, *status_dev is set to 1 and
+ * the kernel returns (no hang).
+ *   mailboxes : host array of `world` device pointers, entry r = rank r's mailbox
+ *               as visible from this process (own: from b2k_peer_mailbox_create;
+ *               others: b2k_peer_mailbox_open of the handle that rank exported).
+ * The mailbox helpers allocate/map b2k_peer_mailbox_bytes() bytes once per
+ * communicator; handles are b2k_peer_handle_bytes() bytes and travel between
+ * processes by any host channel. */
+B2K_API int64_t b2k_peer_mailbox_bytes(void);
+B2K_API int64_t b2k_peer_handle_bytes(void);
+B2K_API int b2k_peer_max_world(void);
+B2K_API int b2k_peer_mailbox_create(void **mailbox_dev);
+B2K_API int b2k_peer_mailbox_destroy(void *mailbox_dev);
+B2K_API int b2k_peer_mailbox_export(void *mailbox_dev, void *handle_out);
+B2K_API int b2k_peer_mailbox_open(const void *handle, void **peer_mailbox_dev);
+B2K_API int b2k_peer_mailbox_close(void *peer_mailbox_dev);
+B2K_API int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+                            void *out_dev, void *scratch_dev, int64_t scratch_bytes,
+                            void *const *mailboxes, int world, int rank, uint64_t epoch,
+                            uint64_t timeout_ns, int *status_dev, void *stream);
+
 /* The same reduction for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Meant for hosts whose device memory belongs to
  * someone else at the time of the call (a numba-cuda process running under an

@@ -31,6 +31,16 @@ SIGNATURES = {
     "b2k_reduce": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "b2k_reduce_noalloc_max_elements": (_i64, []),
     "b2k_reduce_noalloc": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp]),
+    "b2k_peer_mailbox_bytes": (_i64, []),
+    "b2k_peer_handle_bytes": (_i64, []),
+    "b2k_peer_max_world": (_i32, []),
+    "b2k_peer_mailbox_create": (_i32, [ctypes.POINTER(_vp)]),
+    "b2k_peer_mailbox_destroy": (_i32, [_vp]),
+    "b2k_peer_mailbox_export": (_i32, [_vp, _vp]),
+    "b2k_peer_mailbox_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "b2k_peer_mailbox_close": (_i32, [_vp]),
+    "b2k_reduce_peer": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, ctypes.POINTER(_vp), _i32, _i32,
+                               _u64, _u64, _vp, _vp]),
     "b2k_transpose2d": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
     "b2k_xoroshiro128p_tables_bytes": (_i64, []),
     "b2k_xoroshiro128p_build_tables": (_i32, [_vp, _i64, _vp]),

@@ -149,10 +149,103 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
     return r;
 }
 
-template <typename T, typename Op, int THREADS, int UNROLL>
+// ---- cross-GPU combine inside the kernel ------------------------------------------
+// When the array is sharded over several GPUs of one NVLink domain, the block that
+// finishes a GPU's local fold also does the exchange: it stores its value and then
+// a flag into a mailbox in every peer's memory (plain peer stores over NVLink),
+// waits until every peer's flag for this call has arrived in its own mailbox, and
+// folds the values in rank order.  No second launch and no library collective: the
+// cost is one NVLink round trip.  Flags carry the call's epoch and mailboxes are
+// double-buffered by epoch parity, so nothing is ever reset; a peer can be at most
+// one call ahead (it cannot finish call k+1 before this rank has published k+1).
+// The wait is bounded: when it runs out the block records an error status, writes
+// the identity-folded result and returns.
+constexpr int kMaxPeers = 16;
+constexpr int kMailboxWords = 2 * kMaxPeers * 2;  // [parity][writer]{value, flag}, 64-bit words
+
+struct PeerLink {
+    unsigned long long *mailbox[kMaxPeers];  // mailbox of every rank (own one included)
+    int world;
+    int rank;
+    unsigned long long epoch;               // same on every rank for one call; starts at 1
+    unsigned long long timeout_ns;
+    int *status;                             // set to 1 when a wait ran out
+};
+
+__device__ __forceinline__ void store_release_sys(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void store_relaxed_sys(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long load_relaxed_sys(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Runs in the last block of a GPU.  `local` is valid in thread 0.  Returns the fold
+// over all ranks (valid in thread 0).
+template <typename T, typename Op, int THREADS>
+__device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) {
+    __shared__ unsigned long long mine_bits;
+    __shared__ unsigned long long peer_bits[kMaxPeers];
+    __shared__ int all_arrived;
+    if (threadIdx.x == 0) {
+        unsigned long long b = 0;
+        memcpy(&b, &local, sizeof(T));
+        mine_bits = b;
+        all_arrived = 1;
+    }
+    __syncthreads();
+    const int slot_base = static_cast<int>(link.epoch & 1ull) * kMaxPeers;
+    if (threadIdx.x < link.world) {
+        const int p = threadIdx.x;
+        // publish to peer p: value first, then the flag that releases it
+        unsigned long long *theirs = link.mailbox[p] + 2 * (slot_base + link.rank);
+        store_relaxed_sys(theirs, mine_bits);
+        store_release_sys(theirs + 1, link.epoch);
+        // collect from peer p
+        const unsigned long long *here = link.mailbox[link.rank] + 2 * (slot_base + p);
+        const unsigned long long t0 = global_timer_ns();
+        bool arrived = true;
+        while (load_acquire_sys(here + 1) != link.epoch) {
+            if (global_timer_ns() - t0 > link.timeout_ns) { arrived = false; break; }
+            __nanosleep(100);
+        }
+        if (arrived) peer_bits[p] = load_relaxed_sys(here);
+        else atomicExch(&all_arrived, 0);
+    }
+    __syncthreads();
+    T result = Op::template identity<T>();
+    if (threadIdx.x == 0) {
+        if (all_arrived) {
+            for (int p = 0; p < link.world; ++p) {
+                T v;
+                memcpy(&v, &peer_bits[p], sizeof(T));
+                result = Op::template apply<T>(result, v);
+            }
+        } else {
+            *link.status = 1;
+        }
+    }
+    return result;
+}
+
+template <typename T, typename Op, int THREADS, int UNROLL, bool PEER>
 __global__ void __launch_bounds__(THREADS)
 reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
-                   T *partials, unsigned int *ticket) {
+              T *partials, unsigned int *ticket, const PeerLink link) {
     constexpr int VEC = 32 / sizeof(T);
     __shared__ T slots[THREADS / 32];
     __shared__ bool is_last;
@@ -210,12 +303,13 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
         mine = Op::template apply<T>(mine, __ldcg(partials + i));
     total = block_fold<T, Op, THREADS>(mine, slots);
+    if constexpr (PEER) total = exchange_with_peers<T, Op, THREADS>(total, link);
     if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
 }
 
 template <typename T, typename Op>
 int launch(const void *x, int64_t n, const void *init_host, void *out, void *scratch,
-           cudaStream_t stream) {
+           cudaStream_t stream, const PeerLink *link) {
     T init;
     memcpy(&init, init_host, sizeof(T));
     // two persistent CTAs per SM measured best on B200; short inputs get one CTA per chunk
@@ -228,8 +322,13 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
     if (grid > max_grid) grid = max_grid;
     auto *ticket = static_cast<unsigned int *>(scratch);
     auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
-    reduce_kernel<T, Op, kThreads, kUnroll><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-        static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket);
+    if (link) {
+        reduce_kernel<T, Op, kThreads, kUnroll, true><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket, *link);
+    } else {
+        reduce_kernel<T, Op, kThreads, kUnroll, false><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket, PeerLink{});
+    }
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_reduce launch");
     return B2K_OK;
@@ -237,19 +336,19 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
 
 template <typename T>
 int dispatch_op(int op, const void *x, int64_t n, const void *init_host, void *out,
-                void *scratch, cudaStream_t stream) {
+                void *scratch, cudaStream_t stream, const PeerLink *link) {
     switch (op) {
-    case B2K_ADD: return launch<T, OpAdd>(x, n, init_host, out, scratch, stream);
-    case B2K_MUL: return launch<T, OpMul>(x, n, init_host, out, scratch, stream);
-    case B2K_MAX: return launch<T, OpMax>(x, n, init_host, out, scratch, stream);
-    case B2K_MIN: return launch<T, OpMin>(x, n, init_host, out, scratch, stream);
+    case B2K_ADD: return launch<T, OpAdd>(x, n, init_host, out, scratch, stream, link);
+    case B2K_MUL: return launch<T, OpMul>(x, n, init_host, out, scratch, stream, link);
+    case B2K_MAX: return launch<T, OpMax>(x, n, init_host, out, scratch, stream, link);
+    case B2K_MIN: return launch<T, OpMin>(x, n, init_host, out, scratch, stream, link);
     default: break;
     }
     if constexpr (!(std::is_same<T, float>::value || std::is_same<T, double>::value)) {
         switch (op) {
-        case B2K_AND: return launch<T, OpAnd>(x, n, init_host, out, scratch, stream);
-        case B2K_OR: return launch<T, OpOr>(x, n, init_host, out, scratch, stream);
-        case B2K_XOR: return launch<T, OpXor>(x, n, init_host, out, scratch, stream);
+        case B2K_AND: return launch<T, OpAnd>(x, n, init_host, out, scratch, stream, link);
+        case B2K_OR: return launch<T, OpOr>(x, n, init_host, out, scratch, stream, link);
+        case B2K_XOR: return launch<T, OpXor>(x, n, init_host, out, scratch, stream, link);
         default: break;
         }
     }
@@ -272,8 +371,8 @@ extern "C" {
 
 int64_t b2k_reduce_scratch_bytes(void) { return kTicketBytes + 8 * static_cast<int64_t>(kMaxGrid); }
 
-int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
-               void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
+                       void *scratch_dev, int64_t scratch_bytes, void *stream, const PeerLink *link) {
     const size_t size = dtype_size(dtype);
     if (size == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown dtype %d", dtype);
     if (op < B2K_ADD || op > B2K_XOR) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown op %d", op);
@@ -289,17 +388,85 @@ int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init
         return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce: scratch must be 256-byte aligned");
     cudaStream_t s = b2k::as_stream(stream);
     switch (dtype) {
-    case B2K_I8: return dispatch_op<int8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_I16: return dispatch_op<int16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_I32: return dispatch_op<int32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_I64: return dispatch_op<int64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_U8: return dispatch_op<uint8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_U16: return dispatch_op<uint16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_U32: return dispatch_op<uint32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_U64: return dispatch_op<uint64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
-    default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s);
+    case B2K_I8: return dispatch_op<int8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_I16: return dispatch_op<int16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_I32: return dispatch_op<int32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_I64: return dispatch_op<int64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_U8: return dispatch_op<uint8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_U16: return dispatch_op<uint16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_U32: return dispatch_op<uint32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_U64: return dispatch_op<uint64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
     }
+}
+
+
+int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+               void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr);
+}
+
+// ---- mailboxes for the in-kernel cross-GPU combine -----------------------------------
+int64_t b2k_peer_mailbox_bytes(void) { return kMailboxWords * 8; }
+int b2k_peer_max_world(void) { return kMaxPeers; }
+int64_t b2k_peer_handle_bytes(void) { return static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)); }
+
+int b2k_peer_mailbox_create(void **mailbox_dev) {
+    if (!mailbox_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_peer_mailbox_create: null output");
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, kMailboxWords * 8);
+    if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_peer_mailbox_create: cudaMalloc");
+    e = cudaMemset(p, 0, kMailboxWords * 8);
+    if (e != cudaSuccess) { cudaFree(p); return b2k::check_cuda(e, "b2k_peer_mailbox_create: cudaMemset"); }
+    *mailbox_dev = p;
+    return B2K_OK;
+}
+int b2k_peer_mailbox_destroy(void *mailbox_dev) {
+    return b2k::check_cuda(cudaFree(mailbox_dev), "b2k_peer_mailbox_destroy");
+}
+int b2k_peer_mailbox_export(void *mailbox_dev, void *handle_out) {
+    if (!mailbox_dev || !handle_out) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_peer_mailbox_export: null pointer");
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, mailbox_dev);
+    if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_peer_mailbox_export: cudaIpcGetMemHandle");
+    memcpy(handle_out, &h, sizeof h);
+    return B2K_OK;
+}
+int b2k_peer_mailbox_open(const void *handle, void **peer_mailbox_dev) {
+    if (!handle || !peer_mailbox_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_peer_mailbox_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_peer_mailbox_open: cudaIpcOpenMemHandle");
+    *peer_mailbox_dev = p;
+    return B2K_OK;
+}
+int b2k_peer_mailbox_close(void *peer_mailbox_dev) {
+    return b2k::check_cuda(cudaIpcCloseMemHandle(peer_mailbox_dev), "b2k_peer_mailbox_close");
+}
+
+int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
+                    void *scratch_dev, int64_t scratch_bytes, void *const *mailboxes, int world, int rank,
+                    uint64_t epoch, uint64_t timeout_ns, int *status_dev, void *stream) {
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: world %d / rank %d out of range (at most %d ranks)",
+                         world, rank, kMaxPeers);
+    if (!mailboxes || !status_dev || epoch == 0)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: null mailboxes/status or epoch 0");
+    PeerLink link{};
+    for (int p = 0; p < world; ++p) {
+        if (!mailboxes[p] || !b2k::aligned_to<void>(mailboxes[p], 16))
+            return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: mailbox of rank %d missing or unaligned", p);
+        link.mailbox[p] = static_cast<unsigned long long *>(mailboxes[p]);
+    }
+    link.world = world;
+    link.rank = rank;
+    link.epoch = epoch;
+    link.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+    link.status = status_dev;
+    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, &link);
 }
 
 }  // extern "C"

@@ -114,18 +114,100 @@ def combine_partials(partial: torch.Tensor, op: int, dtype, group=None) -> torch
     return partial
 
 
+class PeerMailboxes:
+    """The mailboxes of one communicator for the in-kernel cross-GPU combine
+    (``b2k_reduce_peer``): this rank's own mailbox plus a mapping of every
+    peer's, exchanged as IPC handles over the process group at construction.
+    All ranks of the group must construct it together and must then call
+    ``reduce`` in the same order (the call counter is the epoch the kernels
+    match on).  Single node, at most ``b2k_peer_max_world()`` ranks."""
+
+    def __init__(self, group=None, world_size=None, rank=None, timeout_s: float = 2.0):
+        import ctypes
+        L = _lib.lib()
+        dist, world, my_rank = _world(group)
+        if world_size is not None:
+            world, my_rank = int(world_size), int(rank)
+        if world > L.b2k_peer_max_world():
+            raise ValueError(f"at most {L.b2k_peer_max_world()} ranks")
+        self.world, self.rank, self.group = world, my_rank, group
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        own = ctypes.c_void_p()
+        _lib.check(L.b2k_peer_mailbox_create(ctypes.byref(own)))
+        self._own = own.value
+        self._opened = []
+        ptrs = [None] * world
+        ptrs[my_rank] = self._own
+        if world > 1 and dist is not None:
+            handle = ctypes.create_string_buffer(int(L.b2k_peer_handle_bytes()))
+            _lib.check(L.b2k_peer_mailbox_export(self._own, handle))
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for r, h in enumerate(handles):
+                if r == my_rank:
+                    continue
+                peer = ctypes.c_void_p()
+                _lib.check(L.b2k_peer_mailbox_open(ctypes.create_string_buffer(h, len(h)), ctypes.byref(peer)))
+                ptrs[r] = peer.value
+                self._opened.append(peer.value)
+            dist.barrier(group=group)
+        self._ptrs = (ctypes.c_void_p * world)(*ptrs)
+        self._status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self._scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+
+    def reduce(self, op, dtype_code, x_ptr, n, init_host, out_ptr, stream=0):
+        """One collective call: launches the fused kernel on this rank."""
+        from .devicearray import stream_ptr
+        self.epoch += 1
+        _lib.check(_lib.lib().b2k_reduce_peer(
+            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, self._scratch.data_ptr(),
+            self._scratch.numel(), self._ptrs, self.world, self.rank, self.epoch, self.timeout_ns,
+            self._status.data_ptr(), stream_ptr(stream)))
+
+    def check(self):
+        """Raise if any earlier call gave up waiting for a peer (synchronises)."""
+        if int(self._status.item()) != 0:
+            self._status.zero_()
+            raise RuntimeError("a peer's partial result did not arrive within the time limit")
+
+    def close(self):
+        L = _lib.lib()
+        for p in self._opened:
+            L.b2k_peer_mailbox_close(p)
+        self._opened = []
+        if self._own:
+            L.b2k_peer_mailbox_destroy(self._own)
+            self._own = None
+
+
 class ShardedReduce:
     """``cuda.reduce`` over an array that is sharded by contiguous range across
     the ranks of a process group.  Call on every rank with the local shard; the
-    full result (with ``init`` folded in once) is returned on every rank."""
+    full result (with ``init`` folded in once) is returned on every rank.
 
-    def __init__(self, functor):
+    With ``peer=PeerMailboxes(...)`` the combine happens inside the reduce kernel
+    over NVLink peer memory (one launch per rank, no library collective);
+    without it, one NCCL collective on a one-element buffer follows the kernel."""
+
+    def __init__(self, functor, peer: "PeerMailboxes | None" = None):
         self._functor = functor
         self._local = Reduce(functor)
+        self._peer = peer
 
     def __call__(self, local_arr, init=0, stream=0, group=None):
-        from .api import device_array
+        from .api import auto_device, device_array
+        from .kernels.reduction import _DTYPE_CODES
         dtype = np.dtype(local_arr.dtype)
+        if self._peer is not None:
+            op = self._local._compile(dtype)
+            darr, _ = auto_device(local_arr, stream=stream)
+            slot = device_array(1, dtype=dtype, stream=stream)
+            init_host = np.array([init], dtype=dtype)
+            self._peer.reduce(op, _DTYPE_CODES[dtype], darr._ptr, darr.size, init_host, slot._ptr, stream)
+            result = slot.copy_to_host()[0]
+            self._peer.check()
+            return result
         op = classify_functor(self._functor, dtype) if local_arr.size else self._local._compile(dtype)
         ident = op_identity(op, dtype)
         slot = device_array(1, dtype=dtype, stream=stream)
@@ -163,5 +245,5 @@ def sharded_cast(src_local, src_format, dst_format, out=None, saturate=1, stream
     return cast(src_local, src_format, dst_format, out=out, saturate=saturate, stream=stream)
 
 
-__all__ = ["shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
+__all__ = ["PeerMailboxes", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
            "create_sharded_xoroshiro128p_states", "sharded_cast", "op_name"]

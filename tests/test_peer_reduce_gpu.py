@@ -1,0 +1,202 @@
+"""The reduce kernel's in-kernel cross-GPU combine (``b2k_reduce_peer``).
+
+On one GPU the exchange is exercised without ever making a kernel wait for
+another launch: a peer's mailbox is a second local buffer and the peer's value
+is written into this rank's mailbox *before* the kernel starts.  The give-up path
+is checked by letting a short wait run out on a flag that nothing sets (the
+kernel records a status and returns; the context stays usable).  With two or
+more GPUs, real ranks in separate processes run the fused path end to end."""
+import ctypes
+import os
+import socket
+import sys
+import traceback
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import numba_cuda_b200 as cuda
+from numba_cuda_b200 import _lib, sharded
+from numba_cuda_b200.devicearray import _ForeignBuffer
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+class Mailbox:
+    def __init__(self):
+        L = _lib.lib()
+        p = ctypes.c_void_p()
+        _lib.check(L.b2k_peer_mailbox_create(ctypes.byref(p)))
+        self.ptr = p.value
+        self.words = _ForeignBuffer(self.ptr, int(L.b2k_peer_mailbox_bytes()), self).tensor.view(torch.int64)
+
+    def slot(self, epoch, writer):
+        return 2 * ((epoch & 1) * _lib.lib().b2k_peer_max_world() + writer)
+
+    def close(self):
+        _lib.lib().b2k_peer_mailbox_destroy(self.ptr)
+
+
+def call_peer(op, code, x, init, boxes, world, rank, epoch, timeout_ns, status, scratch, out):
+    L = _lib.lib()
+    ptrs = (ctypes.c_void_p * world)(*[b.ptr for b in boxes])
+    rc = L.b2k_reduce_peer(op, code, x.data_ptr(), x.numel(), init.ctypes.data, out.data_ptr(), scratch.data_ptr(),
+                           scratch.numel(), ptrs, world, rank, epoch, timeout_ns, status.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.b2k_last_error()
+
+
+def test_world_of_one_equals_plain_reduce():
+    L = _lib.lib()
+    box = Mailbox()
+    scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = torch.randint(-2 ** 31, 2 ** 31 - 1, (1 << 20,), dtype=torch.int32, device="cuda")
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    init = np.array([-5], dtype=np.int32)
+    for epoch in (1, 2, 3):
+        call_peer(_lib.MAX, _lib.I32, x, init, [box], 1, 0, epoch, 0, status, scratch, out)
+        assert out.item() == max(int(x.max().item()), -5) and status.item() == 0
+    box.close()
+
+
+@pytest.mark.parametrize("op,code,tdt,name", [(_lib.MAX, _lib.I32, torch.int32, "max"),
+                                              (_lib.ADD, _lib.F64, torch.float64, "add"),
+                                              (_lib.ADD, _lib.I8, torch.int8, "add"),
+                                              (_lib.MIN, _lib.F32, torch.float32, "min")])
+def test_fold_with_a_value_that_already_arrived(op, code, tdt, name):
+    L = _lib.lib()
+    mine, theirs = Mailbox(), Mailbox()         # rank 0's mailbox, and a stand-in for rank 1's memory
+    scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ndt = np.dtype(str(tdt).replace("torch.", ""))
+    if tdt.is_floating_point:
+        x = torch.rand(100003, dtype=tdt, device="cuda")
+    else:
+        info = torch.iinfo(tdt)
+        x = torch.randint(info.min, info.max, (100003,), dtype=tdt, device="cuda")
+    out = torch.zeros(1, dtype=tdt, device="cuda")
+    init = np.array([3], dtype=ndt)
+    peer_value = np.array([7], dtype=ndt)
+    for epoch in (1, 2, 3, 4):                  # both parities, reuse without any reset
+        bits = np.zeros(1, dtype=np.int64)
+        bits.view(np.uint8)[: ndt.itemsize] = peer_value.view(np.uint8)
+        s = mine.slot(epoch, 1)
+        mine.words[s] = int(bits[0])
+        mine.words[s + 1] = epoch
+        torch.cuda.synchronize()
+        call_peer(op, code, x, init, [mine, theirs], 2, 0, epoch, 0, status, scratch, out)
+        local = oracle.fold(x.cpu().numpy(), name, sharded.op_identity(op, ndt))
+        want = sharded.host_fold(op, np.array([local, peer_value[0]], dtype=ndt), init[0])
+        got = out.cpu().numpy()[0]
+        if ndt.kind == "f" and name == "add":
+            assert abs(got - want) <= (1e-12 if ndt == np.float64 else 1e-5) * abs(want)
+        else:
+            assert got == want
+        assert status.item() == 0
+        # this rank published its own value and flag into the peer's mailbox
+        t = theirs.slot(epoch, 0)
+        assert int(theirs.words[t + 1].item()) == epoch
+        pub = np.array([int(theirs.words[t].item())], dtype=np.int64).view(np.uint8)[: ndt.itemsize].view(ndt)[0]
+        assert pub == local or (ndt.kind == "f" and abs(pub - local) <= 1e-5 * abs(local))
+    mine.close(); theirs.close()
+
+
+def test_wait_that_runs_out_sets_status_and_returns():
+    L = _lib.lib()
+    mine, theirs = Mailbox(), Mailbox()
+    scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = torch.ones(1000, dtype=torch.int32, device="cuda")
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    init = np.array([0], dtype=np.int32)
+    # nothing ever sets rank 1's flag: the wait gives up after 2 ms
+    call_peer(_lib.ADD, _lib.I32, x, init, [mine, theirs], 2, 0, 1, 2_000_000, status, scratch, out)
+    torch.cuda.synchronize()
+    assert status.item() == 1
+    # the context is intact and the scratch reusable
+    status.zero_()
+    plain = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert L.b2k_reduce(_lib.ADD, _lib.I32, x.data_ptr(), x.numel(), init.ctypes.data, plain.data_ptr(),
+                        scratch.data_ptr(), scratch.numel(), torch.cuda.current_stream().cuda_stream) == 0
+    assert plain.item() == 1000
+    mine.close(); theirs.close()
+
+
+def test_argument_checks():
+    L = _lib.lib()
+    init = np.zeros(1, dtype=np.int32)
+    ptrs = (ctypes.c_void_p * 1)(4096)
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 0, 0, 1, 0,
+                             4096, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 0, 0,
+                             4096, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 17, 0, 1, 0,
+                             4096, None) == _lib.ERR_INVALID_ARG
+
+
+# ---- real ranks on separate GPUs ---------------------------------------------------
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, errors):
+    try:
+        sys.path.insert(0, ROOT)
+        import torch.distributed as dist
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        boxes = sharded.PeerMailboxes()
+        cases = [("max", lambda a, b: max(a, b), np.int32, 0), ("add", lambda a, b: a + b, np.float64, 2.5),
+                 ("add", lambda a, b: a + b, np.int64, -7), ("min", lambda a, b: min(a, b), np.float32, 1e30),
+                 ("xor", lambda a, b: a ^ b, np.uint16, 0)]
+        for round_no in range(3):
+            for name, fn, dt, init in cases:
+                n = 1 << 20
+                rng = np.random.default_rng(100 + round_no)
+                if np.dtype(dt).kind == "f":
+                    whole = rng.standard_normal(n).astype(dt)
+                else:
+                    info = np.iinfo(dt)
+                    whole = rng.integers(info.min, info.max, size=n, dtype=dt, endpoint=True)
+                lo, hi = sharded.shard_bounds(n, world, rank)
+                fused = sharded.ShardedReduce(fn, peer=boxes)(whole[lo:hi], init=init)
+                nccl = sharded.ShardedReduce(fn)(whole[lo:hi], init=init)
+                want = oracle.fold(whole, name, init)
+                if np.dtype(dt).kind == "f" and name == "add":
+                    assert abs(fused - want) <= 1e-12 * np.abs(whole).sum(), (name, dt, fused, want)
+                    assert abs(nccl - want) <= 1e-12 * np.abs(whole).sum()
+                else:
+                    assert fused == want == nccl, (name, dt, fused, nccl, want)
+        dist.barrier()
+        boxes.close()
+        dist.destroy_process_group()
+    except Exception:
+        errors.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_combine_across_real_ranks():
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    errors = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, errors)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank did not finish")
+    if not errors.empty():
+        rank, tb = errors.get()
+        pytest.fail(f"rank {rank} failed:\n{tb}")
+    assert all(p.exitcode == 0 for p in procs)
