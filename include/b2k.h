@@ -90,6 +90,21 @@ B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* cuda.reduce with an arbitrary user function.  `expr` is a C++ expression over
+ * the operands `a` and `b` (the Python layer obtains it by tracing the user's
+ * function); the reduce kernel is compiled around it at run time with NVRTC for
+ * sm_100a and cached per (device, dtype, expression).  Replaces the reference's
+ * JIT compilation of the functor (numba/cuda/kernels/reduction.py:15-21, :185-192).
+ * Integer operands are widened to 64 bits inside the expression and truncated on
+ * store, float32 literals-with-integers promote to double, as numba types them.
+ * Helpers available to the expression: b2k_floordiv, b2k_mod (Python semantics),
+ * b2k_truediv, b2k_abs, B2K_ILIT(integer literal), B2K_INF, B2K_NAN.
+ * n must be >= 1 (the caller returns init for an empty array).  The op must be
+ * associative and commutative, as the reference requires. */
+B2K_API int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int64_t n,
+                            const void *init_host, void *out_dev, void *scratch_dev,
+                            int64_t scratch_bytes, void *stream);
+
 /* Reduce + cross-GPU combine in ONE kernel per GPU (no counterpart in the
  * reference, which has no distributed layer).  For an array sharded over up to
  * b2k_peer_max_world() GPUs of one NVLink domain: every rank calls

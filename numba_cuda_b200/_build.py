@@ -19,6 +19,7 @@ LIB = os.path.join(CSRC, "libb2k.so")
 SOURCES = [
     "b2k_api.cu",
     "b2k_reduce.cu",
+    "b2k_reduce_user.cu",
     "b2k_cast.cu",
     "b2k_xoroshiro.cu",
     "b2k_transpose.cu",
@@ -82,7 +83,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 raise RuntimeError(f"nvcc failed on {name}")
     objs = [os.path.join(objdir, n[:-3] + ".o") for n in SOURCES]
     if force or jobs or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-cudart", "static"]
+        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-cudart", "static", "-ldl"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             sys.stderr.write(p.stdout + p.stderr)

@@ -29,6 +29,7 @@ SIGNATURES = {
     "b2k_launch_count": (_i64, []),
     "b2k_reduce_scratch_bytes": (_i64, []),
     "b2k_reduce": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "b2k_reduce_expr": (_i32, [ctypes.c_char_p, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "b2k_reduce_noalloc_max_elements": (_i64, []),
     "b2k_reduce_noalloc": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp]),
     "b2k_peer_mailbox_bytes": (_i64, []),

@@ -1,0 +1,356 @@
+// cuda.reduce with an arbitrary user expression: the reduce kernel is specialised
+// at run time.  The reference compiles the user's Python function into its kernel
+// with its JIT (numba/cuda/kernels/reduction.py:15-166); here the Python layer
+// traces the function into a C++ expression over `a` and `b`, and this file
+// compiles the kernel below around it with NVRTC for sm_100a (libnvrtc is loaded
+// on first use; without it the call fails -- nothing falls back to the CPU).
+//
+// An arbitrary op has no known identity element, so the kernel carries a
+// "has a value" flag next to every partial instead of seeding accumulators.
+// Every block owns one contiguous span of 16-byte vectors (at least one), so all
+// block partials are valid; the last block (ticket) folds them in index order and
+// folds `init` in, like the table-op kernel.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "b2k_internal.cuh"
+
+namespace {
+
+const char *kKernelSource = R"b2ksrc(
+typedef B2K_T T;
+typedef B2K_W W;
+#define B2K_INF (__longlong_as_double(0x7ff0000000000000LL))
+#define B2K_NAN (__longlong_as_double(0x7ff8000000000000LL))
+
+__device__ __forceinline__ long long fdiv_(long long a, long long b) {
+    if (b == 0) return 0;
+    long long q = a / b;
+    if ((a % b != 0) && ((a < 0) != (b < 0))) --q;
+    return q;
+}
+__device__ __forceinline__ unsigned long long fdiv_(unsigned long long a, unsigned long long b) { return b == 0 ? 0 : a / b; }
+__device__ __forceinline__ double fdiv_(double a, double b) { return floor(a / b); }
+__device__ __forceinline__ float fdiv_(float a, float b) { return floorf(a / b); }
+__device__ __forceinline__ long long mod_(long long a, long long b) {
+    if (b == 0) return 0;
+    long long r = a % b;
+    if (r != 0 && ((r < 0) != (b < 0))) r += b;
+    return r;
+}
+__device__ __forceinline__ unsigned long long mod_(unsigned long long a, unsigned long long b) { return b == 0 ? 0 : a % b; }
+__device__ __forceinline__ double mod_(double a, double b) {
+    double r = fmod(a, b);
+    if (r != 0.0 && ((r < 0.0) != (b < 0.0))) r += b;
+    return r;
+}
+__device__ __forceinline__ float mod_(float a, float b) {
+    float r = fmodf(a, b);
+    if (r != 0.0f && ((r < 0.0f) != (b < 0.0f))) r += b;
+    return r;
+}
+__device__ __forceinline__ double tdiv_(double a, double b) { return a / b; }
+__device__ __forceinline__ float tdiv_(float a, float b) { return a / b; }
+__device__ __forceinline__ double tdiv_(long long a, long long b) { return (double)a / (double)b; }
+__device__ __forceinline__ double tdiv_(unsigned long long a, unsigned long long b) { return (double)a / (double)b; }
+// operands of different types meet in their common arithmetic type first
+template <class A, class B> __device__ __forceinline__ auto b2k_floordiv(A a, B b) { typedef decltype(a + b) C; return fdiv_((C)a, (C)b); }
+template <class A, class B> __device__ __forceinline__ auto b2k_mod(A a, B b) { typedef decltype(a + b) C; return mod_((C)a, (C)b); }
+template <class A, class B> __device__ __forceinline__ auto b2k_truediv(A a, B b) { typedef decltype(a + b) C; return tdiv_((C)a, (C)b); }
+__device__ __forceinline__ long long b2k_abs(long long a) { return a < 0 ? -a : a; }
+__device__ __forceinline__ unsigned long long b2k_abs(unsigned long long a) { return a; }
+__device__ __forceinline__ double b2k_abs(double a) { return fabs(a); }
+__device__ __forceinline__ float b2k_abs(float a) { return fabsf(a); }
+
+__device__ __forceinline__ T user_op(T a_, T b_) {
+    const W a = (W)a_;
+    const W b = (W)b_;
+    return (T)(B2K_EXPR);
+}
+
+#define THREADS 512
+#define VEC (16 / (int)sizeof(T))
+
+struct Partial { T v; bool has; };
+
+__device__ __forceinline__ void fold(Partial &p, T x) {
+    p.v = p.has ? user_op(p.v, x) : x;
+    p.has = true;
+}
+__device__ __forceinline__ void join(Partial &p, const Partial &q) {
+    if (q.has) fold(p, q.v);
+}
+__device__ __forceinline__ Partial shuffle_xor(const Partial &p, int mask) {
+    unsigned long long bits = 0;
+    memcpy(&bits, &p.v, sizeof(T));
+    bits = __shfl_xor_sync(0xffffffffu, bits, mask);
+    Partial q;
+    memcpy(&q.v, &bits, sizeof(T));
+    q.has = __shfl_xor_sync(0xffffffffu, (int)p.has, mask) != 0;
+    return q;
+}
+// the lane with the lower index keeps the left operand, so the fold stays in index order
+__device__ __forceinline__ Partial block_fold(Partial p, Partial *slots) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int m = 1; m < 32; m <<= 1) {
+        const Partial q = shuffle_xor(p, m);
+        if ((lane & m) == 0) join(p, q);
+        else { Partial r = q; join(r, p); p = r; }
+    }
+    if (lane == 0) slots[warp] = p;
+    __syncthreads();
+    if (warp == 0) {
+        p = (lane < THREADS / 32) ? slots[lane] : Partial{T(), false};
+        for (int m = 1; m < 32; m <<= 1) {
+            const Partial q = shuffle_xor(p, m);
+            if ((lane & m) == 0) join(p, q);
+            else { Partial r = q; join(r, p); p = r; }
+        }
+    }
+    __syncthreads();
+    return p;
+}
+
+extern "C" __global__ void __launch_bounds__(THREADS)
+b2k_user_reduce(const T *__restrict__ x, long long n, T init, T *__restrict__ out, T *partials,
+                unsigned int *ticket, long long per /* vectors per block; no block is empty */) {
+    __shared__ Partial slots[THREADS / 32];
+    __shared__ bool is_last;
+
+    const unsigned long long addr = (unsigned long long)x;
+    long long head = (long long)(((16u - (addr & 15u)) & 15u) / sizeof(T));
+    if (head > n) head = n;
+    const uint4 *xv = (const uint4 *)(x + head);
+    const long long nvec = (n - head) / VEC;
+    const long long tail_begin = head + nvec * VEC;
+    // contiguous span of vectors for this block
+    const long long vlo = (long long)blockIdx.x * per;
+    long long vhi = vlo + per;
+    if (vhi > nvec) vhi = nvec;
+
+    Partial acc{T(), false};
+    if (blockIdx.x == 0 && threadIdx.x < head) fold(acc, x[threadIdx.x]);
+#pragma unroll 4
+    for (long long v = vlo + threadIdx.x; v < vhi; v += THREADS) {
+        const uint4 raw = __ldg(xv + v);
+        union { uint4 q; T e[VEC]; } u;
+        u.q = raw;
+        T t = u.e[0];   // fold the vector on its own first: one flag test per vector
+#pragma unroll
+        for (int k = 1; k < VEC; ++k) t = user_op(t, u.e[k]);
+        fold(acc, t);
+    }
+    if (blockIdx.x == gridDim.x - 1) {
+        const long long t = tail_begin + threadIdx.x;
+        if (t < n) fold(acc, x[t]);
+    }
+    Partial total = block_fold(acc, slots);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = total.v;   // every block owns at least one element
+        __threadfence();
+        const unsigned int t = atomicInc(ticket, gridDim.x - 1);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    Partial mine{T(), false};
+    // contiguous slices per thread keep the fold in block order
+    const unsigned int g = gridDim.x;
+    const unsigned int each = (g + THREADS - 1) / THREADS;
+    for (unsigned int i = threadIdx.x * each; i < g && i < (threadIdx.x + 1) * each; ++i)
+        fold(mine, __ldcg(partials + i));
+    total = block_fold(mine, slots);
+    if (threadIdx.x == 0) out[0] = user_op(total.v, init);
+}
+)b2ksrc";
+
+// ---- NVRTC, loaded on first use ---------------------------------------------------
+struct Nvrtc {
+    void *lib = nullptr;
+    decltype(&nvrtcCreateProgram) create = nullptr;
+    decltype(&nvrtcCompileProgram) compile = nullptr;
+    decltype(&nvrtcGetCUBINSize) cubin_size = nullptr;
+    decltype(&nvrtcGetCUBIN) cubin = nullptr;
+    decltype(&nvrtcGetProgramLogSize) log_size = nullptr;
+    decltype(&nvrtcGetProgramLog) log = nullptr;
+    decltype(&nvrtcDestroyProgram) destroy = nullptr;
+    bool ok = false;
+};
+
+Nvrtc &nvrtc() {
+    static Nvrtc n;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char *names[] = {getenv("B2K_NVRTC_PATH"), "libnvrtc.so.12", "libnvrtc.so",
+                               "/usr/local/cuda/lib64/libnvrtc.so.12"};
+        for (const char *name : names) {
+            if (!name || !*name) continue;
+            n.lib = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+            if (n.lib) break;
+        }
+        if (!n.lib) return;
+#define B2K_SYM(field, sym) n.field = reinterpret_cast<decltype(n.field)>(dlsym(n.lib, sym))
+        B2K_SYM(create, "nvrtcCreateProgram");
+        B2K_SYM(compile, "nvrtcCompileProgram");
+        B2K_SYM(cubin_size, "nvrtcGetCUBINSize");
+        B2K_SYM(cubin, "nvrtcGetCUBIN");
+        B2K_SYM(log_size, "nvrtcGetProgramLogSize");
+        B2K_SYM(log, "nvrtcGetProgramLog");
+        B2K_SYM(destroy, "nvrtcDestroyProgram");
+#undef B2K_SYM
+        n.ok = n.create && n.compile && n.cubin_size && n.cubin && n.log_size && n.log && n.destroy;
+    });
+    return n;
+}
+
+struct Driver {
+    CUresult (*module_load)(CUmodule *, const void *) = nullptr;
+    CUresult (*get_function)(CUfunction *, CUmodule, const char *) = nullptr;
+    CUresult (*launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                       void **, void **) = nullptr;
+    bool ok = false;
+};
+
+Driver &driver() {
+    static Driver d;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        auto get = [](const char *name) -> void * {
+            void *p = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+                return nullptr;
+            return p;
+        };
+        d.module_load = reinterpret_cast<decltype(d.module_load)>(get("cuModuleLoadData"));
+        d.get_function = reinterpret_cast<decltype(d.get_function)>(get("cuModuleGetFunction"));
+        d.launch = reinterpret_cast<decltype(d.launch)>(get("cuLaunchKernel"));
+        d.ok = d.module_load && d.get_function && d.launch;
+    });
+    return d;
+}
+
+struct TypeInfo { const char *t; const char *w; const char *ilit; size_t size; };
+
+bool type_info(int dtype, TypeInfo *out) {
+    switch (dtype) {
+    case B2K_I8: *out = {"signed char", "long long", "((long long)(x))", 1}; return true;
+    case B2K_I16: *out = {"short", "long long", "((long long)(x))", 2}; return true;
+    case B2K_I32: *out = {"int", "long long", "((long long)(x))", 4}; return true;
+    case B2K_I64: *out = {"long long", "long long", "((long long)(x))", 8}; return true;
+    case B2K_U8: *out = {"unsigned char", "long long", "((long long)(x))", 1}; return true;
+    case B2K_U16: *out = {"unsigned short", "long long", "((long long)(x))", 2}; return true;
+    case B2K_U32: *out = {"unsigned int", "long long", "((long long)(x))", 4}; return true;
+    case B2K_U64: *out = {"unsigned long long", "unsigned long long", "((unsigned long long)(x))", 8}; return true;
+    case B2K_F32: *out = {"float", "float", "((double)(x))", 4}; return true;
+    case B2K_F64: *out = {"double", "double", "((double)(x))", 8}; return true;
+    default: return false;
+    }
+}
+
+std::mutex g_cache_mutex;
+std::map<std::string, CUfunction> g_cache;  // key: device / dtype / expression
+
+int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, CUfunction *fn) {
+    Nvrtc &rt = nvrtc();
+    if (!rt.ok) return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: libnvrtc could not be loaded");
+    Driver &drv = driver();
+    if (!drv.ok) return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: driver entry points unavailable");
+    cudaFree(nullptr);  // make sure the primary context exists before loading a module
+    nvrtcProgram prog;
+    if (rt.create(&prog, kKernelSource, "b2k_user_reduce.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: nvrtcCreateProgram failed");
+    const std::string dt = std::string("-DB2K_T=") + ti.t;
+    const std::string dw = std::string("-DB2K_W=") + ti.w;
+    const std::string dl = std::string("-DB2K_ILIT(x)=") + ti.ilit;
+    const std::string de = "-DB2K_EXPR=" + expr;
+    const char *opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-default-device", dt.c_str(), dw.c_str(),
+                          dl.c_str(), de.c_str()};
+    const nvrtcResult rc = rt.compile(prog, 7, opts);
+    if (rc != NVRTC_SUCCESS) {
+        size_t len = 0;
+        rt.log_size(prog, &len);
+        std::string log(len, '\0');
+        if (len) rt.log(prog, &log[0]);
+        rt.destroy(&prog);
+        if (log.size() > 380) log.resize(380);
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: the expression does not compile: %s", log.c_str());
+    }
+    size_t size = 0;
+    rt.cubin_size(prog, &size);
+    std::vector<char> image(size);
+    rt.cubin(prog, image.data());
+    rt.destroy(&prog);
+    CUmodule mod;
+    if (drv.module_load(&mod, image.data()) != CUDA_SUCCESS)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: cuModuleLoadData failed");
+    if (drv.get_function(fn, mod, "b2k_user_reduce") != CUDA_SUCCESS)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: kernel not found in the compiled module");
+    (void)dtype;
+    return B2K_OK;
+}
+
+}  // namespace
+
+extern "C" int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int64_t n, const void *init_host,
+                               void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    TypeInfo ti;
+    if (!type_info(dtype, &ti)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: unknown dtype %d", dtype);
+    if (!expr || !*expr) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: empty expression");
+    if (n < 1) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: needs at least one element");
+    if (!x_dev || !init_host || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: null pointer");
+    if (!scratch_dev || scratch_bytes < b2k_reduce_scratch_bytes() || !b2k::aligned_to<void>(scratch_dev, 256))
+        return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_expr: scratch of %lld bytes (256-byte aligned) required",
+                         (long long)b2k_reduce_scratch_bytes());
+    if (!b2k::aligned_to<void>(x_dev, ti.size) || !b2k::aligned_to<void>(out_dev, ti.size))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_expr: pointers must be aligned to the element size");
+
+    int device = 0;
+    cudaGetDevice(&device);
+    const std::string key = std::to_string(device) + "/" + std::to_string(dtype) + "/" + expr;
+    CUfunction fn = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_cache_mutex);
+        auto it = g_cache.find(key);
+        if (it == g_cache.end()) {
+            const int rc = compile_kernel(expr, dtype, ti, &fn);
+            if (rc != B2K_OK) return rc;
+            g_cache.emplace(key, fn);
+        } else {
+            fn = it->second;
+        }
+    }
+    // one contiguous span of vectors per block, at least one vector each
+    const int64_t vec = 16 / static_cast<int64_t>(ti.size);
+    const int64_t nvec = n / vec;
+    // the head (elements before the first 16-byte boundary) shortens the vector count by at most one
+    const int64_t head = ((16 - (reinterpret_cast<uintptr_t>(x_dev) & 15)) & 15) / static_cast<int64_t>(ti.size);
+    const int64_t nvec_dev = (n - (head < n ? head : n)) / vec;
+    int64_t grid = nvec_dev / (512 * 8);
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * 4;
+    if (grid > cap) grid = cap;
+    if (grid < 1) grid = 1;
+    long long per = (nvec_dev + grid - 1) / grid;
+    if (per > 0) grid = (nvec_dev + per - 1) / per;   // every block gets at least one vector
+    if (grid < 1) grid = 1;
+    (void)nvec;
+    unsigned long long init_bits = 0;
+    memcpy(&init_bits, init_host, ti.size);
+    long long n_arg = n;
+    void *ticket = scratch_dev;
+    void *partials = static_cast<char *>(scratch_dev) + 256;
+    void *args[] = {const_cast<void **>(&x_dev), &n_arg, &init_bits, &out_dev, &partials, &ticket, &per};
+    const CUresult rc = driver().launch(fn, static_cast<unsigned>(grid), 1, 1, 512, 1, 1, 0,
+                                        reinterpret_cast<CUstream>(stream), args, nullptr);
+    b2k::note_launch();
+    if (rc != CUDA_SUCCESS) return b2k::fail(static_cast<int>(cudaErrorLaunchFailure), "b2k_reduce_expr: cuLaunchKernel failed (%d)", (int)rc);
+    return B2K_OK;
+}

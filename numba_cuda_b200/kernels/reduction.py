@@ -5,11 +5,13 @@ Same call surface as numba/cuda/kernels/reduction.py:169-265:
 ``Reduce(functor)(arr, size=None, res=None, init=0, stream=0)``.
 
 The reference JIT-compiles the Python functor into its kernel.  Here the
-functor is *classified* into the table of ops the precompiled kernels carry
-(add, mul, max, min, and, or, xor): it is evaluated on a fixed set of sample
-pairs and must agree with exactly one table op on all of them.  A functor that
-matches none raises ``NotImplementedError`` -- nothing is ever computed on the
-CPU instead.
+functor is first *classified* into the table of ops the precompiled kernels
+carry (add, mul, max, min, and, or, xor): it is evaluated on a fixed set of
+sample pairs and must agree with exactly one table op on all of them.  Any other
+functor is traced into a C++ expression (``_trace.py``) and the reduce kernel is
+compiled around it at run time with NVRTC (``b2k_reduce_expr``).  A functor that
+cannot be traced raises ``NotImplementedError`` -- nothing is ever computed on
+the CPU instead.
 """
 from __future__ import annotations
 
@@ -90,8 +92,7 @@ def classify_functor(functor, dtype) -> int:
         return matches[0]
     raise NotImplementedError(
         "cuda.reduce: the binary function is not one of the precompiled ops "
-        "(a+b, a*b, max(a,b), min(a,b), a&b, a|b, a^b); arbitrary functors are not supported "
-        "and there is no CPU fallback")
+        "(a+b, a*b, max(a,b), min(a,b), a&b, a|b, a^b)")
 
 
 class _Scratch:
@@ -128,10 +129,28 @@ class Reduce:
         self._functor = functor
 
     def _compile(self, dtype):
+        """Table op code for ``(functor, dtype)``, or a C++ expression string when the
+        functor is not a table op (it is then compiled into the kernel at run time)."""
         key = self._functor, np.dtype(dtype)
         op = self._cache.get(key)
         if op is None:
-            op = classify_functor(self._functor, dtype)
+            from ._trace import trace_functor
+            try:
+                op = classify_functor(self._functor, dtype)
+            except NotImplementedError:
+                if np.dtype(dtype) not in _DTYPE_CODES:
+                    raise
+                op = trace_functor(self._functor)
+            else:
+                # The probe only sees moderate magnitudes.  A functor that carries any
+                # constant (a cap, a modulus, a threshold) is never a pure table op, so
+                # it takes the traced path even when it agreed on every sample.
+                try:
+                    expr = trace_functor(self._functor)
+                except NotImplementedError:
+                    expr = None
+                if expr is not None and any(ch.isdigit() for ch in expr):
+                    op = expr
             self._cache[key] = op
         return op
 
@@ -169,9 +188,14 @@ class Reduce:
             out_ptr = slot.data_ptr()
 
         init_host = np.array([init], dtype=arr.dtype)
-        _lib.check(_lib.lib().b2k_reduce(
-            op, _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
-            out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
+        if isinstance(op, str):
+            _lib.check(_lib.lib().b2k_reduce_expr(
+                op.encode(), _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
+                out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
+        else:
+            _lib.check(_lib.lib().b2k_reduce(
+                op, _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
+                out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
         if res is not None:
             return None
         host = np.empty(1, dtype=arr.dtype)

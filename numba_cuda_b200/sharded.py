@@ -201,6 +201,8 @@ class ShardedReduce:
         dtype = np.dtype(local_arr.dtype)
         if self._peer is not None:
             op = self._local._compile(dtype)
+            if isinstance(op, str):
+                raise NotImplementedError("the fused cross-GPU combine supports the precompiled table ops only")
             darr, _ = auto_device(local_arr, stream=stream)
             slot = device_array(1, dtype=dtype, stream=stream)
             init_host = np.array([init], dtype=dtype)
@@ -208,7 +210,9 @@ class ShardedReduce:
             result = slot.copy_to_host()[0]
             self._peer.check()
             return result
-        op = classify_functor(self._functor, dtype) if local_arr.size else self._local._compile(dtype)
+        op = self._local._compile(dtype)
+        if isinstance(op, str):
+            raise NotImplementedError("sharded reduce supports the precompiled table ops only")
         ident = op_identity(op, dtype)
         slot = device_array(1, dtype=dtype, stream=stream)
         if local_arr.size:

@@ -36,6 +36,43 @@ def test_classify_rejects_what_it_cannot_run():
         classify_functor(lambda a, b: a + b, np.complex128)
 
 
+def test_functors_with_constants_take_the_traced_path():
+    # agrees with a+b on every probe sample, but is not a+b
+    def capped(a, b):
+        s = a + b
+        if s > 100000:
+            return 100000
+        return s
+    assert classify_functor(capped, np.int32) == _lib.ADD          # what the probe alone would say
+    op = Reduce(capped)._compile(np.dtype(np.int32))
+    assert isinstance(op, str) and "100000" in op
+    assert Reduce(lambda a, b: a + b)._compile(np.dtype(np.int32)) == _lib.ADD
+    assert Reduce(lambda a, b: max(a, b))._compile(np.dtype(np.float64)) == _lib.MAX
+    assert isinstance(Reduce(lambda a, b: (a + b) % 7)._compile(np.dtype(np.int64)), str)
+    import math
+    with pytest.raises(NotImplementedError):
+        Reduce(lambda a, b: math.sqrt(a) + b)._compile(np.dtype(np.float64))
+
+
+def test_tracer_follows_branches_and_numba_typing():
+    from numba_cuda_b200.kernels._trace import trace_functor
+    assert trace_functor(lambda a, b: a + b) == "(a + b)"
+    assert trace_functor(lambda a, b: max(a, b)) == "((b > a) ? b : a)"
+    assert trace_functor(lambda a, b: a // b) == "b2k_floordiv(a, b)"
+    assert trace_functor(lambda a, b: a * 1.5 + b) == "((a * 1.5) + b)"
+    assert trace_functor(lambda a, b: 3) == "B2K_ILIT(3LL)"
+
+    def three_way(a, b):
+        if a > b:
+            return a - b
+        elif a == b:
+            return 0
+        return b - a
+    assert trace_functor(three_way) == "((a > b) ? (a - b) : ((a == b) ? B2K_ILIT(0LL) : (b - a)))"
+    with pytest.raises(NotImplementedError):
+        trace_functor(lambda a, b: [a, b][a])
+
+
 def test_reduce_argument_checks_come_first():
     # reduction.py:217-228: ndim check, then empty -> init, all before any device work
     r = Reduce(lambda a, b: a + b)

@@ -189,6 +189,9 @@ def test_stream_argument_and_raw_c_abi():
     assert int(scratch[:4].view(torch.int32).item()) == 0
 
 
-def test_unsupported_functor_raises():
+def test_untraceable_functor_raises():
+    import math
     with pytest.raises(NotImplementedError):
-        cuda.reduce(lambda a, b: a - b)(np.arange(10.0))
+        cuda.reduce(lambda a, b: math.sqrt(a) + b)(np.arange(10.0))
+    with pytest.raises(NotImplementedError):
+        cuda.reduce(lambda a, b: a + b)(np.arange(10.0).astype(np.complex128))
