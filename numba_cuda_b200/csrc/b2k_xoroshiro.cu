@@ -227,6 +227,73 @@ xoro_init_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_
     }
 }
 
+// Large arrays: the 128-term masked xor above keeps the integer pipe busy (about
+// 5 instructions per basis state).  This variant first expands the 128 basis
+// states into 16 byte-indexed tables in shared memory, T[p][v] = xor of the basis
+// states selected by byte value v at byte position p of the mask (64 KB per CTA,
+// built once per CTA), after which a state costs 16 128-bit shared loads and 16
+// three-input xors per word.  Persistent CTAs walk runs of `per_thread` states.
+constexpr int kTableBytes = 16 * 256 * 16;
+
+__global__ void __launch_bounds__(256)
+xoro_init_table_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_thread,
+                       const uint4 *__restrict__ ytab, const __grid_constant__ Basis basis,
+                       const Poly4 p_low) {
+    extern __shared__ uint4 table[];  // [16][256]
+    {
+        const uint32_t v = threadIdx.x;  // byte value owned by this thread
+#pragma unroll
+        for (int p = 0; p < 16; ++p) {
+            uint32_t t0 = 0, t1 = 0, t2 = 0, t3 = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t m = static_cast<uint32_t>(static_cast<int32_t>(v << (31 - i)) >> 31);
+                t0 ^= m & basis.w[8 * p + i][0];
+                t1 ^= m & basis.w[8 * p + i][1];
+                t2 ^= m & basis.w[8 * p + i][2];
+                t3 ^= m & basis.w[8 * p + i][3];
+            }
+            table[p * 256 + v] = make_uint4(t0, t1, t2, t3);
+        }
+    }
+    __syncthreads();
+
+    const int64_t runs = (n + per_thread - 1) / per_thread;
+    for (int64_t run = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; run < runs;
+         run += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t first = run * per_thread;
+        const uint64_t e = start + static_cast<uint64_t>(first);
+        Poly4 c{{1, 0, 0, 0}};
+        bool have = false;
+        for (int l = 0; l < 8; ++l) {
+            const uint32_t b = static_cast<uint32_t>(e >> (8 * l)) & 0xFFu;
+            if (b == 0) continue;
+            const uint4 raw = __ldg(ytab + l * 256 + b);
+            const Poly4 f{{raw.x, raw.y, raw.z, raw.w}};
+            c = have ? mulmod_d(c, f, p_low) : f;
+            have = true;
+        }
+        const int64_t last = (first + per_thread < n) ? first + per_thread : n;
+        for (int64_t i = first; i < last; ++i) {
+            uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t word = c.w[w];
+                const uint4 a = table[(4 * w + 0) * 256 + (word & 0xFFu)];
+                const uint4 b = table[(4 * w + 1) * 256 + ((word >> 8) & 0xFFu)];
+                const uint4 d = table[(4 * w + 2) * 256 + ((word >> 16) & 0xFFu)];
+                const uint4 g = table[(4 * w + 3) * 256 + (word >> 24)];
+                s0 ^= a.x ^ b.x; s0 ^= d.x ^ g.x;
+                s1 ^= a.y ^ b.y; s1 ^= d.y ^ g.y;
+                s2 ^= a.z ^ b.z; s2 ^= d.z ^ g.z;
+                s3 ^= a.w ^ b.w; s3 ^= d.w ^ g.w;
+            }
+            states[i] = make_uint4(s0, s1, s2, s3);
+            times_y_d(c, p_low);
+        }
+    }
+}
+
 // ---- device: draws ------------------------------------------------------------------
 // The generator arithmetic lives in include/b2k_xoroshiro128p.cuh so that user
 // CUDA C++ kernels and this library draw from the same code.
@@ -414,14 +481,30 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
                  static_cast<uint32_t>(rc.p_low.hi), static_cast<uint32_t>(rc.p_low.hi >> 32)}};
 
     // long runs per thread amortise the table products; short arrays stay parallel
-    int per_thread = n >= (int64_t(1) << 22) ? 64 : (n >= (int64_t(1) << 16) ? 16 : 1);
+    // runs of 32 measured best for the table kernel (large n); short arrays stay parallel
+    int per_thread = n >= (int64_t(1) << 18) ? 32 : (n >= (int64_t(1) << 16) ? 16 : 1);
     per_thread = b2k::env_int("B2K_XORO_INIT_PER_THREAD", per_thread);
     if (per_thread < 1) per_thread = 1;
     const int64_t threads = (n + per_thread - 1) / per_thread;
-    const int64_t grid = (threads + 255) / 256;
-    xoro_init_kernel<<<static_cast<unsigned>(grid), 256, 0, b2k::as_stream(stream)>>>(
-        static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
-        static_cast<const uint4 *>(tables_dev), basis, p_low);
+    int64_t grid = (threads + 255) / 256;
+    if (n >= (int64_t(1) << 18) && b2k::env_int("B2K_XORO_INIT_TABLES", 1) != 0) {
+        static std::once_flag once;
+        static cudaError_t attr = cudaSuccess;
+        std::call_once(once, [] {
+            attr = cudaFuncSetAttribute(xoro_init_table_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kTableBytes);
+        });
+        if (attr != cudaSuccess) return b2k::check_cuda(attr, "b2k_xoroshiro128p_init: smem attribute");
+        const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_INIT_CTAS_PER_SM", 2);
+        if (grid > cap) grid = cap;
+        xoro_init_table_kernel<<<static_cast<unsigned>(grid), 256, kTableBytes, b2k::as_stream(stream)>>>(
+            static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
+            static_cast<const uint4 *>(tables_dev), basis, p_low);
+    } else {
+        xoro_init_kernel<<<static_cast<unsigned>(grid), 256, 0, b2k::as_stream(stream)>>>(
+            static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
+            static_cast<const uint4 *>(tables_dev), basis, p_low);
+    }
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_xoroshiro128p_init launch");
     return B2K_OK;
