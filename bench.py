@@ -444,6 +444,24 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
                                                  scratch.data_ptr(), scratch.numel(), sptr)), 200, 10)
         res["c1_reduce_sum_f64_2p20"] = dict(_roof(n * 8, ms, peak), us_per_call=ms * 1e3,
                                              note="8 MiB: launch-latency bound, L2 resident")
+        # the same call captured in a CUDA graph (20 launches per replay): what is left
+        # of the 8 MiB case once the launch path is off the critical line
+        try:
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
+                                   scratch.data_ptr(), scratch.numel(), side.cuda_stream))
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
+                                       scratch.data_ptr(), scratch.numel(), torch.cuda.current_stream().cuda_stream))
+            ms_g, _ = timed(graph.replay, 20, 5)
+            res["c1_reduce_sum_f64_2p20"]["us_per_call_in_cuda_graph"] = ms_g * 1e3 / 20
+            del graph
+        except Exception as exc:  # graphs are an extra, never a reason to fail the bench
+            res["c1_reduce_sum_f64_2p20"]["cuda_graph_error"] = repr(exc)
         n2 = 1 << (28 - scale)
         y = torch.rand(n2, dtype=torch.float64, device="cuda")
         ms, _ = timed(lambda: check(L.b2k_reduce(_lib.ADD, _lib.F64, y.data_ptr(), n2, zero.ctypes.data,

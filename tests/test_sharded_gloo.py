@@ -24,10 +24,14 @@ def _free_port():
 
 def _worker(rank, world, port, fn_name, errors):
     try:
+        import datetime
         sys.path.insert(0, ROOT)
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+        if fn_name.startswith("_fail_"):
+            globals()[fn_name](rank, world)
+            return
         globals()[fn_name](rank, world)
         dist.barrier()
         dist.destroy_process_group()
@@ -123,6 +127,36 @@ def _body_world_mismatch(rank, world):
         sharded.shard_bounds(10, world, world)
 
 
+# ---- failures made on the host (no GPU involved) -----------------------------------
+def _fail_rank_leaves_before_the_combine(rank, world):
+    """Rank 1 raises before the collective; rank 0 must get an error from the
+    combine instead of waiting for ever."""
+    from numba_cuda_b200 import _lib, sharded
+    if rank == 1:
+        os._exit(0)          # leaves between steps, nothing in flight
+    buf = torch.from_numpy(np.array([5], dtype=np.int32).view(np.uint8).copy())
+    try:
+        sharded.combine_partials(buf, _lib.MAX, np.int32)
+    except Exception:
+        return               # the expected outcome
+    raise AssertionError("combine returned although a rank was missing")
+
+
+def _fail_ranks_disagree_on_partition(rank, world):
+    """A rank configured with a different world size computes bounds that do not
+    tile the array; the mismatch is detected by exchanging the bounds."""
+    from numba_cuda_b200 import sharded
+    n = 1000
+    claimed_world = world if rank == 0 else world + 1
+    lo, hi = sharded.shard_bounds(n, claimed_world, rank)
+    all_bounds = [None] * world
+    dist.all_gather_object(all_bounds, (lo, hi))
+    covered = sorted(all_bounds)
+    contiguous = covered[0][0] == 0 and covered[-1][1] == n and all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+    assert not contiguous
+    dist.barrier()
+
+
 # ---- tests ------------------------------------------------------------------------
 def test_combine_partials_two_ranks():
     _run("_body_reduce")
@@ -138,6 +172,26 @@ def test_cast_shards_are_aligned_and_complete():
 
 def test_bad_rank_is_rejected():
     _run("_body_world_mismatch")
+
+
+def test_missing_rank_fails_the_combine_instead_of_hanging():
+    ctx = mp.get_context("spawn")
+    errors = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, "_fail_rank_leaves_before_the_combine", errors))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(90)
+        if p.is_alive():
+            p.kill()
+            pytest.fail("a rank hung")
+    assert errors.empty(), errors.get()
+
+
+def test_partition_mismatch_is_detectable():
+    _run("_fail_ranks_disagree_on_partition")
 
 
 def test_single_process_is_world_of_one():
