@@ -1,11 +1,11 @@
 #!/usr/bin/env python
 """Generate the golden fixtures in this folder by EXECUTING THE REFERENCE.
 
-Run only in a container that has the reference tree (default /root/reference);
+Run only in a container that has the reference tree mounted (``--reference``);
 the fixtures it writes are committed so that the tests need no reference at
 run time.  Usage::
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <numba-cuda checkout>]
 
 Recipe (the reference is read-only and its C extensions are not built, and the
 ``cuda-core`` dependency is not installed):

@@ -82,3 +82,27 @@ def test_no_cpu_fallback_without_device():
         cuda.reduce(lambda a, b: a + b)(np.arange(4.0))
     with pytest.raises(RuntimeError):
         cuda.random.create_xoroshiro128p_states(4, 1)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No library, no work: the binding raises instead of finding another way."""
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libb2k.so"))
+    _lib.lib.cache_clear()
+    try:
+        with pytest.raises(ImportError, match="no CPU fallback"):
+            _lib.lib()
+    finally:
+        monkeypatch.undo()
+        _lib.lib.cache_clear()
+        assert _lib.lib().b2k_version() >= 100
+
+
+def test_package_never_touches_the_oracle():
+    """The CPU oracle is test infrastructure: nothing under the package imports,
+    loads or names it."""
+    pkg = os.path.join(ROOT, "numba_cuda_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for name in files:
+            if name.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, name)).read()
+                assert "oracle" not in text.lower(), os.path.join(dirpath, name)
