@@ -330,7 +330,7 @@ __device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
 // aligned leave as 128-bit stores, four rows of 128 bytes per instruction;
 // ragged tiles (last generators, last columns, odd counts) leave one row of
 // scalars per instruction.
-template <typename T, int DRAW>
+template <typename T, int DRAW, int UNROLL>
 __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
                                              int64_t n, const Segment &seg, void *stage) {
     constexpr int CHUNK = sizeof(T) == 4 ? 32 : 16;
@@ -348,7 +348,10 @@ __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool li
         if (live) {
             T *row = buf + lane * PITCH;
             if (m == CHUNK) {
-#pragma unroll 8
+                // uniforms are short integer chains: unroll deep to overlap generators;
+                // normals are long libdevice chains: unroll little to keep registers free
+                constexpr int U = (DRAW == B2K_UNIFORM_F32 || DRAW == B2K_UNIFORM_F64) ? 16 : UNROLL;
+#pragma unroll U
                 for (int i = 0; i < CHUNK; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
             } else {
                 for (int i = 0; i < m; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
@@ -394,18 +397,20 @@ __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool li
     }
 }
 
+template <int UNROLL>
 __device__ __forceinline__ void run_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
                                             int64_t n, const Segment &seg, void *stage) {
     if (seg.count <= 0) return;
     switch (seg.draw) {  // uniform across the grid
-    case B2K_UNIFORM_F32: fill_segment<float, B2K_UNIFORM_F32>(s0, s1, live, base, n, seg, stage); break;
-    case B2K_UNIFORM_F64: fill_segment<double, B2K_UNIFORM_F64>(s0, s1, live, base, n, seg, stage); break;
-    case B2K_NORMAL_F32: fill_segment<float, B2K_NORMAL_F32>(s0, s1, live, base, n, seg, stage); break;
-    default: fill_segment<double, B2K_NORMAL_F64>(s0, s1, live, base, n, seg, stage); break;
+    case B2K_UNIFORM_F32: fill_segment<float, B2K_UNIFORM_F32, UNROLL>(s0, s1, live, base, n, seg, stage); break;
+    case B2K_UNIFORM_F64: fill_segment<double, B2K_UNIFORM_F64, UNROLL>(s0, s1, live, base, n, seg, stage); break;
+    case B2K_NORMAL_F32: fill_segment<float, B2K_NORMAL_F32, UNROLL>(s0, s1, live, base, n, seg, stage); break;
+    default: fill_segment<double, B2K_NORMAL_F64, UNROLL>(s0, s1, live, base, n, seg, stage); break;
     }
 }
 
-__global__ void __launch_bounds__(kFillWarps * 32)
+template <int MINBLOCKS, int UNROLL>
+__global__ void __launch_bounds__(kFillWarps * 32, MINBLOCKS)
 xoro_fill_kernel(ulonglong2 *__restrict__ states, int64_t n, Segment seg0, Segment seg1) {
     __shared__ __align__(16) unsigned char stage_all[kFillWarps][kStageBytes];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -422,8 +427,8 @@ xoro_fill_kernel(ulonglong2 *__restrict__ states, int64_t n, Segment seg0, Segme
             s0 = s.x;
             s1 = s.y;
         }
-        run_segment(s0, s1, live, base, n, seg0, stage);
-        run_segment(s0, s1, live, base, n, seg1, stage);
+        run_segment<UNROLL>(s0, s1, live, base, n, seg0, stage);
+        run_segment<UNROLL>(s0, s1, live, base, n, seg1, stage);
         if (live) states[g] = make_ulonglong2(s0, s1);
     }
 }
@@ -530,10 +535,10 @@ int b2k_xoroshiro128p_fill(void *states_dev, int64_t n, int draw0, void *out0_de
     }
     const int64_t groups = (n + 31) / 32;
     int64_t grid = (groups + kFillWarps - 1) / kFillWarps;
-    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_FILL_CTAS_PER_SM", 6);
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_FILL_CTAS_PER_SM", 8);
     if (grid > cap) grid = cap;
     Segment a{out0_dev, count0, draw0}, b{out1_dev, count1, draw1};
-    xoro_fill_kernel<<<static_cast<unsigned>(grid), kFillWarps * 32, 0, b2k::as_stream(stream)>>>(
+    xoro_fill_kernel<4, 4><<<static_cast<unsigned>(grid), kFillWarps * 32, 0, b2k::as_stream(stream)>>>(
         static_cast<ulonglong2 *>(states_dev), n, a, b);
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_xoroshiro128p_fill launch");
