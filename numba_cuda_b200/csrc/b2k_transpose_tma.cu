@@ -11,6 +11,8 @@
 //            swizzle puts chunk q of row r at chunk (q ^ (r & 7)), so a
 //            quarter-warp always touches eight different bank groups----------.
 //   B[b]   <-st.shared of single items, lanes walk the contiguous direction <-'
+//            (1- and 2-byte items: four / two rows are first interleaved in
+//             registers with byte permutes so that every store is a 32-bit word)
 //   B[b]   --cp.async.bulk.tensor store (tiled, no swizzle)--> global
 //
 // B holds the transposed tile as (128/ES) output rows of R items.  R = 64 (8 KB
@@ -90,6 +92,10 @@ template <> struct Item<16> { using type = uint4; };
 
 // Transpose one staged tile: A is R rows x 128 B (swizzled), B is (128/ES) rows
 // of R items (linear).
+//
+// Items of 4 bytes and more: a thread reads one 16-byte chunk of one row and
+// scatters its items; lanes walk rows, so reads are conflict-free through the
+// swizzle and writes run along B's contiguous direction.
 template <int ES, int R, int THREADS>
 __device__ __forceinline__ void transpose_tile(const unsigned char *A, unsigned char *B) {
     using T = typename Item<ES>::type;
@@ -106,6 +112,63 @@ __device__ __forceinline__ void transpose_tile(const unsigned char *A, unsigned 
         T *dst = reinterpret_cast<T *>(B) + static_cast<size_t>(q * EPC) * R + r;
 #pragma unroll
         for (int k = 0; k < EPC; ++k) dst[k * R] = u.e[k];
+    }
+}
+
+// 2-byte items, R = 64, 256 threads: a thread owns two consecutive rows (2g, 2g+1)
+// and one chunk of eight columns, pairs the rows with byte permutes and stores
+// eight 32-bit words (column c, rows 2g..2g+1).  Lane mapping inside a warp:
+// quarter-warp s, lane j -> row pair g = 8s + j, chunk q0 ^ (j >> 2) with q0 = warp;
+// the eight lanes of a quarter-warp then read eight different swizzled chunks and
+// the 32 lanes of a store hit 32 different banks (bank = g).
+template <>
+__device__ __forceinline__ void transpose_tile<2, 64, 256>(const unsigned char *A, unsigned char *B) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = lane & 7;
+    const int g = (lane >> 3) * 8 + j;
+    const int q = warp ^ (j >> 2);
+    const int r0 = 2 * g;
+    const uint4 a = *reinterpret_cast<const uint4 *>(A + r0 * 128 + ((q ^ (r0 & 7)) << 4));
+    const uint4 b = *reinterpret_cast<const uint4 *>(A + (r0 + 1) * 128 + ((q ^ ((r0 + 1) & 7)) << 4));
+    uint32_t *dst = reinterpret_cast<uint32_t *>(B) + (q * 8) * 32 + g;  // B row = 64 items = 32 words
+    const uint32_t ra[4] = {a.x, a.y, a.z, a.w}, rb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        dst[(2 * k) * 32] = __byte_perm(ra[k], rb[k], 0x5410);      // column 2k:   low halves
+        dst[(2 * k + 1) * 32] = __byte_perm(ra[k], rb[k], 0x7632);  // column 2k+1: high halves
+    }
+}
+
+// 1-byte items, R = 128, 256 threads: a thread owns four consecutive rows and one
+// chunk of sixteen columns, transposes four 4x4 byte blocks with byte permutes and
+// stores sixteen 32-bit words (column c, rows 4g..4g+3).  Lane mapping: quarter-warp
+// s, lane j -> row group g = 8s + j, chunk q0 ^ (j >> 1) with q0 = warp.
+template <>
+__device__ __forceinline__ void transpose_tile<1, 128, 256>(const unsigned char *A, unsigned char *B) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = lane & 7;
+    const int g = (lane >> 3) * 8 + j;
+    const int q = warp ^ (j >> 1);
+    const int r0 = 4 * g;
+    uint4 row[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        row[k] = *reinterpret_cast<const uint4 *>(A + (r0 + k) * 128 + ((q ^ ((r0 + k) & 7)) << 4));
+    uint32_t *dst = reinterpret_cast<uint32_t *>(B) + (q * 16) * 32 + g;  // B row = 128 items = 32 words
+    const uint32_t w0[4] = {row[0].x, row[0].y, row[0].z, row[0].w};
+    const uint32_t w1[4] = {row[1].x, row[1].y, row[1].z, row[1].w};
+    const uint32_t w2[4] = {row[2].x, row[2].y, row[2].z, row[2].w};
+    const uint32_t w3[4] = {row[3].x, row[3].y, row[3].z, row[3].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {  // one 4x4 byte block per 32-bit column group
+        const uint32_t t0 = __byte_perm(w0[k], w1[k], 0x5140);  // a0 b0 a1 b1
+        const uint32_t t1 = __byte_perm(w2[k], w3[k], 0x5140);  // c0 d0 c1 d1
+        const uint32_t t2 = __byte_perm(w0[k], w1[k], 0x7362);  // a2 b2 a3 b3
+        const uint32_t t3 = __byte_perm(w2[k], w3[k], 0x7362);  // c2 d2 c3 d3
+        dst[(4 * k + 0) * 32] = __byte_perm(t0, t1, 0x5410);
+        dst[(4 * k + 1) * 32] = __byte_perm(t0, t1, 0x7632);
+        dst[(4 * k + 2) * 32] = __byte_perm(t2, t3, 0x5410);
+        dst[(4 * k + 3) * 32] = __byte_perm(t2, t3, 0x7632);
     }
 }
 
@@ -129,7 +192,7 @@ struct TileOrder {
     }
 };
 
-template <int ES, int R, int NSTAGE, int THREADS, int NOUT>
+template <int ES, int R, int NSTAGE, int THREADS, int NOUT, bool SPLIT>
 __global__ void __launch_bounds__(THREADS)
 transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
                      const TileOrder order, long long tiles, int refill_thread) {
@@ -168,11 +231,9 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
     }
     __syncthreads();
 
-    // Thread 0 stores finished tiles; `refill_thread` (0 or 32) refills the load
-    // ring.  Tile coordinates are worked out before the wait, so that nothing but
-    // the issue itself sits between the block barriers.  Splitting the two roles
-    // over two warps measured +9 % for 2-byte items and a loss for the others.
-    const int kRefillThread = refill_thread;
+    // Thread 0 stores finished tiles and refills the load ring (SPLIT: as two
+    // separate blocks, the refill by `refill_thread`, which the launcher sets to 0).
+    // Tile coordinates are worked out before the wait for the tile.
     bool ok = true;
     int it = 0;
     for (long long id = first; id < tiles; id += step, ++it) {
@@ -181,14 +242,24 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
         int tx = 0, ty = 0;
         bool refill = false;
         int ltx = 0, lty = 0;
-        if (threadIdx.x == 0) {
-            order.coords(static_cast<unsigned int>(id), tx, ty);
-            tma_wait_read<NOUT - 1>();  // the store that last read B[b] has drained
-        }
-        if (threadIdx.x == kRefillThread) {
-            const long long next = id + NSTAGE * step;
-            refill = next < tiles;
-            if (refill) order.coords(static_cast<unsigned int>(next), ltx, lty);
+        if constexpr (SPLIT) {
+            if (threadIdx.x == 0) {
+                order.coords(static_cast<unsigned int>(id), tx, ty);
+                tma_wait_read<NOUT - 1>();  // the store that last read B[b] has drained
+            }
+            if (threadIdx.x == refill_thread) {
+                const long long next = id + NSTAGE * step;
+                refill = next < tiles;
+                if (refill) order.coords(static_cast<unsigned int>(next), ltx, lty);
+            }
+        } else {
+            if (threadIdx.x == 0) {
+                order.coords(static_cast<unsigned int>(id), tx, ty);
+                const long long next = id + NSTAGE * step;
+                refill = next < tiles;
+                if (refill) order.coords(static_cast<unsigned int>(next), ltx, lty);
+                tma_wait_read<NOUT - 1>();  // the store that last read B[b] has drained
+            }
         }
         ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
         // every thread polls the same barrier, so the vote only guards against skew
@@ -198,14 +269,25 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
         fence_async_smem();
         __syncthreads();
 
-        if (threadIdx.x == 0) {
-            // output coordinates: x runs along input rows, y along input columns
-            tma_store_2d(&out_map, ty * (R * WORDS), tx * TCOLS, B + b * TILE_BYTES);
-            tma_commit();
-        }
-        if (threadIdx.x == kRefillThread && refill) {
-            mbar_expect_tx(&full[s], TILE_BYTES);
-            tma_load_2d(A + s * TILE_BYTES, &in_map, ltx * (TCOLS * WORDS), lty * R, &full[s]);
+        if constexpr (SPLIT) {
+            if (threadIdx.x == 0) {
+                // output coordinates: x runs along input rows, y along input columns
+                tma_store_2d(&out_map, ty * (R * WORDS), tx * TCOLS, B + b * TILE_BYTES);
+                tma_commit();
+            }
+            if (threadIdx.x == refill_thread && refill) {
+                mbar_expect_tx(&full[s], TILE_BYTES);
+                tma_load_2d(A + s * TILE_BYTES, &in_map, ltx * (TCOLS * WORDS), lty * R, &full[s]);
+            }
+        } else {
+            if (threadIdx.x == 0) {
+                tma_store_2d(&out_map, ty * (R * WORDS), tx * TCOLS, B + b * TILE_BYTES);
+                tma_commit();
+                if (refill) {
+                    mbar_expect_tx(&full[s], TILE_BYTES);
+                    tma_load_2d(A + s * TILE_BYTES, &in_map, ltx * (TCOLS * WORDS), lty * R, &full[s]);
+                }
+            }
         }
     }
     if (threadIdx.x == 0) {
@@ -274,11 +356,27 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     const int64_t tiles = tiles_x * tiles_y;
     if (tiles > 0x7FFFFFFFll) return B2K_ERR_UNSUPPORTED;  // the kernel numbers tiles in 31 bits
     constexpr int SMEM = (NSTAGE + NOUT) * R * 128 + NSTAGE * 8 + 1024;
-    auto kernel = transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT>;
+    // Two code shapes for the issuing thread, chosen by measurement.  With the
+    // store and the refill in separate blocks (SPLIT) lines that are not 128-byte
+    // aligned run 10-40 % faster for items of 2 bytes and more, and 4-byte items
+    // gain 2-3 % on aligned lines too; the merged shape is 3-5 % ahead for 1-byte
+    // items and for 2-byte items on 128-byte-aligned lines.  DRAM traffic and the
+    // isolated launch time are the same for both, so the difference comes from how
+    // the CTAs' requests fall into step over back-to-back tiles.
+    const bool aligned = in_pitch % 128 == 0 && out_pitch % 128 == 0;
+    const bool auto_split = ES >= 4 || (ES == 2 && !aligned);
+    const int forced = b2k::env_int("B2K_TRANSPOSE_SPLIT", -1);
+    const bool split = forced < 0 ? auto_split : forced != 0;
+    auto kernel = split ? transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>
+                        : transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>;
     static std::once_flag once;
     static cudaError_t attr_status = cudaSuccess;
     std::call_once(once, [&] {
-        attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        attr_status = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (attr_status == cudaSuccess)
+            attr_status = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     });
     if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
     // two resident CTAs per SM measured best (more CTAs only add DRAM page conflicts)
@@ -288,8 +386,11 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     int panel_w = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
     if (panel_w < 1 || panel_w > tiles_x) panel_w = static_cast<int>(tiles_x);
     const TileOrder order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), panel_w};
-    kernel<<<static_cast<unsigned>(grid), THREADS, SMEM, stream>>>(
-        in_map, out_map, order, static_cast<long long>(tiles), b2k::env_int("B2K_TRANSPOSE_REFILL_THREAD", ES == 2 ? 32 : 0));
+    // the refill thread is a run-time argument on purpose: as a constant the compiler
+    // would fuse the two blocks of the SPLIT shape back into one
+    kernel<<<static_cast<unsigned>(grid), THREADS, SMEM, stream>>>(in_map, out_map, order,
+                                                                   static_cast<long long>(tiles),
+                                                                   b2k::env_int("B2K_TRANSPOSE_REFILL_THREAD", 0));
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_transpose2d (tma) launch");
     return B2K_OK;

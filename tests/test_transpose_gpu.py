@@ -108,7 +108,8 @@ def test_small_shapes_every_itemsize(itemsize):
     (512, 1024, np.float32), (1028, 516, np.float32), (64, 32, np.uint32), (1, 4096 * 8, np.uint32),
     (4096 * 8, 4, np.uint32), (300, 4104, np.uint16), (264, 136, np.uint16), (528, 1040, np.uint8),
     (1024, 2048, np.uint8), (514, 258, np.uint64), (520, 130, np.complex128), (1000, 2000, np.float32),
-    (2049, 4100, np.float32), (1999, 3000, np.float64), (4097, 1032, np.uint16), (777, 1008, np.int8)])
+    (2049, 4100, np.float32), (1999, 3000, np.float64), (4097, 1032, np.uint16), (777, 1008, np.int8),
+    (1024, 2048, np.uint16), (448, 320, np.uint16), (1088, 960, np.int16), (640, 1152, np.uint8)])
 def test_tma_tile_path_shapes(rows, cols, dtype):
     rng = np.random.default_rng(rows * 7 + cols)
     a = rng.integers(0, 1 << 30, size=(rows, cols)).astype(dtype)
