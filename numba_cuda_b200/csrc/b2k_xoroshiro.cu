@@ -229,17 +229,80 @@ xoro_init_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_
 
 // Large arrays: the 128-term masked xor above keeps the integer pipe busy (about
 // 5 instructions per basis state).  This variant first expands the 128 basis
-// states into 16 byte-indexed tables in shared memory, T[p][v] = xor of the basis
+// states into byte-indexed tables in shared memory, T[v][p] = xor of the basis
 // states selected by byte value v at byte position p of the mask (64 KB per CTA,
 // built once per CTA), after which a state costs 16 128-bit shared loads and 16
-// three-input xors per word.  Persistent CTAs walk runs of `per_thread` states.
+// three-input xors per word.
+//
+// Bank conflicts: a 128-bit shared load is served a quarter-warp at a time, and
+// eight 16-byte entries collide unless they sit in eight different 16-byte slots
+// of the 128-byte bank row.  The byte values v are random, so the slot must not
+// depend on v: entries are laid out [v][p] (slot = p mod 8) and lane l walks the
+// byte positions in the rotated order p = (t + l) mod 16, t = 0..15, so the eight
+// lanes of a quarter-warp always read eight different slots.  The rotation is
+// applied to the mask once per state (a 128-bit byte rotate by l mod 16), after
+// which byte t of the rotated mask is extracted with a constant selector.
+//
+// Every thread owns ONE contiguous run of `per_thread` states (an even number), so
+// y^index is built once per thread and then advanced by single steps, and states
+// leave in pairs as 32-byte stores when `states` is 32-byte aligned.
 constexpr int kTableBytes = 16 * 256 * 16;
 
+__device__ __forceinline__ void store_state_pair(uint4 *dst, const uint4 &a, const uint4 &b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(a.x), "r"(a.y), "r"(a.z),
+                 "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
+}
+
+template <int T>
+__device__ __forceinline__ void table_lookup(const unsigned char *tb, const uint32_t (&w)[4], uint32_t r16,
+                                             uint32_t &s0, uint32_t &s1, uint32_t &s2, uint32_t &s3) {
+    // byte (T & 3) of word T / 4, moved to bits 8..15: the byte offset v * 256
+    constexpr uint32_t kSel = 0x4404u | ((T & 3) << 4);
+    const uint32_t voff = __byte_perm(w[T >> 2], 0u, kSel);
+    const uint32_t poff = (r16 + 16u * T) & 0xF0u;
+    const uint4 e = *reinterpret_cast<const uint4 *>(tb + voff + poff);
+    s0 ^= e.x;
+    s1 ^= e.y;
+    s2 ^= e.z;
+    s3 ^= e.w;
+}
+
+__device__ __forceinline__ uint4 state_from_mask(const unsigned char *tb, const Poly4 &c, uint32_t r) {
+    // rotate the 16 mask bytes down by r: byte t of w = byte (t + r) mod 16 of c
+    const bool r4 = (r & 4u) != 0, r8 = (r & 8u) != 0;
+    const uint32_t sh = (r & 3u) * 8u;
+    const uint32_t y0 = r4 ? c.w[1] : c.w[0], y1 = r4 ? c.w[2] : c.w[1];
+    const uint32_t y2 = r4 ? c.w[3] : c.w[2], y3 = r4 ? c.w[0] : c.w[3];
+    const uint32_t x0 = r8 ? y2 : y0, x1 = r8 ? y3 : y1, x2 = r8 ? y0 : y2, x3 = r8 ? y1 : y3;
+    const uint32_t w[4] = {__funnelshift_r(x0, x1, sh), __funnelshift_r(x1, x2, sh), __funnelshift_r(x2, x3, sh),
+                           __funnelshift_r(x3, x0, sh)};
+    const uint32_t r16 = r * 16u;
+    uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    table_lookup<0>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<1>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<2>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<3>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<4>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<5>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<6>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<7>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<8>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<9>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<10>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<11>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<12>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<13>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<14>(tb, w, r16, s0, s1, s2, s3);
+    table_lookup<15>(tb, w, r16, s0, s1, s2, s3);
+    return make_uint4(s0, s1, s2, s3);
+}
+
 __global__ void __launch_bounds__(256)
-xoro_init_table_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_thread,
+xoro_init_table_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, int per_thread, int wide_stores,
                        const uint4 *__restrict__ ytab, const __grid_constant__ Basis basis,
                        const Poly4 p_low) {
-    extern __shared__ uint4 table[];  // [16][256]
+    extern __shared__ uint4 table[];  // [256][16]
     {
         const uint32_t v = threadIdx.x;  // byte value owned by this thread
 #pragma unroll
@@ -253,44 +316,40 @@ xoro_init_table_kernel(uint4 *__restrict__ states, int64_t n, uint64_t start, in
                 t2 ^= m & basis.w[8 * p + i][2];
                 t3 ^= m & basis.w[8 * p + i][3];
             }
-            table[p * 256 + v] = make_uint4(t0, t1, t2, t3);
+            table[v * 16 + p] = make_uint4(t0, t1, t2, t3);
         }
     }
     __syncthreads();
 
-    const int64_t runs = (n + per_thread - 1) / per_thread;
-    for (int64_t run = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; run < runs;
-         run += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t first = run * per_thread;
-        const uint64_t e = start + static_cast<uint64_t>(first);
-        Poly4 c{{1, 0, 0, 0}};
-        bool have = false;
-        for (int l = 0; l < 8; ++l) {
-            const uint32_t b = static_cast<uint32_t>(e >> (8 * l)) & 0xFFu;
-            if (b == 0) continue;
-            const uint4 raw = __ldg(ytab + l * 256 + b);
-            const Poly4 f{{raw.x, raw.y, raw.z, raw.w}};
-            c = have ? mulmod_d(c, f, p_low) : f;
-            have = true;
-        }
-        const int64_t last = (first + per_thread < n) ? first + per_thread : n;
-        for (int64_t i = first; i < last; ++i) {
-            uint32_t s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const uint32_t word = c.w[w];
-                const uint4 a = table[(4 * w + 0) * 256 + (word & 0xFFu)];
-                const uint4 b = table[(4 * w + 1) * 256 + ((word >> 8) & 0xFFu)];
-                const uint4 d = table[(4 * w + 2) * 256 + ((word >> 16) & 0xFFu)];
-                const uint4 g = table[(4 * w + 3) * 256 + (word >> 24)];
-                s0 ^= a.x ^ b.x; s0 ^= d.x ^ g.x;
-                s1 ^= a.y ^ b.y; s1 ^= d.y ^ g.y;
-                s2 ^= a.z ^ b.z; s2 ^= d.z ^ g.z;
-                s3 ^= a.w ^ b.w; s3 ^= d.w ^ g.w;
-            }
-            states[i] = make_uint4(s0, s1, s2, s3);
+    const unsigned char *tb = reinterpret_cast<const unsigned char *>(table);
+    const uint32_t r = threadIdx.x & 15u;
+    const int64_t first = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * per_thread;
+    if (first >= n) return;
+    const uint64_t e = start + static_cast<uint64_t>(first);
+    Poly4 c{{1, 0, 0, 0}};
+    bool have = false;
+    for (int l = 0; l < 8; ++l) {
+        const uint32_t b = static_cast<uint32_t>(e >> (8 * l)) & 0xFFu;
+        if (b == 0) continue;
+        const uint4 raw = __ldg(ytab + l * 256 + b);
+        const Poly4 f{{raw.x, raw.y, raw.z, raw.w}};
+        c = have ? mulmod_d(c, f, p_low) : f;
+        have = true;
+    }
+    const int64_t last = (first + per_thread < n) ? first + per_thread : n;
+    int64_t i = first;
+    if (wide_stores) {  // `first` is even and `states` 32-byte aligned
+        for (; i + 2 <= last; i += 2) {
+            const uint4 a = state_from_mask(tb, c, r);
             times_y_d(c, p_low);
+            const uint4 b = state_from_mask(tb, c, r);
+            times_y_d(c, p_low);
+            store_state_pair(states + i, a, b);
         }
+    }
+    for (; i < last; ++i) {
+        states[i] = state_from_mask(tb, c, r);
+        times_y_d(c, p_low);
     }
 }
 
@@ -485,13 +544,6 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
     Poly4 p_low{{static_cast<uint32_t>(rc.p_low.lo), static_cast<uint32_t>(rc.p_low.lo >> 32),
                  static_cast<uint32_t>(rc.p_low.hi), static_cast<uint32_t>(rc.p_low.hi >> 32)}};
 
-    // long runs per thread amortise the table products; short arrays stay parallel
-    // runs of 32 measured best for the table kernel (large n); short arrays stay parallel
-    int per_thread = n >= (int64_t(1) << 18) ? 32 : (n >= (int64_t(1) << 16) ? 16 : 1);
-    per_thread = b2k::env_int("B2K_XORO_INIT_PER_THREAD", per_thread);
-    if (per_thread < 1) per_thread = 1;
-    const int64_t threads = (n + per_thread - 1) / per_thread;
-    int64_t grid = (threads + 255) / 256;
     if (n >= (int64_t(1) << 18) && b2k::env_int("B2K_XORO_INIT_TABLES", 1) != 0) {
         static std::once_flag once;
         static cudaError_t attr = cudaSuccess;
@@ -500,12 +552,29 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
                                         kTableBytes);
         });
         if (attr != cudaSuccess) return b2k::check_cuda(attr, "b2k_xoroshiro128p_init: smem attribute");
-        const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_INIT_CTAS_PER_SM", 2);
-        if (grid > cap) grid = cap;
+        // one contiguous run per thread over a grid that fills the GPU once; runs of
+        // at least 64 states keep the y^index products a small share of the work
+        const int64_t resident =
+            static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_INIT_CTAS_PER_SM", 2) * 256;
+        int64_t per_thread = (n + resident - 1) / resident;
+        const int64_t floor_run = b2k::env_int("B2K_XORO_INIT_PER_THREAD", 64);
+        if (per_thread < floor_run) per_thread = floor_run;
+        per_thread += per_thread & 1;
+        if (per_thread > 0x7FFFFFFE) per_thread = 0x7FFFFFFE;
+        const int64_t threads = (n + per_thread - 1) / per_thread;
+        const int64_t grid = (threads + 255) / 256;
+        if (grid > 0x7FFFFFFF) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_xoroshiro128p_init: too many states");
+        const int wide = b2k::aligned_to<void>(states_dev, 32) ? 1 : 0;
         xoro_init_table_kernel<<<static_cast<unsigned>(grid), 256, kTableBytes, b2k::as_stream(stream)>>>(
-            static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
+            static_cast<uint4 *>(states_dev), n, subsequence_start, static_cast<int>(per_thread), wide,
             static_cast<const uint4 *>(tables_dev), basis, p_low);
     } else {
+        // short arrays: runs of 16 amortise the table products, tiny ones stay parallel
+        int per_thread = n >= (int64_t(1) << 16) ? 16 : 1;
+        per_thread = b2k::env_int("B2K_XORO_INIT_SHORT_PER_THREAD", per_thread);
+        if (per_thread < 1) per_thread = 1;
+        const int64_t threads = (n + per_thread - 1) / per_thread;
+        const int64_t grid = (threads + 255) / 256;
         xoro_init_kernel<<<static_cast<unsigned>(grid), 256, 0, b2k::as_stream(stream)>>>(
             static_cast<uint4 *>(states_dev), n, subsequence_start, per_thread,
             static_cast<const uint4 *>(tables_dev), basis, p_low);

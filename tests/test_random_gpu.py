@@ -87,6 +87,21 @@ def test_states_large_array_vs_oracle():
     assert got.tobytes() == oracle.init_states(n, 42, 0).tobytes()
 
 
+def test_table_path_on_a_16_byte_offset_view_and_with_a_huge_start():
+    # large arrays take the shared-memory table kernel; a view that starts 16 bytes
+    # into an allocation cannot use its paired 32-byte stores
+    n = (1 << 18) + 3
+    base = cuda.device_array(n + 1, dtype=xoroshiro128p_dtype)
+    view = base[1:]
+    init_xoroshiro128p_states(view, 9, 5)
+    assert view.copy_to_host().tobytes() == oracle.init_states(n, 9, 5).tobytes()
+    start = (1 << 45) + 7
+    big = create_xoroshiro128p_states(n, 3, start).copy_to_host()
+    for off in (0, 777, 131071, n - 40):
+        small = create_xoroshiro128p_states(40, 3, start + off).copy_to_host()   # the small-array kernel
+        assert small.tobytes() == big[off:off + 40].tobytes()
+
+
 def test_huge_subsequence_start_chain_rule():
     for start in (1 << 40, (1 << 63) + 12345, 2 ** 64 - 300):
         s = create_xoroshiro128p_states(256, 11, start).copy_to_host()
