@@ -166,6 +166,20 @@ B2K_API int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, int
                     int64_t out_stride0, int64_t out_stride1,
                     int64_t itemsize, void *stream);
 
+/* ---- strided assignment --------------------------------------------------
+ * Replaces the per-ndim JIT-compiled element kernel behind
+ * DeviceNDArray.__setitem__ (numba/cuda/cudadrv/devicearray.py:535-576, launched
+ * at :735-791): dst[i0, .., ik] = src[i0', .., ik'] over a common `shape`, where a
+ * source stride of 0 repeats the source along that axis (the reference's
+ * "rhs.shape[i] > 1" factor).  Strides are in bytes, may be negative, and are
+ * arbitrary for both sides, so the same call also materialises axis permutations
+ * (N-D transposes) and copies between differently laid out arrays.  The two sides
+ * must not overlap.  ndim <= 32; at most 8 axes may remain after the library has
+ * merged axes that are contiguous on both sides. */
+B2K_API int b2k_assign(void *dst_dev, const void *src_dev, int ndim, const int64_t *shape,
+                       const int64_t *dst_strides, const int64_t *src_strides, int64_t itemsize,
+                       void *stream);
+
 /* ---- xoroshiro128p ------------------------------------------------------
  * b2k_xoroshiro128p_init replaces init_xoroshiro128p_states_cpu + the H2D copy
  * (numba/cuda/random.py:242-282): states[i] = jump^(subsequence_start+i)(seed

@@ -24,6 +24,7 @@ SOURCES = [
     "b2k_xoroshiro.cu",
     "b2k_transpose.cu",
     "b2k_transpose_tma.cu",
+    "b2k_assign.cu",
 ]
 
 NVCC_FLAGS = [

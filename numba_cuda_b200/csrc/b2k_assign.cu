@@ -1,0 +1,277 @@
+// N-D strided assignment with broadcasting: dst[idx] = src[idx'] for every index of
+// a common shape, where both sides are described by byte strides and a source
+// stride of 0 repeats the source along that axis.  This is the device side of
+// DeviceNDArray.__setitem__ (numba/cuda/cudadrv/devicearray.py:535-576, 735-791)
+// and of N-D axis permutations.
+//
+// The host first rewrites the problem: axes of length 1 disappear, the item is
+// split off as an innermost axis of bytes, axes are ordered by falling destination
+// stride (assignment has no order of its own, so the axis that is densest in the
+// destination becomes the fastest one), neighbouring axes that are contiguous on
+// both sides are merged, and the innermost axis is regrouped into the widest unit
+// (16, 8, 4, 2 or 1 bytes) that every pointer and stride allows.  Two kernels:
+//
+//  * direct: one thread per unit, four units in flight per thread, consecutive
+//    threads on consecutive units of the fastest destination axis.  Reads are
+//    coalesced too whenever the source is dense along the same axis (slices,
+//    row / scalar broadcasts, plain copies);
+//  * tiled: when the source is dense along a DIFFERENT axis q than the destination
+//    (axis permutations), 32x32-unit tiles over (destination axis p, source axis q)
+//    go through shared memory so that both sides see coalesced accesses.
+#include <algorithm>
+
+#include "b2k_internal.cuh"
+
+namespace {
+
+constexpr int kMaxAxes = 8;
+
+struct Axes {
+    int n;                        // axes in use, the last one is the fastest
+    int64_t len[kMaxAxes];        // in units
+    int64_t dst_step[kMaxAxes];   // bytes
+    int64_t src_step[kMaxAxes];   // bytes, 0 = broadcast
+};
+
+template <typename Index>
+__device__ __forceinline__ void locate(const Axes &ax, Index linear, int64_t &doff, int64_t &soff) {
+    doff = 0;
+    soff = 0;
+#pragma unroll
+    for (int k = kMaxAxes - 1; k >= 0; --k) {
+        if (k < ax.n) {
+            const Index len = static_cast<Index>(ax.len[k]);
+            const Index q = linear / len;
+            const Index i = linear - q * len;
+            linear = q;
+            doff += static_cast<int64_t>(i) * ax.dst_step[k];
+            soff += static_cast<int64_t>(i) * ax.src_step[k];
+        }
+    }
+}
+
+constexpr int kDirectThreads = 256;
+constexpr int kDirectUnroll = 4;
+
+template <typename U, typename Index>
+__global__ void __launch_bounds__(kDirectThreads)
+assign_direct_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                     const __grid_constant__ Axes ax, uint64_t total) {
+    const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kDirectThreads * kDirectUnroll) + threadIdx.x;
+    U value[kDirectUnroll];
+    int64_t doff[kDirectUnroll];
+#pragma unroll
+    for (int j = 0; j < kDirectUnroll; ++j) {
+        const uint64_t g = base + static_cast<uint64_t>(j) * kDirectThreads;
+        if (g < total) {
+            int64_t soff;
+            locate<Index>(ax, static_cast<Index>(g), doff[j], soff);
+            value[j] = *reinterpret_cast<const U *>(src + soff);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kDirectUnroll; ++j) {
+        const uint64_t g = base + static_cast<uint64_t>(j) * kDirectThreads;
+        if (g < total) *reinterpret_cast<U *>(dst + doff[j]) = value[j];
+    }
+}
+
+// Tiles over (axis p = ax.n-1, the fastest in the destination; axis q, the densest
+// in the source).  Blocks enumerate (other axes..., q tiles, p tiles).
+constexpr int kTile = 32;
+constexpr int kTileRows = 8;
+
+template <typename U>
+struct TileStorage {
+    // a row pitch of 33 units keeps the column reads of 4-byte units conflict-free
+    U cell[kTile][kTile + 1];
+};
+
+template <typename U, typename Index>
+__global__ void __launch_bounds__(kTile * kTileRows)
+assign_tiled_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                    const __grid_constant__ Axes ax, int q, int64_t tiles_p, int64_t tiles_q) {
+    __shared__ TileStorage<U> tile;
+    const int p = ax.n - 1;
+    // block -> (rest, tq, tp)
+    uint64_t b = blockIdx.x;
+    const int64_t tp = static_cast<int64_t>(b % static_cast<uint64_t>(tiles_p));
+    b /= static_cast<uint64_t>(tiles_p);
+    const int64_t tq = static_cast<int64_t>(b % static_cast<uint64_t>(tiles_q));
+    Index rest = static_cast<Index>(b / static_cast<uint64_t>(tiles_q));
+    int64_t dbase = 0, sbase = 0;
+#pragma unroll
+    for (int k = kMaxAxes - 1; k >= 0; --k) {
+        if (k < ax.n && k != p && k != q) {
+            const Index len = static_cast<Index>(ax.len[k]);
+            const Index quo = rest / len;
+            const Index i = rest - quo * len;
+            rest = quo;
+            dbase += static_cast<int64_t>(i) * ax.dst_step[k];
+            sbase += static_cast<int64_t>(i) * ax.src_step[k];
+        }
+    }
+    const int64_t p0 = tp * kTile, q0 = tq * kTile;
+    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x / kTile;
+    // load: lanes along q (dense in the source), rows along p
+    {
+        const int64_t iq = q0 + tx;
+#pragma unroll
+        for (int j = 0; j < kTile / kTileRows; ++j) {
+            const int row = ty + j * kTileRows;
+            const int64_t ip = p0 + row;
+            if (iq < ax.len[q] && ip < ax.len[p])
+                tile.cell[row][tx] =
+                    *reinterpret_cast<const U *>(src + sbase + ip * ax.src_step[p] + iq * ax.src_step[q]);
+        }
+    }
+    __syncthreads();
+    // store: lanes along p (dense in the destination), rows along q
+    {
+        const int64_t ip = p0 + tx;
+#pragma unroll
+        for (int j = 0; j < kTile / kTileRows; ++j) {
+            const int row = ty + j * kTileRows;
+            const int64_t iq = q0 + row;
+            if (iq < ax.len[q] && ip < ax.len[p])
+                *reinterpret_cast<U *>(dst + dbase + ip * ax.dst_step[p] + iq * ax.dst_step[q]) =
+                    tile.cell[tx][row];
+        }
+    }
+}
+
+int64_t iabs64(int64_t v) { return v < 0 ? -v : v; }
+
+template <typename U>
+int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool narrow_index, int q,
+                cudaStream_t stream) {
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    if (q >= 0) {
+        const int p = ax.n - 1;
+        const int64_t tiles_p = (ax.len[p] + kTile - 1) / kTile;
+        const int64_t tiles_q = (ax.len[q] + kTile - 1) / kTile;
+        uint64_t rest = 1;
+        for (int k = 0; k < ax.n; ++k)
+            if (k != p && k != q) rest *= static_cast<uint64_t>(ax.len[k]);
+        const uint64_t blocks = rest * static_cast<uint64_t>(tiles_p) * static_cast<uint64_t>(tiles_q);
+        if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many tiles");
+        if (narrow_index)
+            assign_tiled_kernel<U, uint32_t><<<static_cast<unsigned>(blocks), kTile * kTileRows, 0, stream>>>(
+                d, s, ax, q, tiles_p, tiles_q);
+        else
+            assign_tiled_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kTile * kTileRows, 0, stream>>>(
+                d, s, ax, q, tiles_p, tiles_q);
+    } else {
+        const uint64_t per_block = kDirectThreads * kDirectUnroll;
+        const uint64_t blocks = (total + per_block - 1) / per_block;
+        if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many units");
+        if (narrow_index)
+            assign_direct_kernel<U, uint32_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
+                d, s, ax, total);
+        else
+            assign_direct_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
+                d, s, ax, total);
+    }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
+    return B2K_OK;
+}
+
+}  // namespace
+
+extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *shape, const int64_t *dst_strides,
+                          const int64_t *src_strides, int64_t itemsize, void *stream) {
+    if (ndim < 0 || ndim > 32) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: ndim %d outside 0..32", ndim);
+    if (itemsize <= 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: itemsize must be positive");
+    if (ndim > 0 && (!shape || !dst_strides || !src_strides))
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null shape or strides");
+
+    struct Axis {
+        int64_t len, ds, ss;
+    };
+    Axis axes[34];
+    int n = 0;
+    for (int k = 0; k < ndim; ++k) {
+        if (shape[k] < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: negative extent");
+        if (shape[k] == 0) return B2K_OK;
+        if (shape[k] == 1) continue;
+        if (dst_strides[k] == 0)
+            return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: destination stride 0 on axis %d of length %lld", k,
+                             static_cast<long long>(shape[k]));
+        axes[n++] = Axis{shape[k], dst_strides[k], src_strides[k]};
+    }
+    if (!dst || !src) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null pointer");
+
+    // densest destination axis last; equal strides keep their given order
+    std::stable_sort(axes, axes + n, [](const Axis &a, const Axis &b) { return iabs64(a.ds) > iabs64(b.ds); });
+    // the item itself: one more axis of bytes, dense on both sides
+    axes[n++] = Axis{itemsize, 1, 1};
+    // merge neighbours that are contiguous on both sides
+    int m = 0;
+    for (int k = 0; k < n; ++k) {
+        if (m > 0 && axes[m - 1].ds == axes[k].len * axes[k].ds && axes[m - 1].ss == axes[k].len * axes[k].ss) {
+            axes[m - 1].len *= axes[k].len;
+            axes[m - 1].ds = axes[k].ds;
+            axes[m - 1].ss = axes[k].ss;
+        } else {
+            axes[m++] = axes[k];
+        }
+    }
+    n = m;
+    // widest unit: divides the dense run, both addresses and every other step
+    int64_t unit = 16;
+    auto fits = [&](int64_t u) {
+        if (axes[n - 1].len % u) return false;
+        if (reinterpret_cast<uintptr_t>(dst) % u || reinterpret_cast<uintptr_t>(src) % u) return false;
+        for (int k = 0; k + 1 < n; ++k)
+            if (axes[k].ds % u || axes[k].ss % u) return false;
+        return true;
+    };
+    while (unit > 1 && !fits(unit)) unit /= 2;
+    axes[n - 1].len /= unit;
+    axes[n - 1].ds = unit;
+    axes[n - 1].ss = unit;
+    if (axes[n - 1].len == 1 && n > 1) --n;
+    if (n > kMaxAxes)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_assign: %d axes remain after merging (at most %d)", n, kMaxAxes);
+
+    Axes ax{};
+    ax.n = n;
+    uint64_t total = 1;
+    bool narrow = true;
+    for (int k = 0; k < n; ++k) {
+        ax.len[k] = axes[k].len;
+        ax.dst_step[k] = axes[k].ds;
+        ax.src_step[k] = axes[k].ss;
+        if (axes[k].len > 0xFFFFFFFFll) narrow = false;
+        if (total > (uint64_t(1) << 62) / static_cast<uint64_t>(axes[k].len))
+            return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: more than 2^62 units");
+        total *= static_cast<uint64_t>(axes[k].len);
+    }
+    if (total > 0xFFFFFFFFull) narrow = false;
+
+    // Source densest along another axis than the destination: go through tiles.
+    int q = -1;
+    if (n >= 2 && b2k::env_int("B2K_ASSIGN_TILED", 1) != 0) {
+        int best = -1;
+        for (int k = 0; k < n; ++k) {
+            if (ax.src_step[k] == 0) continue;
+            if (best < 0 || iabs64(ax.src_step[k]) < iabs64(ax.src_step[best])) best = k;
+        }
+        // worth it only when the source run along the destination's fastest axis is
+        // strided by more than a sector and both tile axes are long enough
+        if (best >= 0 && best != n - 1 && iabs64(ax.src_step[n - 1]) >= 32 && ax.len[best] >= 8 &&
+            ax.len[n - 1] >= 8)
+            q = best;
+    }
+
+    cudaStream_t st = b2k::as_stream(stream);
+    switch (unit) {
+    case 16: return launch_unit<uint4>(dst, src, ax, total, narrow, q, st);
+    case 8: return launch_unit<uint2>(dst, src, ax, total, narrow, q, st);
+    case 4: return launch_unit<uint32_t>(dst, src, ax, total, narrow, q, st);
+    case 2: return launch_unit<uint16_t>(dst, src, ax, total, narrow, q, st);
+    default: return launch_unit<uint8_t>(dst, src, ax, total, narrow, q, st);
+    }
+}

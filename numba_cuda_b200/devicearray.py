@@ -325,27 +325,44 @@ class DeviceNDArray:
         return self.__getitem__(item)
 
     def __setitem__(self, key, value):
-        shape, strides, offset = _basic_index(self.shape, self.strides, key)
-        if len(shape) == 0:
-            shape, strides = (1,), (self.dtype.itemsize,)
-        target = self._sub(shape, strides, offset)
-        if isinstance(value, DeviceNDArray):
-            value = value.copy_to_host()
-        host = np.broadcast_to(np.asarray(value, dtype=self.dtype), shape)
-        if target.flags["C_CONTIGUOUS"]:
-            target.copy_to_device(np.ascontiguousarray(host))
-        elif target.flags["F_CONTIGUOUS"]:
-            target.copy_to_device(np.asfortranarray(host))
-        else:
-            # strided target: read-modify-write of the spanned bytes
-            raw = np.empty(target.alloc_size, dtype=np.uint8)
-            with torch.cuda.stream(_torch_stream(self.stream)):
-                torch.from_numpy(raw).copy_(target._bytes_view())
-                np.ndarray(shape=shape, dtype=self.dtype, strides=strides, buffer=raw)[...] = host
-                target._bytes_view().copy_(torch.from_numpy(raw))
+        return self._do_setitem(key, value)
 
     def setitem(self, key, value, stream=0):
-        self.__setitem__(key, value)
+        """Do `__setitem__(key, value)` with CUDA stream"""
+        return self._do_setitem(key, value, stream=stream)
+
+    def _do_setitem(self, key, value, stream=0):
+        """Broadcasting assignment on the device (devicearray.py:735-791): the
+        left side is the indexed view, the right side any device array, host
+        array or scalar with at most as many axes; axes of length 1 repeat.
+        One ``b2k_assign`` launch; synchronous when no stream is involved."""
+        stream = self._default_stream(stream)
+        synchronous = not stream
+        shape, strides, offset = _basic_index(self.shape, self.strides, key)
+        lhs = self._sub(shape, strides, offset)
+
+        if isinstance(value, DeviceNDArray) or hasattr(value, "__cuda_array_interface__"):
+            rhs = value if isinstance(value, DeviceNDArray) else from_cuda_array_interface(value)
+            if rhs.dtype != self.dtype:
+                # values are converted like a NumPy assignment would; on the host
+                rhs = _upload(np.asarray(rhs.copy_to_host()).astype(self.dtype), stream)
+        else:
+            host = np.asarray(value)
+            if host.dtype != self.dtype:
+                host = host.astype(self.dtype)
+            rhs = _upload(host, stream)
+        if rhs.ndim > lhs.ndim:
+            raise ValueError("Can't assign %s-D array to %s-D self" % (rhs.ndim, lhs.ndim))
+        lead = lhs.ndim - rhs.ndim
+        rhs_shape = (1,) * lead + tuple(rhs.shape)
+        rhs_strides = (0,) * lead + tuple(rhs.strides)
+        for i, (l, r) in enumerate(zip(lhs.shape, rhs_shape)):
+            if r != 1 and l != r:
+                raise ValueError("Can't copy sequence with size %d to array axis %d with dimension %d" % (r, i, l))
+        src_strides = tuple(0 if r == 1 else st for r, st in zip(rhs_shape, rhs_strides))
+        assign_strided(lhs._ptr, rhs._ptr, lhs.shape, lhs.strides, src_strides, self.dtype.itemsize, stream)
+        if synchronous:
+            torch.cuda.current_stream().synchronize()
 
     def reshape(self, *newshape, order="C"):
         if len(newshape) == 1 and isinstance(newshape[0], (tuple, list)):
@@ -408,6 +425,33 @@ _TORCH_DTYPES = {
     "<f2": torch.float16, "<f4": torch.float32, "<f8": torch.float64, "|b1": torch.bool,
     "<c8": torch.complex64, "<c16": torch.complex128, "bfloat16": torch.bfloat16,
 }
+
+
+def _upload(host: np.ndarray, stream=0) -> "DeviceNDArray":
+    """A C-contiguous host array (0-d included) as a new device array."""
+    if not host.flags["C_CONTIGUOUS"]:      # (ascontiguousarray would turn a 0-d array into a 1-d one)
+        host = np.ascontiguousarray(host)
+    dev = DeviceNDArray(host.shape, _c_strides(host.shape, host.dtype.itemsize), host.dtype, stream=stream)
+    if host.size:
+        raw = host.reshape(-1).view(np.uint8) if host.dtype.itemsize else host.reshape(-1)
+        with torch.cuda.stream(_torch_stream(stream)):
+            dev._buf[dev._offset:dev._offset + raw.size].copy_(
+                torch.from_numpy(raw if raw.flags.writeable else raw.copy()))
+    return dev
+
+
+def assign_strided(dst_ptr, src_ptr, shape, dst_strides, src_strides, itemsize, stream=0):
+    """``dst[idx] = src[idx]`` over ``shape`` with byte strides on both sides
+    (source stride 0 = broadcast): one ``b2k_assign`` launch."""
+    import ctypes
+    from . import _lib
+    nd = len(shape)
+    if any(int(n) == 0 for n in shape):
+        return
+    arr = ctypes.c_int64 * max(nd, 1)
+    _lib.check(_lib.lib().b2k_assign(
+        dst_ptr, src_ptr, nd, arr(*[int(v) for v in shape]), arr(*[int(v) for v in dst_strides]),
+        arr(*[int(v) for v in src_strides]), int(itemsize), stream_ptr(stream)))
 
 
 def _host_bytes(host: np.ndarray) -> np.ndarray:

@@ -1,0 +1,167 @@
+"""Device-side broadcasting assignment and N-D axis permutation (b2k_assign)
+against NumPy, which is what the reference's own array tests compare with
+(numba/cuda/tests/cudadrv/test_cuda_ndarray.py and test_cuda_array_slicing.py:
+``assert_array_equal`` after ``d_arr[key] = value``)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+import numba_cuda_b200 as cuda  # noqa: E402
+from numba_cuda_b200 import _lib  # noqa: E402
+from numba_cuda_b200.kernels.transpose import permute  # noqa: E402
+
+REC = np.dtype([("i", np.int32), ("j", np.float32, (3, 2))], align=True)   # 28 bytes
+
+
+def _filled(shape, dtype, seed=0):
+    rng = np.random.default_rng(seed)
+    dtype = np.dtype(dtype)
+    n = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+    raw = rng.integers(0, 256, size=n * dtype.itemsize, dtype=np.uint8)
+    return raw.view(dtype).reshape(shape).copy()
+
+
+SETITEM_CASES = [
+    # (shape, key, value shape or None for a scalar)
+    ((10,), slice(None), None),
+    ((10,), 3, None),
+    ((10,), slice(2, 9, 3), (3,)),
+    ((10,), slice(None, None, -1), (10,)),
+    ((6, 7), (slice(None), 2), (6,)),
+    ((6, 7), (1, slice(None)), (7,)),
+    ((6, 7), (slice(1, 5), slice(None, None, 2)), (4, 4)),
+    ((6, 7), (slice(1, 5), slice(None, None, 2)), (1, 4)),
+    ((6, 7), (slice(1, 5), slice(None, None, 2)), (4, 1)),
+    ((6, 7), (slice(1, 5), slice(None, None, 2)), (4,)),
+    ((6, 7), (slice(None, None, -2), slice(None, None, -1)), (3, 7)),
+    ((4, 5, 6), (slice(None), 2), (4, 6)),
+    ((4, 5, 6), (Ellipsis, 0), (4, 5)),
+    ((4, 5, 6), (slice(None), slice(None), slice(None)), (5, 6)),
+    ((4, 5, 6), (2, 3, 4), None),
+    ((3, 4, 5, 6, 2), (slice(None), slice(1, 3), Ellipsis, slice(None, None, 2), 1), (3, 2, 5, 3)),
+    ((257, 130), (slice(None), slice(None)), (257, 130)),
+    ((257, 130), (slice(3, 250, 5), slice(1, 129)), (1, 128)),
+]
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int16, np.float32, np.float64, np.complex128, REC])
+@pytest.mark.parametrize("shape,key,vshape", SETITEM_CASES)
+def test_setitem_matches_numpy(dtype, shape, key, vshape):
+    host = _filled(shape, dtype, 1)
+    value = _filled(() if vshape is None else vshape, dtype, 2)
+    if vshape is None:
+        value = value[()]
+    dev = cuda.to_device(host)
+    dev[key] = value
+    host[key] = value
+    assert dev.copy_to_host().tobytes() == host.tobytes()
+
+
+def test_setitem_from_device_arrays_and_views():
+    host = _filled((64, 96), np.float32, 3)
+    other = _filled((64, 96), np.float32, 4)
+    dev, dother = cuda.to_device(host), cuda.to_device(other)
+    dev[::2, 1:90] = dother[1::2, 5:94]          # both sides strided views
+    host[::2, 1:90] = other[1::2, 5:94]
+    assert dev.copy_to_host().tobytes() == host.tobytes()
+    dev[:, 0] = dother[7, :64]                    # a row into a column
+    host[:, 0] = other[7, :64]
+    assert dev.copy_to_host().tobytes() == host.tobytes()
+    import torch
+    t = torch.arange(96, dtype=torch.float32, device="cuda")
+    dev[5] = t                                     # any CUDA-array-interface exporter
+    host[5] = np.arange(96, dtype=np.float32)
+    assert dev.copy_to_host().tobytes() == host.tobytes()
+
+
+def test_setitem_converts_values_like_numpy():
+    host = np.zeros((4, 5), dtype=np.int32)
+    dev = cuda.to_device(host)
+    dev[1] = 7.9                       # Python float into int32
+    host[1] = 7.9
+    dev[:, 2] = np.arange(4, dtype=np.int64) * 1000
+    host[:, 2] = np.arange(4, dtype=np.int64) * 1000
+    dev[3] = cuda.to_device(np.arange(5, dtype=np.float64))
+    host[3] = np.arange(5, dtype=np.float64)
+    assert (dev.copy_to_host() == host).all()
+
+
+def test_setitem_errors_follow_the_reference():
+    dev = cuda.to_device(np.zeros((4, 5), dtype=np.float32))
+    with pytest.raises(ValueError, match="Can't assign 3-D array to 2-D self"):
+        dev[:, :] = np.zeros((1, 4, 5), dtype=np.float32)
+    with pytest.raises(ValueError, match="Can't copy sequence with size 3 to array axis 1 with dimension 5"):
+        dev[:, :] = np.zeros((4, 3), dtype=np.float32)
+    with pytest.raises(IndexError):
+        dev[4, 0] = 1.0
+
+
+def test_setitem_with_stream():
+    s = cuda.stream()
+    host = _filled((33, 65), np.float64, 5)
+    dev = cuda.to_device(host, stream=s)
+    dev.setitem((slice(None), slice(0, 64, 2)), 1.5, stream=s)
+    s.synchronize()
+    host[:, 0:64:2] = 1.5
+    assert dev.copy_to_host().tobytes() == host.tobytes()
+
+
+PERMUTE_CASES = [
+    ((5, 6), None), ((5, 6), (0, 1)), ((3, 4, 5), None), ((3, 4, 5), (0, 2, 1)), ((3, 4, 5), (1, 0, 2)),
+    ((3, 4, 5), (2, 0, 1)), ((3, 4, 5), (1, 2, 0)), ((2, 3, 4, 5), (3, 1, 0, 2)), ((2, 3, 4, 5), (0, 1, 3, 2)),
+    ((7, 1, 9), (2, 1, 0)), ((2, 3, 2, 3, 2, 3), (5, 3, 1, 4, 2, 0)), ((40, 50, 60), (2, 1, 0)),
+    ((40, 50, 60), (1, 0, 2)), ((33, 70, 130), (0, 2, 1)), ((16, 8, 64, 64), (0, 2, 1, 3)),
+    ((0, 4, 5), (2, 0, 1)), ((), ()), ((9,), (0,)),
+]
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.uint16, np.float32, np.float64, np.complex128, REC])
+@pytest.mark.parametrize("shape,axes", PERMUTE_CASES)
+def test_permute_matches_numpy(dtype, shape, axes):
+    host = _filled(shape, dtype, 6)
+    got = permute(cuda.to_device(host), axes)
+    want = host.transpose(axes).copy(order="C")
+    assert got.shape == want.shape and got.is_c_contiguous()
+    assert got.copy_to_host().tobytes() == want.tobytes()
+
+
+def test_permute_of_a_strided_view_into_a_given_array_and_errors():
+    host = _filled((20, 30, 40), np.float32, 7)
+    dev = cuda.to_device(host)
+    view = dev[2:18:3, ::-1, 4:36]
+    out = cuda.device_array((32, 6, 30), dtype=np.float32)
+    assert permute(view, (2, 0, 1), out) is out
+    want = np.ascontiguousarray(host[2:18:3, ::-1, 4:36].transpose(2, 0, 1))
+    assert out.copy_to_host().tobytes() == want.tobytes()
+    with pytest.raises(ValueError, match="invalid axes list"):
+        permute(dev, (0, 0, 1))
+    with pytest.raises(ValueError, match="incompatible shape"):
+        permute(dev, (2, 0, 1), cuda.device_array((40, 30, 20), dtype=np.float32))
+    with pytest.raises(TypeError, match="incompatible dtype"):
+        permute(dev, (2, 0, 1), cuda.device_array((40, 20, 30), dtype=np.int32))
+
+
+def test_large_permutations_through_both_kernels():
+    # (batch, rows, cols) -> (batch, cols, rows): tiles; (a, b, c) -> (b, a, c): direct, wide units
+    host = _filled((8, 1000, 1100), np.float32, 8)
+    dev = cuda.to_device(host)
+    assert permute(dev, (0, 2, 1)).copy_to_host().tobytes() == np.ascontiguousarray(host.transpose(0, 2, 1)).tobytes()
+    assert permute(dev, (1, 0, 2)).copy_to_host().tobytes() == np.ascontiguousarray(host.transpose(1, 0, 2)).tobytes()
+    assert permute(dev, (2, 1, 0)).copy_to_host().tobytes() == np.ascontiguousarray(host.transpose(2, 1, 0)).tobytes()
+
+
+def test_c_abi_argument_checks():
+    L = _lib.lib()
+    arr3 = ctypes.c_int64 * 3
+    assert L.b2k_assign(None, None, 3, arr3(2, 0, 4), arr3(32, 16, 4), arr3(32, 16, 4), 4, None) == 0   # empty
+    assert L.b2k_assign(None, None, 3, arr3(2, 2, 4), arr3(32, 16, 4), arr3(32, 16, 4), 4, None) < 0    # null
+    assert L.b2k_assign(None, None, 40, None, None, None, 4, None) < 0
+    assert L.b2k_assign(None, None, 1, arr3(2, 0, 0), arr3(4, 0, 0), arr3(4, 0, 0), 0, None) < 0
+    assert b"itemsize" in L.b2k_last_error()
+    import torch
+    buf = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    rc = L.b2k_assign(buf.data_ptr(), buf.data_ptr() + 32, 1, arr3(4, 0, 0), arr3(0, 0, 0), arr3(4, 0, 0), 4, None)
+    assert rc < 0 and b"destination stride 0" in L.b2k_last_error()
