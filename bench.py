@@ -161,7 +161,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-paths", action="store_true", help="skip the secondary configurations")
-    ap.add_argument("--only", default=None, help="run a single path (profiling aid): c1,c2,c3a,c3b,c4,c5")
+    ap.add_argument("--only", default=None, help="run a single path (profiling aid): c1,c2,c3a,c3b,c4,c5,n2")
     ap.add_argument("--scale", type=int, default=0, help="shrink the --only workload by 2^scale (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -381,6 +381,19 @@ def secondary_cpu_baselines():
     dt, _ = clock(lambda: np.ascontiguousarray(a.T))
     out["c3a_transpose_f32"] = {"GBps": 2 * a.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
                                 "sample": "4096x4096 float32 block, np.ascontiguousarray(a.T)"}
+    # assignment / permutation: the simulator's device array is a NumPy array underneath
+    src = np.random.default_rng(4).standard_normal(1 << 24, dtype=np.float32)
+    dst = np.empty_like(src)
+
+    def copy():
+        dst[:] = src
+    dt, _ = clock(copy)
+    out["n2_assign_copy_f32"] = {"GBps": 2 * src.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                 "sample": "2^24 of the 2^28 float32, NumPy slice assignment"}
+    cube = src.reshape(64, 512, 512)
+    dt, _ = clock(lambda: np.ascontiguousarray(cube.transpose(0, 2, 1)))
+    out["n4_permute_021_f32"] = {"GBps": 2 * src.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                 "sample": "64x512x512 float32, np.ascontiguousarray(a.transpose(0, 2, 1))"}
     # C4: serial state chain (random.py:242-257) and the draw loop, C restatement
     n = 1 << 16
     dt, st = clock(lambda: oracle.init_states(n, 42, 0))
@@ -499,6 +512,47 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
                                                                0, None, 0, sptr)), iters, warm)
         res["rng_uniform_f32_only_64"] = dict(_roof(n * (32 + 256), ms_u, peak), Gsamples_per_s=n * 64 / ms_u / 1e6)
         del u, z, states
+
+    if want("n2"):
+        # the callers either side of the path: device-side assignment (slice copies,
+        # fills) and N-D axis permutations, all through b2k_assign
+        import ctypes
+
+        def assign(dst, src, shape, dstr, sstr, item):
+            arr = ctypes.c_int64 * len(shape)
+            check(L.b2k_assign(dst, src, len(shape), arr(*shape), arr(*dstr), arr(*sstr), item, sptr))
+
+        def c_steps(shape, item):
+            steps = [item] * len(shape)
+            for k in range(len(shape) - 2, -1, -1):
+                steps[k] = steps[k + 1] * shape[k + 1]
+            return steps
+
+        n = 1 << (28 - scale)
+        a = torch.randn(n, device="cuda")
+        b = torch.empty(n, device="cuda")
+        ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [n], [4], [4], 4), iters, warm)
+        res["n2_assign_copy_f32_2p28"] = dict(_roof(n * 8, ms, peak), spot_check=bool(torch.equal(a[:4096], b[:4096])))
+        ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [n], [4], [0], 4), iters, warm)
+        res["n2_assign_fill_scalar_f32_2p28"] = dict(_roof(n * 4, ms, peak), note="write-only: 4 B per item",
+                                                     spot_check=bool((b[-4096:] == a[0]).all()))
+        rows = 16384 >> scale
+        ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [rows // 2, 16384], [2 * 65536, 4], [2 * 65536, 4], 4),
+                      iters, warm)
+        res["n2_assign_every_other_row_f32"] = _roof(rows // 2 * 16384 * 8, ms, peak)
+        for label, shape, perm in (("n4_permute_021_f32_64x2048x2048", [64 >> scale, 2048, 2048], (0, 2, 1)),
+                                   ("n4_permute_102_f32_2048x64x2048", [2048 >> scale, 64, 2048], (1, 0, 2)),
+                                   ("n4_permute_210_f32_512x512x1024", [512 >> scale, 512, 1024], (2, 1, 0))):
+            count = shape[0] * shape[1] * shape[2]
+            src = a[:count].view(shape)
+            in_steps = c_steps(shape, 4)
+            out_shape = [shape[k] for k in perm]
+            ms, _ = timed(lambda: assign(b.data_ptr(), src.data_ptr(), out_shape, c_steps(out_shape, 4),
+                                         [in_steps[k] for k in perm], 4), iters, warm)
+            got = b[:count].view(out_shape)
+            res[label] = dict(_roof(count * 8, ms, peak),
+                              spot_check=bool(torch.equal(got[:2, :64], src.permute(perm)[:2, :64])))
+        del a, b
 
     if want("c5"):
         n = 1 << (30 - scale)

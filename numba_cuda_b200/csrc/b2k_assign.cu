@@ -9,15 +9,19 @@
 // stride (assignment has no order of its own, so the axis that is densest in the
 // destination becomes the fastest one), neighbouring axes that are contiguous on
 // both sides are merged, and the innermost axis is regrouped into the widest unit
-// (16, 8, 4, 2 or 1 bytes) that every pointer and stride allows.  Two kernels:
+// (16, 8, 4, 2 or 1 bytes) that every pointer and stride allows.  Kernels:
 //
 //  * direct: one thread per unit, four units in flight per thread, consecutive
 //    threads on consecutive units of the fastest destination axis.  Reads are
 //    coalesced too whenever the source is dense along the same axis (slices,
 //    row / scalar broadcasts, plain copies);
+//  * fill: the source repeats along the fastest destination axis (scalar and
+//    per-row fills): the unit is replicated into 16-byte stores;
 //  * tiled: when the source is dense along a DIFFERENT axis q than the destination
-//    (axis permutations), 32x32-unit tiles over (destination axis p, source axis q)
-//    go through shared memory so that both sides see coalesced accesses.
+//    (axis permutations), square tiles over (destination axis p, source axis q)
+//    go through shared memory so that both sides see coalesced accesses;
+//  * the TMA tile transpose of b2k_transpose_tma.cu, as a stack of 2-D problems,
+//    when such a permutation also meets the tensor-map alignment rules.
 #include <algorithm>
 
 #include "b2k_internal.cuh"
@@ -76,22 +80,45 @@ assign_direct_kernel(unsigned char *__restrict__ dst, const unsigned char *__res
     }
 }
 
+// The source repeats along the fastest destination axis (row fills, scalar fills):
+// a thread reads one source unit S and stores it replicated into a 16-byte unit.
+template <typename S, typename Index>
+__global__ void __launch_bounds__(kDirectThreads)
+assign_fill_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                   const __grid_constant__ Axes ax, uint64_t total) {
+    constexpr int REP = 16 / sizeof(S);
+    const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kDirectThreads * kDirectUnroll) + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < kDirectUnroll; ++j) {
+        const uint64_t g = base + static_cast<uint64_t>(j) * kDirectThreads;
+        if (g < total) {
+            int64_t doff, soff;
+            locate<Index>(ax, static_cast<Index>(g), doff, soff);
+            union {
+                uint4 wide;
+                S part[REP];
+            } v;
+            const S one = *reinterpret_cast<const S *>(src + soff);
+#pragma unroll
+            for (int k = 0; k < REP; ++k) v.part[k] = one;
+            *reinterpret_cast<uint4 *>(dst + doff) = v.wide;
+        }
+    }
+}
+
 // Tiles over (axis p = ax.n-1, the fastest in the destination; axis q, the densest
-// in the source).  Blocks enumerate (other axes..., q tiles, p tiles).
-constexpr int kTile = 32;
-constexpr int kTileRows = 8;
+// in the source).  Blocks enumerate (other axes..., q tiles, p tiles).  TILE = 64
+// for units up to 4 bytes (16 loads in flight per thread), 32 for wider units.
+constexpr int kTiledThreads = 256;
 
-template <typename U>
-struct TileStorage {
-    // a row pitch of 33 units keeps the column reads of 4-byte units conflict-free
-    U cell[kTile][kTile + 1];
-};
-
-template <typename U, typename Index>
-__global__ void __launch_bounds__(kTile * kTileRows)
+template <typename U, typename Index, int TILE>
+__global__ void __launch_bounds__(kTiledThreads)
 assign_tiled_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
                     const __grid_constant__ Axes ax, int q, int64_t tiles_p, int64_t tiles_q) {
-    __shared__ TileStorage<U> tile;
+    // a row pitch of TILE + 1 units keeps the column reads of 4-byte units conflict-free
+    __shared__ U cell[TILE][TILE + 1];
+    constexpr int ROWS = kTiledThreads / TILE;  // tile rows covered per pass
+    constexpr int PASSES = TILE / ROWS;
     const int p = ax.n - 1;
     // block -> (rest, tq, tp)
     uint64_t b = blockIdx.x;
@@ -111,31 +138,31 @@ assign_tiled_kernel(unsigned char *__restrict__ dst, const unsigned char *__rest
             sbase += static_cast<int64_t>(i) * ax.src_step[k];
         }
     }
-    const int64_t p0 = tp * kTile, q0 = tq * kTile;
-    const int tx = threadIdx.x & (kTile - 1), ty = threadIdx.x / kTile;
+    const int64_t p0 = tp * TILE, q0 = tq * TILE;
+    const int64_t np = ax.len[p] - p0, nq = ax.len[q] - q0;  // extent left along each tile axis
+    const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
     // load: lanes along q (dense in the source), rows along p
     {
-        const int64_t iq = q0 + tx;
+        const unsigned char *from = src + sbase + p0 * ax.src_step[p] + (q0 + tx) * ax.src_step[q];
+        const int64_t row_step = ax.src_step[p];
+        U held[PASSES];
 #pragma unroll
-        for (int j = 0; j < kTile / kTileRows; ++j) {
-            const int row = ty + j * kTileRows;
-            const int64_t ip = p0 + row;
-            if (iq < ax.len[q] && ip < ax.len[p])
-                tile.cell[row][tx] =
-                    *reinterpret_cast<const U *>(src + sbase + ip * ax.src_step[p] + iq * ax.src_step[q]);
+        for (int j = 0; j < PASSES; ++j) {
+            const int row = ty + j * ROWS;
+            if (tx < nq && row < np) held[j] = *reinterpret_cast<const U *>(from + row * row_step);
         }
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) cell[ty + j * ROWS][tx] = held[j];
     }
     __syncthreads();
     // store: lanes along p (dense in the destination), rows along q
     {
-        const int64_t ip = p0 + tx;
+        unsigned char *to = dst + dbase + (p0 + tx) * ax.dst_step[p] + q0 * ax.dst_step[q];
+        const int64_t row_step = ax.dst_step[q];
 #pragma unroll
-        for (int j = 0; j < kTile / kTileRows; ++j) {
-            const int row = ty + j * kTileRows;
-            const int64_t iq = q0 + row;
-            if (iq < ax.len[q] && ip < ax.len[p])
-                *reinterpret_cast<U *>(dst + dbase + ip * ax.dst_step[p] + iq * ax.dst_step[q]) =
-                    tile.cell[tx][row];
+        for (int j = 0; j < PASSES; ++j) {
+            const int row = ty + j * ROWS;
+            if (tx < np && row < nq) *reinterpret_cast<U *>(to + row * row_step) = cell[tx][row];
         }
     }
 }
@@ -148,19 +175,20 @@ int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool
     unsigned char *d = static_cast<unsigned char *>(dst);
     const unsigned char *s = static_cast<const unsigned char *>(src);
     if (q >= 0) {
+        constexpr int TILE = sizeof(U) <= 4 ? 64 : 32;
         const int p = ax.n - 1;
-        const int64_t tiles_p = (ax.len[p] + kTile - 1) / kTile;
-        const int64_t tiles_q = (ax.len[q] + kTile - 1) / kTile;
+        const int64_t tiles_p = (ax.len[p] + TILE - 1) / TILE;
+        const int64_t tiles_q = (ax.len[q] + TILE - 1) / TILE;
         uint64_t rest = 1;
         for (int k = 0; k < ax.n; ++k)
             if (k != p && k != q) rest *= static_cast<uint64_t>(ax.len[k]);
         const uint64_t blocks = rest * static_cast<uint64_t>(tiles_p) * static_cast<uint64_t>(tiles_q);
         if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many tiles");
         if (narrow_index)
-            assign_tiled_kernel<U, uint32_t><<<static_cast<unsigned>(blocks), kTile * kTileRows, 0, stream>>>(
+            assign_tiled_kernel<U, uint32_t, TILE><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
                 d, s, ax, q, tiles_p, tiles_q);
         else
-            assign_tiled_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kTile * kTileRows, 0, stream>>>(
+            assign_tiled_kernel<U, uint64_t, TILE><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
                 d, s, ax, q, tiles_p, tiles_q);
     } else {
         const uint64_t per_block = kDirectThreads * kDirectUnroll;
@@ -173,6 +201,23 @@ int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool
             assign_direct_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
                 d, s, ax, total);
     }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
+    return B2K_OK;
+}
+
+template <typename S>
+int launch_fill(void *dst, const void *src, const Axes &ax, uint64_t total, bool narrow_index,
+                cudaStream_t stream) {
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    const uint64_t per_block = kDirectThreads * kDirectUnroll;
+    const uint64_t blocks = (total + per_block - 1) / per_block;
+    if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many units");
+    if (narrow_index)
+        assign_fill_kernel<S, uint32_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(d, s, ax, total);
+    else
+        assign_fill_kernel<S, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(d, s, ax, total);
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
     return B2K_OK;
@@ -251,7 +296,30 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
     }
     if (total > 0xFFFFFFFFull) narrow = false;
 
-    // Source densest along another axis than the destination: go through tiles.
+    cudaStream_t st = b2k::as_stream(stream);
+
+    // The source repeats along the fastest axis and the destination is dense there:
+    // store the repeated unit 16 bytes at a time where the rows allow it.
+    if (unit < 16 && ax.src_step[n - 1] == 0 && ax.dst_step[n - 1] == unit) {
+        const int64_t rep = 16 / unit;
+        bool wide = ax.len[n - 1] % rep == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+        for (int k = 0; k + 1 < n; ++k)
+            if (ax.dst_step[k] % 16) wide = false;
+        if (wide) {
+            Axes fill = ax;
+            fill.len[n - 1] /= rep;
+            fill.dst_step[n - 1] = 16;
+            const uint64_t units = total / static_cast<uint64_t>(rep);
+            switch (unit) {
+            case 8: return launch_fill<uint2>(dst, src, fill, units, narrow, st);
+            case 4: return launch_fill<uint32_t>(dst, src, fill, units, narrow, st);
+            case 2: return launch_fill<uint16_t>(dst, src, fill, units, narrow, st);
+            default: return launch_fill<uint8_t>(dst, src, fill, units, narrow, st);
+            }
+        }
+    }
+
+    // Source densest along another axis q than the destination (an axis permutation).
     int q = -1;
     if (n >= 2 && b2k::env_int("B2K_ASSIGN_TILED", 1) != 0) {
         int best = -1;
@@ -265,8 +333,26 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
             ax.len[n - 1] >= 8)
             q = best;
     }
+    // Both sides dense along their own axis, everything 16-byte aligned, at most
+    // three further axes: a stack of 2-D transposes for the TMA tile kernel.
+    if (q >= 0 && n <= 5 && ax.dst_step[n - 1] == unit && ax.src_step[q] == unit && ax.len[q] >= 32 &&
+        ax.len[n - 1] >= 32 && total * static_cast<uint64_t>(unit) >= (1u << 20) &&
+        b2k::env_int("B2K_ASSIGN_TMA", 1) != 0) {
+        int64_t blen[3], istep[3], ostep[3];
+        int nb = 0;
+        for (int k = n - 2; k >= 0; --k) {  // fastest batch axis first
+            if (k == q) continue;
+            blen[nb] = ax.len[k];
+            istep[nb] = ax.src_step[k];
+            ostep[nb] = ax.dst_step[k];
+            ++nb;
+        }
+        // in = rows (axis p) x cols (axis q, dense); out = cols x rows (axis p dense)
+        const int rc = b2k::transpose_tma_batched(src, dst, ax.len[n - 1], ax.len[q], ax.src_step[n - 1],
+                                                  ax.dst_step[q], nb, blen, istep, ostep, unit, st);
+        if (rc != B2K_ERR_UNSUPPORTED) return rc;
+    }
 
-    cudaStream_t st = b2k::as_stream(stream);
     switch (unit) {
     case 16: return launch_unit<uint4>(dst, src, ax, total, narrow, q, st);
     case 8: return launch_unit<uint2>(dst, src, ax, total, narrow, q, st);

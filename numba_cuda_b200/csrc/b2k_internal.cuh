@@ -26,6 +26,16 @@ inline bool aligned_to(const void *p, size_t a) {
     return (reinterpret_cast<uintptr_t>(p) % a) == 0;
 }
 
+// TMA tile transposes (b2k_transpose_tma.cu).  Both return B2K_OK when they
+// launched, a positive cudaError_t when the launch failed, and B2K_ERR_UNSUPPORTED
+// when the arrays do not meet the tensor-map rules (the caller then takes a
+// general kernel).
+int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_stride0, int64_t in_stride1,
+                  int64_t out_stride0, int64_t out_stride1, int64_t itemsize, cudaStream_t stream);
+int transpose_tma_batched(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pitch,
+                          int64_t out_pitch, int nbatch, const int64_t *batch_len, const int64_t *in_batch_step,
+                          const int64_t *out_batch_step, int64_t itemsize, cudaStream_t stream);
+
 }  // namespace b2k
 
 #define B2K_RETURN_IF_LAUNCH_FAILED(what)                      \

@@ -7,15 +7,6 @@
 // b2k_transpose_tma.cu and is tried first.
 #include "b2k_internal.cuh"
 
-namespace b2k {
-// Defined in b2k_transpose_tma.cu.  Returns B2K_OK when it launched, a positive
-// cudaError_t on failure, or B2K_ERR_UNSUPPORTED when the layout does not meet
-// the tensor-map rules (the caller then uses the general kernels below).
-int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_stride0,
-                  int64_t in_stride1, int64_t out_stride0, int64_t out_stride1, int64_t itemsize,
-                  cudaStream_t stream);
-}  // namespace b2k
-
 namespace {
 
 constexpr int kTile = 32;

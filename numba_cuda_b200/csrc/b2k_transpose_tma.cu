@@ -75,6 +75,19 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int 
                  ::"l"(map), "r"(x), "r"(y), "r"(smem_addr(src))
                  : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(void *dst, const CUtensorMap *map, int x, int y, int b0, int b1,
+                                            int b2, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], "
+        "[%7];" ::"r"(smem_addr(dst)), "l"(map), "r"(x), "r"(y), "r"(b0), "r"(b1), "r"(b2), "r"(smem_addr(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap *map, int x, int y, int b0, int b1, int b2,
+                                             const void *src) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(b0), "r"(b1), "r"(b2), "r"(smem_addr(src))
+                 : "memory");
+}
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_wait_read() {
@@ -296,6 +309,142 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
     }
 }
 
+// The same pipeline over a stack of 2-D problems: up to three further axes (batch
+// axes) select the 2-D slice, tile numbers run slice by slice, and the tensor maps
+// are five-dimensional with a box depth of 1 along the batch axes.  This serves
+// N-D axis permutations whose source and destination are dense along two
+// different axes (b2k_assign).
+struct BatchSplit {
+    unsigned int tiles2d;     // tiles per 2-D slice
+    unsigned int len0, len1;  // lengths of the first two batch axes (the third takes the rest)
+    // one grid stride (gridDim.x tiles) as slice-local tiles plus batch steps, so
+    // that a CTA walks its tiles with additions instead of divisions
+    unsigned int adv_tile, adv0, adv1, adv2;
+};
+
+struct TileCoord {
+    int tx, ty, b0, b1, b2;
+};
+
+// Position of a CTA's next tile to load: tile number inside the slice and the
+// batch coordinates.
+struct TileCursor {
+    unsigned int id2, b0, b1, b2;
+
+    __device__ __forceinline__ void seek(const BatchSplit &bs, unsigned int id) {
+        const unsigned int b = id / bs.tiles2d;
+        id2 = id - b * bs.tiles2d;
+        const unsigned int q0 = b / bs.len0;
+        b0 = b - q0 * bs.len0;
+        const unsigned int q1 = q0 / bs.len1;
+        b1 = q0 - q1 * bs.len1;
+        b2 = q1;
+    }
+    __device__ __forceinline__ void advance(const BatchSplit &bs) {
+        id2 += bs.adv_tile;
+        unsigned int carry = id2 >= bs.tiles2d;
+        if (carry) id2 -= bs.tiles2d;
+        b0 += bs.adv0 + carry;
+        carry = b0 >= bs.len0;
+        if (carry) b0 -= bs.len0;
+        b1 += bs.adv1 + carry;
+        carry = b1 >= bs.len1;
+        if (carry) b1 -= bs.len1;
+        b2 += bs.adv2 + carry;
+    }
+    __device__ __forceinline__ TileCoord coord(const TileOrder &order) const {
+        TileCoord c;
+        order.coords(id2, c.tx, c.ty);
+        c.b0 = static_cast<int>(b0);
+        c.b1 = static_cast<int>(b1);
+        c.b2 = static_cast<int>(b2);
+        return c;
+    }
+};
+
+template <int ES, int R, int NSTAGE, int THREADS, int NOUT>
+__global__ void __launch_bounds__(THREADS)
+transpose_tma_batched_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
+                             const TileOrder order, const BatchSplit bs, long long tiles, int refill_thread) {
+    constexpr int TILE_BYTES = R * 128;
+    constexpr int TCOLS = 128 / ES;
+    constexpr int WORDS = ES > 4 ? ES / 4 : 1;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *base = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char *A = base;
+    unsigned char *B = base + NSTAGE * TILE_BYTES;
+    uint64_t *full = reinterpret_cast<uint64_t *>(B + NOUT * TILE_BYTES);
+    // where each staged tile goes: written when its load is issued, read when it is stored
+    __shared__ TileCoord staged[NSTAGE];
+
+    const long long first = blockIdx.x;
+    const long long step = gridDim.x;
+
+    TileCursor cursor{0, 0, 0, 0};
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < NSTAGE; ++s) mbar_init(&full[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+        cursor.seek(bs, static_cast<unsigned int>(first));
+#pragma unroll
+        for (int s = 0; s < NSTAGE; ++s) {
+            const long long id = first + s * step;
+            if (id < tiles) {
+                const TileCoord c = cursor.coord(order);
+                staged[s] = c;
+                mbar_expect_tx(&full[s], TILE_BYTES);
+                tma_load_5d(A + s * TILE_BYTES, &in_map, c.tx * (TCOLS * WORDS), c.ty * R, c.b0, c.b1, c.b2,
+                            &full[s]);
+                cursor.advance(bs);
+            }
+        }
+    }
+    __syncthreads();
+
+    // Thread 0 issues everything (the launcher passes refill_thread = 0; see launch()
+    // for why the store and the refill stay two separate blocks).
+    bool ok = true;
+    int it = 0;
+    for (long long id = first; id < tiles; id += step, ++it) {
+        const int s = it % NSTAGE;
+        const int b = it % NOUT;
+        TileCoord cur{0, 0, 0, 0, 0}, nxt{0, 0, 0, 0, 0};
+        bool refill = false;
+        if (threadIdx.x == 0) {
+            cur = staged[s];
+            tma_wait_read<NOUT - 1>();  // the store that last read B[b] has drained
+        }
+        if (threadIdx.x == refill_thread) {
+            refill = id + NSTAGE * step < tiles;
+            if (refill) nxt = cursor.coord(order);
+        }
+        ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
+        if (!__syncthreads_and(ok)) { ok = false; break; }
+
+        transpose_tile<ES, R, THREADS>(A + s * TILE_BYTES, B + b * TILE_BYTES);
+        fence_async_smem();
+        __syncthreads();
+
+        if (threadIdx.x == 0) {
+            tma_store_5d(&out_map, cur.ty * (R * WORDS), cur.tx * TCOLS, cur.b0, cur.b1, cur.b2, B + b * TILE_BYTES);
+            tma_commit();
+        }
+        if (threadIdx.x == refill_thread && refill) {
+            staged[s] = nxt;
+            mbar_expect_tx(&full[s], TILE_BYTES);
+            tma_load_5d(A + s * TILE_BYTES, &in_map, nxt.tx * (TCOLS * WORDS), nxt.ty * R, nxt.b0, nxt.b1, nxt.b2,
+                        &full[s]);
+            cursor.advance(bs);
+        }
+    }
+    if (threadIdx.x == 0) {
+        if (!ok) atomicAdd(&g_wait_timeouts, 1u);
+        tma_wait_all();
+    }
+}
+
 // ---- host --------------------------------------------------------------------------
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -396,6 +545,76 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     return B2K_OK;
 }
 
+// A 5-D map for the batched kernel: axis 0 and 1 as in make_map, then up to three
+// batch axes (length 1 where unused) with a box depth of 1.
+template <int ES>
+bool make_map5(CUtensorMap *map, const void *ptr, int64_t rows, int64_t cols, int64_t pitch, int box_cols,
+               int box_rows, bool swizzle, const int64_t *batch_len, const int64_t *batch_step) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    constexpr int UNIT = ES >= 4 ? 4 : ES;
+    constexpr int WORDS = ES / UNIT;
+    const CUtensorMapDataType type = UNIT == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32
+                                     : UNIT == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const cuuint64_t dims[5] = {static_cast<cuuint64_t>(cols) * WORDS, static_cast<cuuint64_t>(rows),
+                                static_cast<cuuint64_t>(batch_len[0]), static_cast<cuuint64_t>(batch_len[1]),
+                                static_cast<cuuint64_t>(batch_len[2])};
+    const cuuint64_t strides[4] = {static_cast<cuuint64_t>(pitch), static_cast<cuuint64_t>(batch_step[0]),
+                                   static_cast<cuuint64_t>(batch_step[1]), static_cast<cuuint64_t>(batch_step[2])};
+    const cuuint32_t box[5] = {static_cast<cuuint32_t>(box_cols * WORDS), static_cast<cuuint32_t>(box_rows), 1, 1, 1};
+    const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+    return enc(map, type, 5, const_cast<void *>(ptr), dims, strides, box, elem_strides,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int ES, int R, int NSTAGE, int THREADS = 256, int NOUT = 2>
+int launch_batched(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pitch, int64_t out_pitch,
+                   const int64_t *batch_len, const int64_t *in_batch_step, const int64_t *out_batch_step,
+                   cudaStream_t stream) {
+    constexpr int TCOLS = 128 / ES;
+    CUtensorMap in_map, out_map;
+    if (!make_map5<ES>(&in_map, in, rows, cols, in_pitch, TCOLS, R, true, batch_len, in_batch_step) ||
+        !make_map5<ES>(&out_map, out, cols, rows, out_pitch, R, TCOLS, false, batch_len, out_batch_step))
+        return B2K_ERR_UNSUPPORTED;
+    const int64_t tiles_x = (cols + TCOLS - 1) / TCOLS;
+    const int64_t tiles_y = (rows + R - 1) / R;
+    const int64_t tiles2d = tiles_x * tiles_y;
+    const int64_t slices = batch_len[0] * batch_len[1] * batch_len[2];
+    if (tiles2d > 0x7FFFFFFFll || slices > 0x7FFFFFFFll || tiles2d * slices > 0x7FFFFFFFll)
+        return B2K_ERR_UNSUPPORTED;  // the kernel numbers tiles in 31 bits
+    const int64_t tiles = tiles2d * slices;
+    constexpr int SMEM = (NSTAGE + NOUT) * R * 128 + NSTAGE * 8 + 1024;
+    auto kernel = transpose_tma_batched_kernel<ES, R, NSTAGE, THREADS, NOUT>;
+    static std::once_flag once;
+    static cudaError_t attr_status = cudaSuccess;
+    std::call_once(once, [&] {
+        attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    });
+    if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
+    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 2);
+    int64_t grid = static_cast<int64_t>(b2k::sm_count()) * (per_sm < 1 ? 1 : per_sm);
+    if (grid > tiles) grid = tiles;
+    int panel_w = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
+    if (panel_w < 1 || panel_w > tiles_x) panel_w = static_cast<int>(tiles_x);
+    const TileOrder order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), panel_w};
+    const int64_t adv_slices = grid / tiles2d;
+    const BatchSplit bs{static_cast<unsigned int>(tiles2d),
+                        static_cast<unsigned int>(batch_len[0]),
+                        static_cast<unsigned int>(batch_len[1]),
+                        static_cast<unsigned int>(grid % tiles2d),
+                        static_cast<unsigned int>(adv_slices % batch_len[0]),
+                        static_cast<unsigned int>(adv_slices / batch_len[0] % batch_len[1]),
+                        static_cast<unsigned int>(adv_slices / batch_len[0] / batch_len[1])};
+    // (the refill thread, always 0 here, is a kernel argument for the same reason as in launch())
+    kernel<<<static_cast<unsigned>(grid), THREADS, SMEM, stream>>>(in_map, out_map, order, bs,
+                                                                   static_cast<long long>(tiles), 0);
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("batched transpose (tma) launch");
+    return B2K_OK;
+}
+
 }  // namespace
 
 namespace b2k {
@@ -421,6 +640,43 @@ int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t
     case 4: return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 8: return launch<8, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     default: return launch<16, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    }
+}
+
+
+// out[b..., j, i] = in[b..., i, j] for up to three batch axes with their own byte
+// steps on each side; rows of both sides contiguous.  B2K_ERR_UNSUPPORTED when the
+// tensor-map rules (16-byte alignment of bases, pitches and steps) do not hold.
+int transpose_tma_batched(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pitch,
+                          int64_t out_pitch, int nbatch, const int64_t *batch_len, const int64_t *in_batch_step,
+                          const int64_t *out_batch_step, int64_t itemsize, cudaStream_t stream) {
+    if (itemsize != 1 && itemsize != 2 && itemsize != 4 && itemsize != 8 && itemsize != 16)
+        return B2K_ERR_UNSUPPORTED;
+    if (nbatch < 0 || nbatch > 3) return B2K_ERR_UNSUPPORTED;
+    if (!aligned_to<void>(in, 16) || !aligned_to<void>(out, 16)) return B2K_ERR_UNSUPPORTED;
+    const int64_t limit = int64_t(1) << 40;
+    if (in_pitch % 16 != 0 || out_pitch % 16 != 0 || in_pitch <= 0 || out_pitch <= 0 || in_pitch >= limit ||
+        out_pitch >= limit)
+        return B2K_ERR_UNSUPPORTED;
+    if (in_pitch < cols * itemsize || out_pitch < rows * itemsize) return B2K_ERR_UNSUPPORTED;
+    const int64_t words = itemsize >= 4 ? itemsize / 4 : 1;
+    if (rows * words >= (int64_t(1) << 31) || cols * words >= (int64_t(1) << 31)) return B2K_ERR_UNSUPPORTED;
+    int64_t len[3] = {1, 1, 1}, istep[3] = {in_pitch, in_pitch, in_pitch}, ostep[3] = {out_pitch, out_pitch, out_pitch};
+    for (int k = 0; k < nbatch; ++k) {
+        if (batch_len[k] < 1 || batch_len[k] >= (int64_t(1) << 31)) return B2K_ERR_UNSUPPORTED;
+        if (in_batch_step[k] <= 0 || out_batch_step[k] <= 0 || in_batch_step[k] % 16 != 0 ||
+            out_batch_step[k] % 16 != 0 || in_batch_step[k] >= limit || out_batch_step[k] >= limit)
+            return B2K_ERR_UNSUPPORTED;
+        len[k] = batch_len[k];
+        istep[k] = in_batch_step[k];
+        ostep[k] = out_batch_step[k];
+    }
+    switch (itemsize) {
+    case 1: return launch_batched<1, 128, 3>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
+    case 2: return launch_batched<2, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
+    case 4: return launch_batched<4, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
+    case 8: return launch_batched<8, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
+    default: return launch_batched<16, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
     }
 }
 
