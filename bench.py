@@ -392,6 +392,10 @@ def secondary_cpu_baselines():
                                  "sample": "2^24 of the 2^28 float32, NumPy slice assignment"}
     cube = src.reshape(64, 512, 512)
     dt, _ = clock(lambda: np.ascontiguousarray(cube.transpose(0, 2, 1)))
+    mat = src[:1 << 22].reshape(2048, 2048)
+    dt, _ = clock(lambda: (mat.sum(axis=0), mat.sum(axis=1)))
+    out["n4_reduce_sum_axis_f32"] = {"GBps": 2 * mat.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
+                                     "sample": "2048x2048 float32, NumPy sum along axis 0 and along axis 1"}
     out["n4_permute_021_f32"] = {"GBps": 2 * src.nbytes / dt / 1e9, "seconds": dt, "cores": 1, "kind": "port",
                                  "sample": "64x512x512 float32, np.ascontiguousarray(a.transpose(0, 2, 1))"}
     # C4: serial state chain (random.py:242-257) and the draw loop, C restatement
@@ -552,6 +556,19 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
             got = b[:count].view(out_shape)
             res[label] = dict(_roof(count * 8, ms, peak),
                               spot_check=bool(torch.equal(got[:2, :64], src.permute(perm)[:2, :64])))
+        rows = cols = 16384 >> (scale // 2)
+        m = a[:rows * cols].view(rows, cols)
+        zero32 = np.zeros(1, dtype=np.float32)
+        for axis in (0, 1):
+            need = int(L.b2k_reduce_axis_scratch_bytes(rows, cols, _lib.F32, axis))
+            scr = torch.zeros(max(need, 256), dtype=torch.uint8, device="cuda")
+            outv = torch.empty(cols if axis == 0 else rows, dtype=torch.float32, device="cuda")
+            ms, _ = timed(lambda: check(L.b2k_reduce_axis(_lib.ADD, _lib.F32, m.data_ptr(), rows, cols, cols * 4, axis,
+                                                          zero32.ctypes.data, outv.data_ptr(), scr.data_ptr(),
+                                                          scr.numel(), sptr)), iters, warm)
+            ref = m[:, :256].sum(dim=0) if axis == 0 else m[:256].sum(dim=1)
+            res[f"n4_reduce_sum_axis{axis}_f32_16384x16384"] = dict(
+                _roof(rows * cols * 4, ms, peak), spot_check=bool(torch.allclose(outv[:256], ref, rtol=1e-4, atol=1e-2)))
         del a, b
 
     if want("c5"):

@@ -90,6 +90,23 @@ B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* Reduction of a rows x cols matrix along one axis with a table op:
+ *   axis 0: out_dev[j] = op(fold_i x[i, j], *init_host)   (cols outputs)
+ *   axis 1: out_dev[i] = op(fold_j x[i, j], *init_host)   (rows outputs)
+ * Rows are contiguous and `pitch_bytes` apart.  The reference reduces 1-D arrays
+ * only (Reduce.__call__ raises TypeError("only support 1D array") otherwise,
+ * numba/cuda/kernels/reduction.py:217-218); this is the axis-wise step after it,
+ * with the ops, dtypes and wrap-around rules of b2k_reduce.  One launch.
+ *   scratch : b2k_reduce_axis_scratch_bytes(rows, cols, dtype, axis) bytes (0 for
+ *             most axis-1 shapes), 256-byte aligned, zero-filled once before first
+ *             use; the kernel leaves it reusable for calls of the same or a smaller
+ *             requirement.  Calls that may overlap on the GPU need separate scratch.
+ * An empty reduced axis writes *init_host to every output. */
+B2K_API int64_t b2k_reduce_axis_scratch_bytes(int64_t rows, int64_t cols, int dtype, int axis);
+B2K_API int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols,
+                            int64_t pitch_bytes, int axis, const void *init_host, void *out_dev,
+                            void *scratch_dev, int64_t scratch_bytes, void *stream);
+
 /* cuda.reduce with an arbitrary user function.  `expr` is a C++ expression over
  * the operands `a` and `b` (the Python layer obtains it by tracing the user's
  * function); the reduce kernel is compiled around it at run time with NVRTC for

@@ -20,6 +20,7 @@ SOURCES = [
     "b2k_api.cu",
     "b2k_reduce.cu",
     "b2k_reduce_user.cu",
+    "b2k_reduce_axis.cu",
     "b2k_cast.cu",
     "b2k_xoroshiro.cu",
     "b2k_transpose.cu",

@@ -1,0 +1,505 @@
+// Reduction of a matrix along one axis with a table op: out[j] = fold_i x[i, j]
+// (axis 0) or out[i] = fold_j x[i, j] (axis 1), `init` folded into every output.
+// The reference reduces 1-D arrays only (numba/cuda/kernels/reduction.py:217-218
+// raises for anything else); this is the axis-wise step after it, with the same
+// ops, dtypes and wrap-around rules as b2k_reduce.
+//
+// Rows are contiguous (column stride = item size) and `pitch` bytes apart.  When
+// the base, the pitch and the row length allow it, threads move 16-byte packs of
+// 16/sizeof(T) items (V items per pack); otherwise single items (V = 1).
+//
+//  * axis 0, reduce_cols_kernel: a thread owns one pack of columns and walks down
+//    the rows; a CTA is `lx` column packs wide (32 for wide matrices, fewer for
+//    narrow ones) and 256/lx row lanes tall, four row loads in flight per thread.
+//    Row lanes combine through shared memory.  Rows are split into `chunks`
+//    (gridDim.y) to fill the GPU: every CTA publishes its partial row, takes a
+//    ticket per column tile (atomicInc that wraps to zero), and the CTA that draws
+//    the last ticket folds the partial rows (row lanes stride over the chunks, then
+//    the same tree).
+//  * axis 1, reduce_rows_kernel: a group of G lanes (1..32, or the whole CTA) owns
+//    one row, lanes striding over its packs with four loads in flight, then a
+//    shuffle butterfly inside the group.  G grows with the row length, so short
+//    rows are read coalesced by neighbouring lanes and long rows by whole CTAs.
+//  * axis 1 with few, very long rows, reduce_rows_split_kernel: every row is cut
+//    into `segments` CTAs with the same ticket scheme.
+//
+// The order of every fold depends only on the shape and the grid, so float
+// results are reproducible.  HBM roofline: sizeof(T) bytes read per item.
+#include <cstring>
+#include <type_traits>
+
+#include "b2k_internal.cuh"
+#include "b2k_reduce_ops.cuh"
+
+namespace {
+
+using namespace b2k_reduce_ops;
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;
+constexpr int kMaxChunks = 1024;
+// Scratch layout: a fixed region of tickets first (always back at zero when a kernel
+// ends), partials behind it.  The region is the same for every shape, so a buffer
+// that served one shape can serve any other without being cleared again.
+constexpr int64_t kMaxTickets = 4096;
+constexpr int64_t kTicketRegion = kMaxTickets * 4;
+
+template <typename T, int V>
+struct Pack {
+    T e[V];
+};
+
+template <typename T, int V>
+__device__ __forceinline__ Pack<T, V> load_pack(const unsigned char *p) {
+    if constexpr (V == 1) {
+        Pack<T, 1> r;
+        r.e[0] = *reinterpret_cast<const T *>(p);
+        return r;
+    } else {
+        static_assert(V * sizeof(T) == 16, "a pack is one item or 16 bytes");
+        union {
+            uint4 raw;
+            Pack<T, V> v;
+        } u;
+        asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(u.raw.x), "=r"(u.raw.y), "=r"(u.raw.z), "=r"(u.raw.w)
+                     : "l"(p));
+        return u.v;
+    }
+}
+
+// 8- and 16-bit items, four or two to a 32-bit word: the per-byte / per-halfword
+// video instructions fold a whole word at once (add wraps per item, as the scalar op
+// does); products have no such form.
+template <typename T, typename Op>
+struct WordWise {
+    static constexpr bool value = std::is_integral<T>::value && sizeof(T) < 4 && !std::is_same<Op, OpMul>::value;
+};
+
+template <typename T, typename Op>
+__device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
+    constexpr bool bytes = sizeof(T) == 1, is_signed = std::is_signed<T>::value;
+    if constexpr (std::is_same<Op, OpAdd>::value) return bytes ? __vadd4(a, b) : __vadd2(a, b);
+    else if constexpr (std::is_same<Op, OpAnd>::value) return a & b;
+    else if constexpr (std::is_same<Op, OpOr>::value) return a | b;
+    else if constexpr (std::is_same<Op, OpXor>::value) return a ^ b;
+    else if constexpr (std::is_same<Op, OpMax>::value)
+        return bytes ? (is_signed ? __vmaxs4(a, b) : __vmaxu4(a, b)) : (is_signed ? __vmaxs2(a, b) : __vmaxu2(a, b));
+    else
+        return bytes ? (is_signed ? __vmins4(a, b) : __vminu4(a, b)) : (is_signed ? __vmins2(a, b) : __vminu2(a, b));
+}
+
+template <typename T, typename Op, int V>
+__device__ __forceinline__ void fold_into(Pack<T, V> &acc, const Pack<T, V> &v) {
+    if constexpr (WordWise<T, Op>::value && V * sizeof(T) == 16) {
+        union Words {
+            Pack<T, V> items;
+            uint32_t w[4];
+        };
+        Words a, b;
+        a.items = acc;
+        b.items = v;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a.w[k] = apply_word<T, Op>(a.w[k], b.w[k]);
+        acc = a.items;
+    } else {
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc.e[k] = Op::template apply<T>(acc.e[k], v.e[k]);
+    }
+}
+
+template <typename T, typename Op, int V>
+__device__ __forceinline__ Pack<T, V> identity_pack() {
+    Pack<T, V> r;
+#pragma unroll
+    for (int k = 0; k < V; ++k) r.e[k] = Op::template identity<T>();
+    return r;
+}
+
+template <typename T, typename Op, int V>
+__device__ __forceinline__ T fold_pack(T acc, const Pack<T, V> &v) {
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc = Op::template apply<T>(acc, v.e[k]);
+    return acc;
+}
+
+// ---- axis 0 ----------------------------------------------------------------------
+template <typename T, typename Op, int V>
+__global__ void __launch_bounds__(kThreads)
+reduce_cols_kernel(const unsigned char *__restrict__ x, int64_t rows, int64_t packs, int64_t pitch, int lx_log2,
+                   int64_t rows_per_chunk, T init, Pack<T, V> *__restrict__ out, Pack<T, V> *__restrict__ partials,
+                   unsigned int *__restrict__ tickets) {
+    __shared__ Pack<T, V> lanes[kThreads];
+    __shared__ bool is_last;
+    const int lx = 1 << lx_log2;
+    const int tx = threadIdx.x & (lx - 1), ty = threadIdx.x >> lx_log2, ny = kThreads >> lx_log2;
+    const int64_t pack = static_cast<int64_t>(blockIdx.x) * lx + tx;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
+    const int64_t r1 = (r0 + rows_per_chunk < rows) ? r0 + rows_per_chunk : rows;
+
+    Pack<T, V> acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) acc[u] = identity_pack<T, Op, V>();
+    if (pack < packs) {
+        const unsigned char *col = x + pack * static_cast<int64_t>(V * sizeof(T));
+        int64_t r = r0 + ty;
+        for (; r + (kUnroll - 1) * ny < r1; r += kUnroll * ny) {
+            Pack<T, V> v[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) v[u] = load_pack<T, V>(col + (r + u * ny) * pitch);
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) fold_into<T, Op, V>(acc[u], v[u]);
+        }
+        for (; r < r1; r += ny) fold_into<T, Op, V>(acc[0], load_pack<T, V>(col + r * pitch));
+    }
+#pragma unroll
+    for (int u = 1; u < kUnroll; ++u) fold_into<T, Op, V>(acc[0], acc[u]);
+
+    lanes[threadIdx.x] = acc[0];
+    __syncthreads();
+    for (int s = ny >> 1; s >= 1; s >>= 1) {
+        if (ty < s) {
+            Pack<T, V> mine = lanes[threadIdx.x];
+            fold_into<T, Op, V>(mine, lanes[threadIdx.x + s * lx]);
+            lanes[threadIdx.x] = mine;
+        }
+        __syncthreads();
+    }
+    const bool owner = ty == 0 && pack < packs;
+    const unsigned int chunks = gridDim.y;
+    if (chunks == 1) {
+        if (owner) {
+            Pack<T, V> total = lanes[threadIdx.x];
+#pragma unroll
+            for (int k = 0; k < V; ++k) total.e[k] = Op::template apply<T>(total.e[k], init);
+            out[pack] = total;
+        }
+        return;
+    }
+    if (owner) partials[static_cast<int64_t>(blockIdx.y) * packs + pack] = lanes[threadIdx.x];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicInc(&tickets[blockIdx.x], chunks - 1) == chunks - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // the last CTA folds the partial rows: row lanes take chunks ty, ty + ny, ..., then
+    // the same shared-memory tree as above
+    Pack<T, V> total = identity_pack<T, Op, V>();
+    if (pack < packs) {
+        for (unsigned int c = ty; c < chunks; c += ny) {
+            const Pack<T, V> *src = partials + static_cast<int64_t>(c) * packs + pack;
+            Pack<T, V> v;
+#pragma unroll
+            for (int k = 0; k < V; ++k) v.e[k] = __ldcg(&src->e[k]);
+            fold_into<T, Op, V>(total, v);
+        }
+    }
+    lanes[threadIdx.x] = total;
+    __syncthreads();
+    for (int s = ny >> 1; s >= 1; s >>= 1) {
+        if (ty < s) {
+            Pack<T, V> mine = lanes[threadIdx.x];
+            fold_into<T, Op, V>(mine, lanes[threadIdx.x + s * lx]);
+            lanes[threadIdx.x] = mine;
+        }
+        __syncthreads();
+    }
+    if (owner) {
+        total = lanes[threadIdx.x];
+#pragma unroll
+        for (int k = 0; k < V; ++k) total.e[k] = Op::template apply<T>(total.e[k], init);
+        out[pack] = total;
+    }
+}
+
+// ---- axis 1 ----------------------------------------------------------------------
+// Fold of packs [first, last) of one row by `width` cooperating lanes.
+template <typename T, typename Op, int V>
+__device__ __forceinline__ T fold_row_part(const unsigned char *row, int64_t first, int64_t last, int lane,
+                                           int width) {
+    T acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) acc[u] = Op::template identity<T>();
+    int64_t k = first + lane;
+    for (; k + static_cast<int64_t>(kUnroll - 1) * width < last; k += static_cast<int64_t>(kUnroll) * width) {
+        Pack<T, V> v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+            v[u] = load_pack<T, V>(row + (k + static_cast<int64_t>(u) * width) * static_cast<int64_t>(V * sizeof(T)));
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) acc[u] = fold_pack<T, Op, V>(acc[u], v[u]);
+    }
+    for (; k < last; k += width)
+        acc[0] = fold_pack<T, Op, V>(acc[0], load_pack<T, V>(row + k * static_cast<int64_t>(V * sizeof(T))));
+#pragma unroll
+    for (int u = 1; u < kUnroll; ++u) acc[0] = Op::template apply<T>(acc[0], acc[u]);
+    return acc[0];
+}
+
+// Block-wide fold; the result is valid in thread 0.
+template <typename T, typename Op>
+__device__ __forceinline__ T block_fold(T v, T *slots) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = Op::template apply<T>(v, shuffle_xor(v, m));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) slots[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = (lane < kThreads / 32) ? slots[lane] : Op::template identity<T>();
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) v = Op::template apply<T>(v, shuffle_xor(v, m));
+    }
+    __syncthreads();
+    return v;
+}
+
+template <typename T, typename Op, int V>
+__global__ void __launch_bounds__(kThreads)
+reduce_rows_kernel(const unsigned char *__restrict__ x, int64_t rows, int64_t packs, int64_t pitch, int group_log2,
+                   T init, T *__restrict__ out) {
+    __shared__ T slots[kThreads / 32];
+    const int width = 1 << group_log2;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads >> group_log2) + (threadIdx.x >> group_log2);
+    const int lane = threadIdx.x & (width - 1);
+    T acc = Op::template identity<T>();
+    if (row < rows) acc = fold_row_part<T, Op, V>(x + row * pitch, 0, packs, lane, width);
+    if (width == kThreads) {
+        acc = block_fold<T, Op>(acc, slots);
+    } else {
+        // groups are aligned inside a warp: butterfly over the group's lanes only
+        for (int m = (width < 32 ? width : 32) >> 1; m > 0; m >>= 1)
+            acc = Op::template apply<T>(acc, shuffle_xor(acc, m));
+    }
+    if (lane == 0 && row < rows) out[row] = Op::template apply<T>(acc, init);
+}
+
+template <typename T, typename Op, int V>
+__global__ void __launch_bounds__(kThreads)
+reduce_rows_split_kernel(const unsigned char *__restrict__ x, int64_t packs, int64_t pitch, int64_t packs_per_segment,
+                         T init, T *__restrict__ out, T *__restrict__ partials, unsigned int *__restrict__ tickets) {
+    __shared__ T slots[kThreads / 32];
+    __shared__ bool is_last;
+    const int64_t row = blockIdx.y;
+    const unsigned int segments = gridDim.x;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * packs_per_segment;
+    const int64_t last = (first + packs_per_segment < packs) ? first + packs_per_segment : packs;
+    T acc = fold_row_part<T, Op, V>(x + row * pitch, first, last, threadIdx.x, kThreads);
+    acc = block_fold<T, Op>(acc, slots);
+    if (threadIdx.x == 0) {
+        partials[row * segments + blockIdx.x] = acc;
+        __threadfence();
+        is_last = atomicInc(&tickets[row], segments - 1) == segments - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) {
+        T total = Op::template identity<T>();
+        for (unsigned int s = 0; s < segments; ++s) total = Op::template apply<T>(total, __ldcg(partials + row * segments + s));
+        out[row] = Op::template apply<T>(total, init);
+    }
+}
+
+// ---- host ------------------------------------------------------------------------
+struct Plan {
+    bool packed;          // 16-byte packs (else single items)
+    int64_t packs;        // packs per row
+    // axis 0
+    int lx_log2;
+    int64_t tiles, chunks, rows_per_chunk;
+    // axis 1
+    int group_log2;
+    bool split;
+    int64_t segments, packs_per_segment;
+    // scratch layout: tickets first, partials after `ticket_bytes`
+    int64_t ticket_bytes, scratch_bytes;
+};
+
+int log2_ceil(int64_t v) {
+    int l = 0;
+    while ((int64_t(1) << l) < v) ++l;
+    return l;
+}
+
+Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, bool aligned) {
+    Plan p{};
+    const int64_t per_pack = 16 / item;
+    p.packed = aligned && cols % per_pack == 0;
+    p.packs = p.packed ? cols / per_pack : cols;
+    const int64_t sms = b2k::sm_count();
+    if (axis == 0) {
+        p.lx_log2 = p.packs >= 32 ? 5 : log2_ceil(p.packs < 1 ? 1 : p.packs);
+        const int64_t lx = int64_t(1) << p.lx_log2, ny = kThreads / lx;
+        p.tiles = (p.packs + lx - 1) / lx;
+        int64_t chunks = (sms * 8 + p.tiles - 1) / p.tiles;
+        const int64_t most = rows / (ny * kUnroll);  // every chunk gets at least one unrolled pass
+        if (chunks > most) chunks = most;
+        if (chunks > kMaxChunks) chunks = kMaxChunks;
+        if (chunks < 1 || p.tiles > kMaxTickets) chunks = 1;
+        p.rows_per_chunk = (rows + chunks - 1) / chunks;
+        p.chunks = (rows + p.rows_per_chunk - 1) / (p.rows_per_chunk < 1 ? 1 : p.rows_per_chunk);
+        if (p.chunks < 1) p.chunks = 1;
+        p.ticket_bytes = p.chunks > 1 ? kTicketRegion : 0;
+        p.scratch_bytes = p.ticket_bytes + (p.chunks > 1 ? p.chunks * p.packs * 16 : 0);
+        if (!p.packed && p.chunks > 1) p.scratch_bytes = p.ticket_bytes + p.chunks * p.packs * item;
+    } else {
+        // lanes per row: about four packs per lane, a whole CTA for long rows
+        const int64_t want = (p.packs + kUnroll - 1) / kUnroll;
+        p.group_log2 = want >= 64 ? 8 : (want > 32 ? 5 : log2_ceil(want < 1 ? 1 : want));
+        p.split = p.group_log2 == 8 && rows < 2 * sms && rows <= kMaxTickets && p.packs >= 16 * kThreads * kUnroll;
+        if (p.split) {
+            int64_t segments = (4 * sms + rows - 1) / rows;
+            const int64_t most = p.packs / (kThreads * kUnroll * 2);
+            if (segments > most) segments = most;
+            if (segments > 64) segments = 64;  // folded by one thread per row
+            if (segments < 2) {
+                p.split = false;
+            } else {
+                p.packs_per_segment = (p.packs + segments - 1) / segments;
+                p.segments = (p.packs + p.packs_per_segment - 1) / p.packs_per_segment;
+                p.ticket_bytes = kTicketRegion;
+                p.scratch_bytes = p.ticket_bytes + rows * p.segments * item;
+            }
+        }
+    }
+    return p;
+}
+
+template <typename T, typename Op, int V>
+int launch_planned(const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis, T init, void *out,
+                   void *scratch, cudaStream_t stream) {
+    const unsigned char *src = static_cast<const unsigned char *>(x);
+    unsigned char *sc = static_cast<unsigned char *>(scratch);
+    if (axis == 0) {
+        if (p.tiles > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_reduce_axis: too many columns");
+        const dim3 grid(static_cast<unsigned>(p.tiles), static_cast<unsigned>(p.chunks));
+        reduce_cols_kernel<T, Op, V><<<grid, kThreads, 0, stream>>>(
+            src, rows, p.packs, pitch, p.lx_log2, p.rows_per_chunk, init, static_cast<Pack<T, V> *>(out),
+            reinterpret_cast<Pack<T, V> *>(sc + p.ticket_bytes), reinterpret_cast<unsigned int *>(sc));
+    } else if (p.split) {
+        const dim3 grid(static_cast<unsigned>(p.segments), static_cast<unsigned>(rows));
+        reduce_rows_split_kernel<T, Op, V><<<grid, kThreads, 0, stream>>>(
+            src, p.packs, pitch, p.packs_per_segment, init, static_cast<T *>(out),
+            reinterpret_cast<T *>(sc + p.ticket_bytes), reinterpret_cast<unsigned int *>(sc));
+    } else {
+        const int64_t per_cta = kThreads >> p.group_log2;
+        const int64_t grid = (rows + per_cta - 1) / per_cta;
+        if (grid > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_reduce_axis: too many rows");
+        reduce_rows_kernel<T, Op, V><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+            src, rows, p.packs, pitch, p.group_log2, init, static_cast<T *>(out));
+    }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_reduce_axis launch");
+    return B2K_OK;
+}
+
+template <typename T, typename Op>
+int launch_typed(const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis, const void *init_host,
+                 void *out, void *scratch, cudaStream_t stream) {
+    T init;
+    memcpy(&init, init_host, sizeof(T));
+    if (p.packed) return launch_planned<T, Op, 16 / sizeof(T)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    return launch_planned<T, Op, 1>(p, x, rows, pitch, axis, init, out, scratch, stream);
+}
+
+// Integer +, *, &, |, ^ wrap identically for both signs, so signed types run those
+// ops in the unsigned type of their width; only max and min need the sign.
+template <typename S, typename U>
+int dispatch_integer(int op, bool is_signed, const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis,
+                     const void *init_host, void *out, void *scratch, cudaStream_t stream) {
+    switch (op) {
+    case B2K_ADD: return launch_typed<U, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MUL: return launch_typed<U, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_AND: return launch_typed<U, OpAnd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_OR: return launch_typed<U, OpOr>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_XOR: return launch_typed<U, OpXor>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MAX:
+        return is_signed ? launch_typed<S, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream)
+                         : launch_typed<U, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MIN:
+        return is_signed ? launch_typed<S, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream)
+                         : launch_typed<U, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    default: return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: unknown op %d", op);
+    }
+}
+
+template <typename F>
+int dispatch_float(int op, const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis,
+                   const void *init_host, void *out, void *scratch, cudaStream_t stream) {
+    switch (op) {
+    case B2K_ADD: return launch_typed<F, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MUL: return launch_typed<F, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MAX: return launch_typed<F, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_MIN: return launch_typed<F, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    default: return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_axis: bitwise op on a floating-point type");
+    }
+}
+
+int64_t item_size(int dtype) {
+    switch (dtype) {
+    case B2K_I8: case B2K_U8: return 1;
+    case B2K_I16: case B2K_U16: return 2;
+    case B2K_I32: case B2K_U32: case B2K_F32: return 4;
+    case B2K_I64: case B2K_U64: case B2K_F64: return 8;
+    default: return 0;
+    }
+}
+
+bool layout_aligned(const void *x, int64_t pitch, const void *out) {
+    return reinterpret_cast<uintptr_t>(x) % 16 == 0 && pitch % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b2k_reduce_axis_scratch_bytes(int64_t rows, int64_t cols, int dtype, int axis) {
+    const int64_t item = item_size(dtype);
+    if (rows <= 0 || cols <= 0 || item == 0 || (axis != 0 && axis != 1)) return 0;
+    // the larger of the packed and the item-wise plan, so that one buffer serves any alignment
+    const Plan a = make_plan(rows, cols, item, axis, true), b = make_plan(rows, cols, item, axis, false);
+    return a.scratch_bytes > b.scratch_bytes ? a.scratch_bytes : b.scratch_bytes;
+}
+
+int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols, int64_t pitch_bytes, int axis,
+                    const void *init_host, void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    const int64_t item = item_size(dtype);
+    if (item == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: unknown dtype %d", dtype);
+    if (axis != 0 && axis != 1) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: axis must be 0 or 1");
+    if (rows < 0 || cols < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: negative shape");
+    if (!init_host) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null init");
+    const int64_t outputs = axis == 0 ? cols : rows;
+    if (outputs == 0) return B2K_OK;
+    if (!out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null output");
+    if (reinterpret_cast<uintptr_t>(out_dev) % item) return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_axis: output not aligned to its item size");
+    const int64_t reduced = axis == 0 ? rows : cols;
+    if (reduced > 0) {
+        if (!x_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null input");
+        if (reinterpret_cast<uintptr_t>(x_dev) % item || pitch_bytes % item)
+            return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_axis: input or pitch not aligned to the item size");
+        if (pitch_bytes < cols * item) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: pitch shorter than a row");
+    }
+    // an empty reduced axis leaves `init` in every output: same kernels, zero rows / packs
+    const Plan p = make_plan(rows, cols, item, axis, layout_aligned(x_dev, pitch_bytes, out_dev));
+    if (p.scratch_bytes > 0) {
+        if (!scratch_dev || scratch_bytes < p.scratch_bytes || reinterpret_cast<uintptr_t>(scratch_dev) % 256)
+            return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_axis: scratch of %lld bytes (256-byte aligned, zeroed once) needed",
+                             static_cast<long long>(p.scratch_bytes));
+    }
+    cudaStream_t s = b2k::as_stream(stream);
+    switch (dtype) {
+    case B2K_I8: return dispatch_integer<int8_t, uint8_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_U8: return dispatch_integer<int8_t, uint8_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_I16: return dispatch_integer<int16_t, uint16_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_U16: return dispatch_integer<int16_t, uint16_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_I32: return dispatch_integer<int32_t, uint32_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_U32: return dispatch_integer<int32_t, uint32_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_I64: return dispatch_integer<int64_t, uint64_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_U64: return dispatch_integer<int64_t, uint64_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_F32: return dispatch_float<float>(op, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    default: return dispatch_float<double>(op, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    }
+}
+
+}  // extern "C"

@@ -204,6 +204,74 @@ class Reduce:
         return host[0]
 
 
+    def along_axis(self, arr, axis, res=None, init=0, stream=0):
+        """Reduce a 2-D array along ``axis`` (0: over rows, one result per column;
+        1: over columns, one result per row).  ``init`` is folded into every
+        result, as ``__call__`` folds it into its one.  Returns a 1-D device array
+        (``res`` if given).  The reference stops at 1-D arrays
+        (reduction.py:217-218); table ops only."""
+        if arr.ndim != 2:
+            raise TypeError("only support 2D array")
+        if axis not in (0, 1, -1, -2):
+            raise ValueError("axis %r is out of bounds for a 2D array" % (axis,))
+        axis %= 2
+        dtype = np.dtype(arr.dtype)
+        op = self._compile(dtype)
+        if isinstance(op, str):
+            raise NotImplementedError("axis-wise reduction supports the precompiled table ops only")
+        darr, _ = auto_device(arr, stream=stream)
+        item = dtype.itemsize
+        rows, cols = darr.shape
+        if darr.strides[1] == item or cols <= 1:
+            pitch = darr.strides[0] if rows > 1 else max(cols, 1) * item
+        elif darr.strides[0] == item or rows <= 1:
+            # columns are the contiguous runs: the same bytes are a row-major matrix
+            # of the transposed shape, reduced along the other axis
+            rows, cols, axis = cols, rows, 1 - axis
+            pitch = darr.strides[1] if rows > 1 else max(cols, 1) * item
+        else:
+            raise ValueError("one axis of the array must be contiguous")
+        if pitch < cols * item:
+            raise ValueError("rows of the array overlap")
+        outputs = cols if axis == 0 else rows
+        if res is None:
+            from ..api import device_array
+            dres = device_array(outputs, dtype, stream=stream)
+        else:
+            dres, _ = auto_device(res, stream=stream, copy=False)
+            if np.dtype(dres.dtype) != dtype:
+                raise TypeError("incompatible dtype: %s vs. %s" % (dres.dtype, dtype))
+            if dres.ndim != 1 or dres.shape[0] != outputs or (outputs > 1 and dres.strides[0] != item):
+                raise ValueError("incompatible shape: res must be a contiguous 1-D array of %d items" % outputs)
+        L = _lib.lib()
+        need = int(L.b2k_reduce_axis_scratch_bytes(rows, cols, _DTYPE_CODES[dtype], axis))
+        scratch = _AxisScratch.get(stream, need)
+        init_host = np.array([init], dtype=dtype)
+        _lib.check(L.b2k_reduce_axis(op, _DTYPE_CODES[dtype], darr._ptr, rows, cols, pitch, axis,
+                                     init_host.ctypes.data, dres._ptr, scratch.data_ptr() if need else None,
+                                     need, stream_ptr(stream)))
+        return dres
+
+
+class _AxisScratch:
+    """Per (device, stream) zero-initialised scratch for the axis-wise kernels,
+    regrown when a shape needs more (the kernels leave it zeroed where it must be)."""
+
+    _lock = threading.Lock()
+    _pool: dict = {}
+
+    @classmethod
+    def get(cls, stream, nbytes):
+        key = (torch.cuda.current_device(), stream_ptr(stream))
+        with cls._lock:
+            buf = cls._pool.get(key)
+            if buf is None or buf.numel() < nbytes:
+                with torch.cuda.stream(_torch_stream(stream)):
+                    buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device="cuda")
+                cls._pool[key] = buf
+            return buf
+
+
 class _OneItem:
     """Shape/stride descriptor of ``partials[:1]`` for the compatibility check."""
 
@@ -221,10 +289,9 @@ def _gather_contiguous(darr: DeviceNDArray, stream) -> DeviceNDArray:
     if step <= 0 or step % item:
         raise NotImplementedError("cuda.reduce: only positive item-multiple strides are supported")
     from ..api import device_array
+    from ..devicearray import assign_strided
     out = device_array(darr.size, darr.dtype, stream=stream)
-    with torch.cuda.stream(_torch_stream(stream)):
-        src = torch.as_strided(darr._buf[darr._offset:], (darr.size, item), (step, 1))
-        out._bytes_view().view(darr.size, item).copy_(src)
+    assign_strided(out._ptr, darr._ptr, (darr.size,), (item,), (step,), item, stream)
     return out
 
 
