@@ -64,17 +64,49 @@ def device_array(shape, dtype=np.float64, strides=None, order="C", stream=0) -> 
     return DeviceNDArray(shape, strides, dtype, stream=stream)
 
 
+def strides_like(shape, strides, itemsize):
+    """Strides of a new dense array "like" one with the given shape and strides
+    (api.py:295-328, which follows NumPy's ``zeros_like``): a C- or F-contiguous
+    source keeps its order; any other source keeps the ranking of its axes by
+    stride, so the axis that was densest in a view stays densest in the copy."""
+    shape, strides = tuple(shape), tuple(strides)
+    c, f = _c_strides(shape, itemsize), _f_strides(shape, itemsize)
+    size = int(np.prod(shape, dtype=np.int64)) if shape else 1
+    if len(shape) <= 1 or size == 0 or strides == c or _dense(shape, strides, c):
+        return c
+    if strides == f or _dense(shape, strides, f):
+        return f
+    ranking = sorted(range(len(shape)), key=lambda k: strides[k])   # stable: ties keep axis order
+    out, step = [0] * len(shape), itemsize
+    for k in ranking:
+        out[k] = step
+        step *= shape[k]
+    return tuple(out)
+
+
+def _dense(shape, strides, want):
+    """Same layout as ``want`` once axes of length 1 (whose stride is free) are ignored."""
+    return all(n == 1 or a == b for n, a, b in zip(shape, strides, want))
+
+
 def device_array_like(ary, stream=0) -> DeviceNDArray:
-    """Allocate with the shape, dtype and (where contiguous) the axis order of
-    ``ary`` (api.py:243-250 / api_util.py)."""
+    """Allocate a dense array with the shape, dtype and axis order of ``ary``
+    (api.py:331-344)."""
     shape, dtype = tuple(ary.shape), np.dtype(ary.dtype)
     strides = getattr(ary, "strides", None)
-    order = "C"
-    if strides is not None and len(shape) > 1:
-        item = dtype.itemsize
-        if tuple(strides) == _f_strides(shape, item) and tuple(strides) != _c_strides(shape, item):
-            order = "F"
-    return device_array(shape, dtype, order=order, stream=stream)
+    if strides is None:
+        strides = _c_strides(shape, dtype.itemsize)
+    return device_array(shape, dtype, strides=strides_like(shape, strides, dtype.itemsize), stream=stream)
+
+
+def pinned_array_like(ary) -> np.ndarray:
+    """Page-locked host array with the shape, dtype and axis order of ``ary`` (api.py:365-374)."""
+    shape, dtype = tuple(ary.shape), np.dtype(ary.dtype)
+    strides = getattr(ary, "strides", None) or _c_strides(shape, dtype.itemsize)
+    like = strides_like(shape, strides, dtype.itemsize)
+    n = (int(np.prod(shape, dtype=np.int64)) if shape else 1) * dtype.itemsize
+    raw = torch.empty(max(n, 1), dtype=torch.uint8, pin_memory=torch.cuda.is_available()).numpy()
+    return np.ndarray(shape, dtype=dtype, buffer=raw, strides=like)
 
 
 def to_device(obj, stream=0, copy=True, to=None) -> DeviceNDArray:
@@ -139,5 +171,6 @@ def auto_device(obj, stream=0, copy=True):
 __all__ = [
     "is_available", "is_bfloat16_supported", "is_fp8_supported", "synchronize", "stream",
     "default_stream", "external_stream", "device_array", "device_array_like", "to_device",
-    "is_cuda_array", "as_cuda_array", "pinned_array", "auto_device", "stream_ptr",
+    "is_cuda_array", "as_cuda_array", "pinned_array", "pinned_array_like", "auto_device", "stream_ptr",
+    "strides_like",
 ]

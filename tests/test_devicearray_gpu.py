@@ -139,3 +139,23 @@ def test_streams_and_pinned():
     with s.auto_synchronize():
         pass
     assert cuda.is_bfloat16_supported() and cuda.is_fp8_supported()
+
+
+def test_device_array_like_of_views_and_transposes():
+    # test_array.py:176-263
+    for order in ("C", "F"):
+        for shape, key in (((10,), (slice(None, None, 2),)), ((10, 12), (slice(None, None, 2), slice(None, None, 2)))):
+            view = np.zeros(shape, order=order)[key]
+            d_view = cuda.device_array(shape, order=order)[key]
+            like = cuda.device_array_like(d_view)
+            want = np.zeros_like(view)
+            assert like.shape == want.shape and like.dtype == want.dtype and like.strides == want.strides
+            assert like.flags["C_CONTIGUOUS"] == want.flags["C_CONTIGUOUS"]
+            assert like.flags["F_CONTIGUOUS"] == want.flags["F_CONTIGUOUS"]
+            pinned = cuda.pinned_array_like(d_view)
+            assert pinned.shape == want.shape and pinned.strides == want.strides
+    # the transpose of a device view is a new dense allocation (test_array.py:221-237)
+    d_t = cuda.device_array((10, 12))[::2, ::2].T
+    like = cuda.device_array_like(d_t)
+    assert like.shape == d_t.shape and like.strides == (40, 8)
+    assert like.flags["C_CONTIGUOUS"] and not like.flags["F_CONTIGUOUS"]

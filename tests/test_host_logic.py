@@ -138,3 +138,73 @@ def test_format_names():
     assert casts.saturation_t.SATFINITE == 1 and casts.fp8_interpretation_t.E5M2 == 1
     with pytest.raises(ValueError):
         casts._format_code("fp4")
+
+
+def test_array_like_strides_follow_numpy_zeros_like():
+    # numba/cuda/tests/cudapy/test_array.py:100-263 compares device_array_like with
+    # np.zeros_like on contiguous arrays and on views; the rule itself needs no GPU
+    from numba_cuda_b200.api import strides_like
+    rng = np.random.default_rng(0)
+    checked = 0
+    for _ in range(2000):
+        nd = int(rng.integers(1, 5))
+        shape = tuple(int(x) for x in rng.integers(2, 7, size=nd))
+        base = np.zeros(shape, dtype=rng.choice([np.float32, np.float64, np.int8]), order=rng.choice(["C", "F"]))
+        view = base[tuple(slice(None, None, int(rng.choice([1, 1, 2, 3]))) for _ in range(nd))]
+        if rng.random() < 0.3:
+            view = view.T
+        if min(view.shape) < 2:
+            continue
+        assert strides_like(view.shape, view.strides, view.dtype.itemsize) == np.zeros_like(view).strides
+        checked += 1
+    assert checked > 1000
+    for shape, order in (((10,), "C"), ((10, 12), "C"), ((10, 12, 14), "C"), ((10,), "F"), ((10, 12), "F"),
+                         ((10, 12, 14), "F")):
+        a = np.zeros(shape, order=order)
+        assert strides_like(a.shape, a.strides, 8) == a.strides
+        assert strides_like(a.T.shape, a.T.strides, 8) == a.T.strides
+    # a signed sort, as the reference does: a reversed axis ranks first
+    assert strides_like((3, 4), (-32, 8), 8) == (8, 24)
+
+
+def test_basic_indexing_matches_numpy_views():
+    # shape, strides and byte offset of every view numba's dummy array would give
+    # (numba/cuda/tests/nocuda/test_dummyarray.py compares against NumPy the same way)
+    from numba_cuda_b200.devicearray import _basic_index
+    rng = np.random.default_rng(1)
+
+    def one_slice(dim):
+        def bound():
+            return None if rng.random() < 0.3 else int(rng.integers(-dim - 2, dim + 3))
+        step = None if rng.random() < 0.4 else int(rng.choice([1, 2, 3, -1, -2, -3]))
+        return slice(bound(), bound(), step)
+
+    def one_item(dim):
+        return int(rng.integers(-dim, dim)) if rng.random() < 0.4 else one_slice(dim)
+
+    views = 0
+    for _ in range(4000):
+        nd = int(rng.integers(1, 5))
+        shape = tuple(int(x) for x in rng.integers(1, 6, size=nd))
+        base = np.zeros(shape, dtype=np.int32)
+        head = [one_item(shape[d]) for d in range(int(rng.integers(0, nd + 1)))]
+        key = head
+        if rng.random() < 0.3 and len(head) < nd:
+            tail_len = int(rng.integers(0, nd - len(head) + 1))
+            key = head + [Ellipsis] + [one_item(shape[nd - tail_len + j]) for j in range(tail_len)]
+        key = tuple(key)
+        want = base[key]
+        got_shape, got_strides, got_offset = _basic_index(base.shape, base.strides, key)
+        assert got_shape == want.shape
+        if not isinstance(want, np.ndarray) or want.size == 0:
+            continue
+        assert all(a == b for a, b, n in zip(got_strides, want.strides, got_shape) if n > 1)
+        assert got_offset == want.__array_interface__["data"][0] - base.__array_interface__["data"][0]
+        views += 1
+    assert views > 2000
+    with pytest.raises(IndexError):
+        _basic_index((3, 4), (16, 4), (0, 4))
+    with pytest.raises(IndexError):
+        _basic_index((3, 4), (16, 4), (0, 0, 0))
+    with pytest.raises(IndexError):
+        _basic_index((3, 4), (16, 4), (Ellipsis, Ellipsis))
