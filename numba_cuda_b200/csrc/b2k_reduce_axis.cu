@@ -4,9 +4,9 @@
 // raises for anything else); this is the axis-wise step after it, with the same
 // ops, dtypes and wrap-around rules as b2k_reduce.
 //
-// Rows are contiguous (column stride = item size) and `pitch` bytes apart.  When
-// the base, the pitch and the row length allow it, threads move 16-byte packs of
-// 16/sizeof(T) items (V items per pack); otherwise single items (V = 1).
+// Rows are contiguous (column stride = item size) and `pitch` bytes apart.  Threads
+// move packs of V items: 16 bytes when the base, the pitch and the row length are
+// multiples of 16, else 8 or 4 bytes on the same condition, else single items.
 //
 //  * axis 0, reduce_cols_kernel: a thread owns one pack of columns and walks down
 //    the rows; a CTA is `lx` column packs wide (32 for wide matrices, fewer for
@@ -51,19 +51,25 @@ struct Pack {
 
 template <typename T, int V>
 __device__ __forceinline__ Pack<T, V> load_pack(const unsigned char *p) {
+    constexpr int BYTES = V * sizeof(T);
     if constexpr (V == 1) {
         Pack<T, 1> r;
         r.e[0] = *reinterpret_cast<const T *>(p);
         return r;
     } else {
-        static_assert(V * sizeof(T) == 16, "a pack is one item or 16 bytes");
+        static_assert(BYTES == 16 || BYTES == 8 || BYTES == 4, "a pack is one item or 4, 8 or 16 bytes");
         union {
-            uint4 raw;
+            uint32_t w[BYTES / 4];
             Pack<T, V> v;
         } u;
-        asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-                     : "=r"(u.raw.x), "=r"(u.raw.y), "=r"(u.raw.z), "=r"(u.raw.w)
-                     : "l"(p));
+        if constexpr (BYTES == 16)
+            asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(u.w[0]), "=r"(u.w[1]), "=r"(u.w[2]), "=r"(u.w[3])
+                         : "l"(p));
+        else if constexpr (BYTES == 8)
+            asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(u.w[0]), "=r"(u.w[1]) : "l"(p));
+        else
+            asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(u.w[0]) : "l"(p));
         return u.v;
     }
 }
@@ -91,16 +97,17 @@ __device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
 
 template <typename T, typename Op, int V>
 __device__ __forceinline__ void fold_into(Pack<T, V> &acc, const Pack<T, V> &v) {
-    if constexpr (WordWise<T, Op>::value && V * sizeof(T) == 16) {
+    if constexpr (WordWise<T, Op>::value && (V * sizeof(T)) % 4 == 0) {
+        constexpr int WORDS = V * sizeof(T) / 4;
         union Words {
             Pack<T, V> items;
-            uint32_t w[4];
+            uint32_t w[WORDS];
         };
         Words a, b;
         a.items = acc;
         b.items = v;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) a.w[k] = apply_word<T, Op>(a.w[k], b.w[k]);
+        for (int k = 0; k < WORDS; ++k) a.w[k] = apply_word<T, Op>(a.w[k], b.w[k]);
         acc = a.items;
     } else {
 #pragma unroll
@@ -303,7 +310,7 @@ reduce_rows_split_kernel(const unsigned char *__restrict__ x, int64_t packs, int
 
 // ---- host ------------------------------------------------------------------------
 struct Plan {
-    bool packed;          // 16-byte packs (else single items)
+    int64_t pack_bytes;   // bytes moved per load: 16, 8, 4 or one item
     int64_t packs;        // packs per row
     // axis 0
     int lx_log2;
@@ -322,11 +329,17 @@ int log2_ceil(int64_t v) {
     return l;
 }
 
-Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, bool aligned) {
+Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, int64_t alignment) {
     Plan p{};
-    const int64_t per_pack = 16 / item;
-    p.packed = aligned && cols % per_pack == 0;
-    p.packs = p.packed ? cols / per_pack : cols;
+    // widest pack that the layout's alignment and the row length allow
+    p.pack_bytes = item;
+    for (int64_t bytes = 16; bytes > item && bytes >= 4; bytes /= 2) {
+        if (alignment % bytes == 0 && (cols * item) % bytes == 0) {
+            p.pack_bytes = bytes;
+            break;
+        }
+    }
+    p.packs = cols * item / p.pack_bytes;
     const int64_t sms = b2k::sm_count();
     if (axis == 0) {
         p.lx_log2 = p.packs >= 32 ? 5 : log2_ceil(p.packs < 1 ? 1 : p.packs);
@@ -341,11 +354,10 @@ Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, bool aligned)
         p.chunks = (rows + p.rows_per_chunk - 1) / (p.rows_per_chunk < 1 ? 1 : p.rows_per_chunk);
         if (p.chunks < 1) p.chunks = 1;
         p.ticket_bytes = p.chunks > 1 ? kTicketRegion : 0;
-        p.scratch_bytes = p.ticket_bytes + (p.chunks > 1 ? p.chunks * p.packs * 16 : 0);
-        if (!p.packed && p.chunks > 1) p.scratch_bytes = p.ticket_bytes + p.chunks * p.packs * item;
+        p.scratch_bytes = p.ticket_bytes + (p.chunks > 1 ? p.chunks * p.packs * p.pack_bytes : 0);
     } else {
-        // lanes per row: about four packs per lane, a whole CTA for long rows
-        const int64_t want = (p.packs + kUnroll - 1) / kUnroll;
+        // lanes per row: about 64 bytes per lane, a whole CTA for long rows
+        const int64_t want = (p.packs * p.pack_bytes + 63) / 64;
         p.group_log2 = want >= 64 ? 8 : (want > 32 ? 5 : log2_ceil(want < 1 ? 1 : want));
         p.split = p.group_log2 == 8 && rows < 2 * sms && rows <= kMaxTickets && p.packs >= 16 * kThreads * kUnroll;
         if (p.split) {
@@ -399,7 +411,16 @@ int launch_typed(const Plan &p, const void *x, int64_t rows, int64_t pitch, int 
                  void *out, void *scratch, cudaStream_t stream) {
     T init;
     memcpy(&init, init_host, sizeof(T));
-    if (p.packed) return launch_planned<T, Op, 16 / sizeof(T)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    constexpr int SIZE = sizeof(T);
+    if constexpr (SIZE < 16) {
+        if (p.pack_bytes == 16) return launch_planned<T, Op, 16 / SIZE>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    }
+    if constexpr (SIZE < 8) {
+        if (p.pack_bytes == 8) return launch_planned<T, Op, (8 / SIZE > 0 ? 8 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    }
+    if constexpr (SIZE < 4) {
+        if (p.pack_bytes == 4) return launch_planned<T, Op, (4 / SIZE > 0 ? 4 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    }
     return launch_planned<T, Op, 1>(p, x, rows, pitch, axis, init, out, scratch, stream);
 }
 
@@ -446,8 +467,12 @@ int64_t item_size(int dtype) {
     }
 }
 
-bool layout_aligned(const void *x, int64_t pitch, const void *out) {
-    return reinterpret_cast<uintptr_t>(x) % 16 == 0 && pitch % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+// Largest power of two (up to 16) that divides the input base, the pitch and the
+// output base.
+int64_t layout_alignment(const void *x, int64_t pitch, const void *out) {
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(x) | static_cast<uintptr_t>(pitch) |
+                           reinterpret_cast<uintptr_t>(out) | 16u;
+    return static_cast<int64_t>(bits & (~bits + 1));
 }
 
 }  // namespace
@@ -457,9 +482,13 @@ extern "C" {
 int64_t b2k_reduce_axis_scratch_bytes(int64_t rows, int64_t cols, int dtype, int axis) {
     const int64_t item = item_size(dtype);
     if (rows <= 0 || cols <= 0 || item == 0 || (axis != 0 && axis != 1)) return 0;
-    // the larger of the packed and the item-wise plan, so that one buffer serves any alignment
-    const Plan a = make_plan(rows, cols, item, axis, true), b = make_plan(rows, cols, item, axis, false);
-    return a.scratch_bytes > b.scratch_bytes ? a.scratch_bytes : b.scratch_bytes;
+    // the largest over the pack widths, so that one buffer serves any alignment
+    int64_t most = 0;
+    for (int64_t alignment = 16; alignment >= 1; alignment /= 2) {
+        const Plan p = make_plan(rows, cols, item, axis, alignment);
+        if (p.scratch_bytes > most) most = p.scratch_bytes;
+    }
+    return most;
 }
 
 int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols, int64_t pitch_bytes, int axis,
@@ -481,7 +510,7 @@ int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t 
         if (pitch_bytes < cols * item) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: pitch shorter than a row");
     }
     // an empty reduced axis leaves `init` in every output: same kernels, zero rows / packs
-    const Plan p = make_plan(rows, cols, item, axis, layout_aligned(x_dev, pitch_bytes, out_dev));
+    const Plan p = make_plan(rows, cols, item, axis, layout_alignment(x_dev, pitch_bytes, out_dev));
     if (p.scratch_bytes > 0) {
         if (!scratch_dev || scratch_bytes < p.scratch_bytes || reinterpret_cast<uintptr_t>(scratch_dev) % 256)
             return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_axis: scratch of %lld bytes (256-byte aligned, zeroed once) needed",
