@@ -544,6 +544,9 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
         ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [rows // 2, 16384], [2 * 65536, 4], [2 * 65536, 4], 4),
                       iters, warm)
         res["n2_assign_every_other_row_f32"] = _roof(rows // 2 * 16384 * 8, ms, peak)
+        ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [rows, 16384], [65536, 4], [0, 4], 4), iters, warm)
+        res["n2_assign_row_to_every_row_f32"] = dict(_roof(rows * 16384 * 4, ms, peak), note="write-only: 4 B per item",
+                                                     spot_check=bool(torch.equal(b[-16384:], a[:16384])))
         for label, shape, perm in (("n4_permute_021_f32_64x2048x2048", [64 >> scale, 2048, 2048], (0, 2, 1)),
                                    ("n4_permute_102_f32_2048x64x2048", [2048 >> scale, 64, 2048], (1, 0, 2)),
                                    ("n4_permute_210_f32_512x512x1024", [512 >> scale, 512, 1024], (2, 1, 0))):

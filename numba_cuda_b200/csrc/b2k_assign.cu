@@ -17,6 +17,8 @@
 //    row / scalar broadcasts, plain copies);
 //  * fill: the source repeats along the fastest destination axis (scalar and
 //    per-row fills): the unit is replicated into 16-byte stores;
+//  * repeat: the source repeats along a slower axis (one row assigned to every
+//    row): each thread reads its unit once and stores it to 16 rows;
 //  * tiled: when the source is dense along a DIFFERENT axis q than the destination
 //    (axis permutations), square tiles over (destination axis p, source axis q)
 //    go through shared memory so that both sides see coalesced accesses;
@@ -103,6 +105,34 @@ assign_fill_kernel(unsigned char *__restrict__ dst, const unsigned char *__restr
             for (int k = 0; k < REP; ++k) v.part[k] = one;
             *reinterpret_cast<uint4 *>(dst + doff) = v.wide;
         }
+    }
+}
+
+// The source repeats along an axis that is not the fastest one (a row assigned to
+// every row of a matrix): a thread reads its unit once and stores it to `per_thread`
+// consecutive positions of the repeated axis.  `ax` holds the other axes, with the
+// repeated axis replaced by its chunks (axis 0, the slowest).
+constexpr int kRepeatRows = 16;
+
+template <typename U, typename Index>
+__global__ void __launch_bounds__(kDirectThreads)
+assign_repeat_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                     const __grid_constant__ Axes ax, uint64_t total, uint64_t units_per_chunk, int64_t repeat_step,
+                     int64_t repeat_len) {
+    const uint64_t g = static_cast<uint64_t>(blockIdx.x) * kDirectThreads + threadIdx.x;
+    if (g >= total) return;
+    int64_t doff, soff;
+    locate<Index>(ax, static_cast<Index>(g), doff, soff);
+    const int64_t chunk = static_cast<int64_t>(static_cast<Index>(g) / static_cast<Index>(units_per_chunk));
+    int64_t count = repeat_len - chunk * kRepeatRows;
+    if (count > kRepeatRows) count = kRepeatRows;
+    const U value = *reinterpret_cast<const U *>(src + soff);
+    unsigned char *to = dst + doff;
+    if (count == kRepeatRows) {
+#pragma unroll
+        for (int r = 0; r < kRepeatRows; ++r) *reinterpret_cast<U *>(to + r * repeat_step) = value;
+    } else {
+        for (int64_t r = 0; r < count; ++r) *reinterpret_cast<U *>(to + r * repeat_step) = value;
     }
 }
 
@@ -201,6 +231,43 @@ int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool
             assign_direct_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
                 d, s, ax, total);
     }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
+    return B2K_OK;
+}
+
+template <typename U>
+int launch_repeat(void *dst, const void *src, const Axes &ax, int b, cudaStream_t stream) {
+    // the other axes keep their order; the chunks of axis b become the slowest axis
+    Axes rest{};
+    const int64_t chunks = (ax.len[b] + kRepeatRows - 1) / kRepeatRows;
+    rest.n = ax.n;
+    rest.len[0] = chunks;
+    rest.dst_step[0] = ax.dst_step[b] * kRepeatRows;
+    rest.src_step[0] = 0;
+    uint64_t units_per_chunk = 1;
+    bool narrow = chunks <= 0xFFFFFFFFll;
+    for (int k = 0, j = 1; k < ax.n; ++k) {
+        if (k == b) continue;
+        rest.len[j] = ax.len[k];
+        rest.dst_step[j] = ax.dst_step[k];
+        rest.src_step[j] = ax.src_step[k];
+        units_per_chunk *= static_cast<uint64_t>(ax.len[k]);
+        if (ax.len[k] > 0xFFFFFFFFll) narrow = false;
+        ++j;
+    }
+    const uint64_t total = units_per_chunk * static_cast<uint64_t>(chunks);
+    if (total > 0xFFFFFFFFull) narrow = false;
+    const uint64_t blocks = (total + kDirectThreads - 1) / kDirectThreads;
+    if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many units");
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    if (narrow)
+        assign_repeat_kernel<U, uint32_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
+            d, s, rest, total, units_per_chunk, ax.dst_step[b], ax.len[b]);
+    else
+        assign_repeat_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
+            d, s, rest, total, units_per_chunk, ax.dst_step[b], ax.len[b]);
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
     return B2K_OK;
@@ -315,6 +382,23 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
             case 4: return launch_fill<uint32_t>(dst, src, fill, units, narrow, st);
             case 2: return launch_fill<uint16_t>(dst, src, fill, units, narrow, st);
             default: return launch_fill<uint8_t>(dst, src, fill, units, narrow, st);
+            }
+        }
+    }
+
+    // The source repeats along a slower axis and both sides are dense along the
+    // fastest one: read once, store to many rows.
+    if (n >= 2 && ax.src_step[n - 1] == unit && ax.dst_step[n - 1] == unit) {
+        int b = -1;
+        for (int k = 0; k + 1 < n; ++k)
+            if (ax.src_step[k] == 0 && ax.len[k] >= 2 * kRepeatRows && (b < 0 || ax.len[k] > ax.len[b])) b = k;
+        if (b >= 0) {
+            switch (unit) {
+            case 16: return launch_repeat<uint4>(dst, src, ax, b, st);
+            case 8: return launch_repeat<uint2>(dst, src, ax, b, st);
+            case 4: return launch_repeat<uint32_t>(dst, src, ax, b, st);
+            case 2: return launch_repeat<uint16_t>(dst, src, ax, b, st);
+            default: return launch_repeat<uint8_t>(dst, src, ax, b, st);
             }
         }
     }

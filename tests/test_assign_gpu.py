@@ -44,6 +44,12 @@ SETITEM_CASES = [
     ((3, 4, 5, 6, 2), (slice(None), slice(1, 3), Ellipsis, slice(None, None, 2), 1), (3, 2, 5, 3)),
     ((257, 130), (slice(None), slice(None)), (257, 130)),
     ((257, 130), (slice(3, 250, 5), slice(1, 129)), (1, 128)),
+    # one row / plane repeated over a long slower axis (the read-once, store-many kernel)
+    ((100, 40, 64), (slice(None), slice(None), slice(None)), (40, 64)),
+    ((100, 40, 64), (slice(None), slice(None), slice(None)), (100, 1, 64)),
+    ((100, 40, 64), (slice(1, 99), slice(None), slice(0, 60)), (1, 1, 60)),
+    ((1000, 36), (slice(None), slice(None)), (36,)),
+    ((1000, 36), (slice(None, None, -1), slice(2, 34)), (32,)),
 ]
 
 
