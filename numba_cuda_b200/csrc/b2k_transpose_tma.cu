@@ -15,8 +15,10 @@
 //             registers with byte permutes so that every store is a 32-bit word)
 //   B[b]   --cp.async.bulk.tensor store (tiled, no swizzle)--> global
 //
-// B holds the transposed tile as (128/ES) output rows of R items.  R = 64 (8 KB
-// tiles, four load stages) for items of 2 bytes and more, 128 for single bytes.  Edge tiles
+// B holds the transposed tile as (128/ES) output rows of R items, R = 64 (8 KB
+// tiles, four load stages).  For single bytes an output row of a tile is 64 bytes,
+// half a line: the tile below writes the other half a few tiles later and the two
+// meet in L2 (measured faster than 128-row tiles of 16 KB).  Edge tiles
 // need no code: out-of-range parts of a load read as zero and out-of-range
 // parts of a store are dropped by the tensor-map bounds.
 //
@@ -152,36 +154,47 @@ __device__ __forceinline__ void transpose_tile<2, 64, 256>(const unsigned char *
     }
 }
 
-// 1-byte items, R = 128, 256 threads: a thread owns four consecutive rows and one
-// chunk of sixteen columns, transposes four 4x4 byte blocks with byte permutes and
-// stores sixteen 32-bit words (column c, rows 4g..4g+3).  Lane mapping: quarter-warp
-// s, lane j -> row group g = 8s + j, chunk q0 ^ (j >> 1) with q0 = warp.
+// 1-byte items, R = 64, 256 threads: a thread owns four consecutive rows (4g..4g+3)
+// and eight columns (half h of chunk q), transposes two 4x4 byte blocks with byte
+// permutes and stores eight 32-bit words (column c, rows 4g..4g+3; a B row is 64
+// bytes = 16 words).  Thread t: i = t mod 16 gives h = i & 1 and the swizzled chunk
+// position i >> 1, so the sixteen lanes of a half-warp read sixteen different 8-byte
+// bank pairs whatever their rows; g = (i + t / 16) mod 16 puts every row group twice
+// into a warp, and the upper half-warp stores its columns in swapped pairs, so the
+// two lanes that share a row group hit different banks (bank = 16 (c & 1) + g).
 template <>
-__device__ __forceinline__ void transpose_tile<1, 128, 256>(const unsigned char *A, unsigned char *B) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int j = lane & 7;
-    const int g = (lane >> 3) * 8 + j;
-    const int q = warp ^ (j >> 1);
+__device__ __forceinline__ void transpose_tile<1, 64, 256>(const unsigned char *A, unsigned char *B) {
+    const int i = threadIdx.x & 15, upper = (threadIdx.x >> 4) & 1;
+    const int g = (i + (threadIdx.x >> 4)) & 15;
+    const int h = i & 1;
+    const int q = (i >> 1) ^ ((g & 1) << 2);
     const int r0 = 4 * g;
-    uint4 row[4];
+    uint2 row[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k)
-        row[k] = *reinterpret_cast<const uint4 *>(A + (r0 + k) * 128 + ((q ^ ((r0 + k) & 7)) << 4));
-    uint32_t *dst = reinterpret_cast<uint32_t *>(B) + (q * 16) * 32 + g;  // B row = 128 items = 32 words
-    const uint32_t w0[4] = {row[0].x, row[0].y, row[0].z, row[0].w};
-    const uint32_t w1[4] = {row[1].x, row[1].y, row[1].z, row[1].w};
-    const uint32_t w2[4] = {row[2].x, row[2].y, row[2].z, row[2].w};
-    const uint32_t w3[4] = {row[3].x, row[3].y, row[3].z, row[3].w};
+        row[k] = *reinterpret_cast<const uint2 *>(A + (r0 + k) * 128 + ((q ^ ((r0 + k) & 7)) << 4) + h * 8);
+    uint32_t o[8];
+    {
+        const uint32_t t0 = __byte_perm(row[0].x, row[1].x, 0x5140), t1 = __byte_perm(row[2].x, row[3].x, 0x5140);
+        const uint32_t t2 = __byte_perm(row[0].x, row[1].x, 0x7362), t3 = __byte_perm(row[2].x, row[3].x, 0x7362);
+        o[0] = __byte_perm(t0, t1, 0x5410);
+        o[1] = __byte_perm(t0, t1, 0x7632);
+        o[2] = __byte_perm(t2, t3, 0x5410);
+        o[3] = __byte_perm(t2, t3, 0x7632);
+    }
+    {
+        const uint32_t t0 = __byte_perm(row[0].y, row[1].y, 0x5140), t1 = __byte_perm(row[2].y, row[3].y, 0x5140);
+        const uint32_t t2 = __byte_perm(row[0].y, row[1].y, 0x7362), t3 = __byte_perm(row[2].y, row[3].y, 0x7362);
+        o[4] = __byte_perm(t0, t1, 0x5410);
+        o[5] = __byte_perm(t0, t1, 0x7632);
+        o[6] = __byte_perm(t2, t3, 0x5410);
+        o[7] = __byte_perm(t2, t3, 0x7632);
+    }
+    uint32_t *dst = reinterpret_cast<uint32_t *>(B) + (q * 16 + h * 8) * 16 + g;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {  // one 4x4 byte block per 32-bit column group
-        const uint32_t t0 = __byte_perm(w0[k], w1[k], 0x5140);  // a0 b0 a1 b1
-        const uint32_t t1 = __byte_perm(w2[k], w3[k], 0x5140);  // c0 d0 c1 d1
-        const uint32_t t2 = __byte_perm(w0[k], w1[k], 0x7362);  // a2 b2 a3 b3
-        const uint32_t t3 = __byte_perm(w2[k], w3[k], 0x7362);  // c2 d2 c3 d3
-        dst[(4 * k + 0) * 32] = __byte_perm(t0, t1, 0x5410);
-        dst[(4 * k + 1) * 32] = __byte_perm(t0, t1, 0x7632);
-        dst[(4 * k + 2) * 32] = __byte_perm(t2, t3, 0x5410);
-        dst[(4 * k + 3) * 32] = __byte_perm(t2, t3, 0x7632);
+    for (int j = 0; j < 8; ++j) {
+        const int c = upper ? (j ^ 1) : j;
+        dst[c * 16] = upper ? o[j ^ 1] : o[j];
     }
 }
 
@@ -507,13 +520,13 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     constexpr int SMEM = (NSTAGE + NOUT) * R * 128 + NSTAGE * 8 + 1024;
     // Two code shapes for the issuing thread, chosen by measurement.  With the
     // store and the refill in separate blocks (SPLIT) lines that are not 128-byte
-    // aligned run 10-40 % faster for items of 2 bytes and more, and 4-byte items
-    // gain 2-3 % on aligned lines too; the merged shape is 3-5 % ahead for 1-byte
-    // items and for 2-byte items on 128-byte-aligned lines.  DRAM traffic and the
-    // isolated launch time are the same for both, so the difference comes from how
-    // the CTAs' requests fall into step over back-to-back tiles.
+    // aligned run 10-40 % faster, and 4-byte items gain 2-3 % on aligned lines too;
+    // the merged shape is 3-7 % ahead for 1- and 2-byte items on 128-byte-aligned
+    // lines.  DRAM traffic and the isolated launch time are the same for both, so
+    // the difference comes from how the CTAs' requests fall into step over
+    // back-to-back tiles.
     const bool aligned = in_pitch % 128 == 0 && out_pitch % 128 == 0;
-    const bool auto_split = ES >= 4 || (ES == 2 && !aligned);
+    const bool auto_split = ES >= 4 || !aligned;
     const int forced = b2k::env_int("B2K_TRANSPOSE_SPLIT", -1);
     const bool split = forced < 0 ? auto_split : forced != 0;
     auto kernel = split ? transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>
@@ -635,7 +648,7 @@ int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t
     // small arrays: the general tile kernel has less fixed cost
     if (rows * cols * itemsize < b2k::env_int("B2K_TRANSPOSE_TMA_MIN_BYTES", 1 << 16)) return B2K_ERR_UNSUPPORTED;
     switch (itemsize) {
-    case 1: return launch<1, 128, 3>(in, out, rows, cols, in_stride0, out_stride0, stream);
+    case 1: return launch<1, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 2: return launch<2, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 4: return launch<4, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
     case 8: return launch<8, 64, 4>(in, out, rows, cols, in_stride0, out_stride0, stream);
@@ -672,7 +685,7 @@ int transpose_tma_batched(const void *in, void *out, int64_t rows, int64_t cols,
         ostep[k] = out_batch_step[k];
     }
     switch (itemsize) {
-    case 1: return launch_batched<1, 128, 3>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
+    case 1: return launch_batched<1, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
     case 2: return launch_batched<2, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
     case 4: return launch_batched<4, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
     case 8: return launch_batched<8, 64, 4>(in, out, rows, cols, in_pitch, out_pitch, len, istep, ostep, stream);
