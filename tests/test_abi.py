@@ -55,6 +55,27 @@ def test_argument_errors_are_reported_on_host():
     assert L.b2k_xoroshiro128p_init(1028, 8, 1, 0, 4096, 1 << 20, None) == _lib.ERR_ALIGNMENT
     assert L.b2k_xoroshiro128p_fill(1024, 8, 7, 2048, 4, 0, None, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_xoroshiro128p_fill(1024, -8, 0, 2048, 4, 0, None, 0, None) == _lib.ERR_INVALID_ARG
+    # strided assignment and axis-wise reduce
+    arr2 = ctypes.c_int64 * 2
+    assert L.b2k_assign(1024, 2048, 40, None, None, None, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_assign(1024, 2048, 2, arr2(4, 4), arr2(16, 4), arr2(16, 4), 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_assign(1024, 2048, 2, arr2(4, -4), arr2(16, 4), arr2(16, 4), 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_assign(1024, 2048, 2, arr2(4, 4), arr2(16, 0), arr2(16, 4), 4, None) == _lib.ERR_INVALID_ARG
+    assert b"destination stride 0" in L.b2k_last_error()
+    assert L.b2k_assign(None, 2048, 2, arr2(4, 4), arr2(16, 4), arr2(16, 4), 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_assign(None, None, 2, arr2(4, 0), arr2(16, 4), arr2(16, 4), 4, None) == 0          # empty
+    assert L.b2k_reduce_axis(_lib.ADD, 99, 1024, 4, 4, 16, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, 4, 4, 16, 2, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, -4, 4, 16, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, 4, 4, 8, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert b"pitch" in L.b2k_last_error()
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1026, 4, 4, 16, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_reduce_axis(_lib.XOR, _lib.F64, 1024, 4, 4, 32, 1, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, 1 << 20, 8, 32, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_SCRATCH
+    assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, None, 0, 0, 0, 0, init.ctypes.data, None, None, 0, None) == 0   # no outputs
+    assert L.b2k_reduce_axis_scratch_bytes(1 << 20, 8, _lib.F32, 0) > 16384
+    assert L.b2k_reduce_axis_scratch_bytes(64, 64, _lib.F32, 1) == 0
+    assert L.b2k_reduce_axis_scratch_bytes(64, 64, 99, 1) == 0
     # empty work is a no-op that needs no device
     assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, None, None, 0, None) == 0
     assert L.b2k_transpose2d(None, None, 0, 4, 16, 4, 0, 4, 4, None) == 0
