@@ -48,9 +48,15 @@ struct xoroshiro128p_generator {
     }
     /* random.py:146-156.  (x >> 11) * 2^-53 is exact in float64, so rounding the
      * 53-bit integer to float32 first and scaling by a power of two gives the
-     * same bits as rounding the float64 product. */
-    __device__ __forceinline__ double uniform_float64() { return __ull2double_rn(next() >> 11) * 0x1p-53; }
-    __device__ __forceinline__ float uniform_float32() { return __ull2float_rn(next() >> 11) * 0x1p-53f; }
+     * same bits as rounding the float64 product.  Clearing the low 11 bits and
+     * scaling by 2^-64 is the same value again (a power-of-two factor moved from
+     * the integer into the scale) and saves the 64-bit shift. */
+    __device__ __forceinline__ double uniform_float64() {
+        return __ull2double_rn(next() & 0xFFFFFFFFFFFFF800ull) * 0x1p-64;
+    }
+    __device__ __forceinline__ float uniform_float32() {
+        return __ull2float_rn(next() & 0xFFFFFFFFFFFFF800ull) * 0x1p-64f;
+    }
     /* random.py:192-238: Box-Muller, cosine branch, from two float32 uniforms */
     __device__ __forceinline__ float normal_float32() {
         const float u1 = uniform_float32();

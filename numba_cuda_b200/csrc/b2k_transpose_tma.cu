@@ -66,26 +66,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
     return false;
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
-// Named barrier over the first `count` threads of the block (count a multiple of 32).
-__device__ __forceinline__ void bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-// The same with an AND reduction of `pred` over the participants.
-__device__ __forceinline__ bool bar_and(int id, int count, bool pred) {
-    uint32_t all;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, %2, %3, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(all)
-        : "r"(static_cast<uint32_t>(pred)), "r"(id), "r"(count)
-        : "memory");
-    return all != 0;
-}
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -342,91 +322,6 @@ transpose_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_co
     }
 }
 
-// Warp-specialised form of the same pipeline: warps 0..7 transpose tiles and issue
-// the stores, warp 8 only feeds the load ring.  The producer waits for a stage to be
-// released (empty[s]: one arrival per consumer warp), works out the tile's
-// coordinates, parks them in shared memory for the store and issues the load; the
-// consumers never compute coordinates and never wait for a load to be issued.
-constexpr int kConsumerThreads = 256;
-
-template <int ES, int R, int NSTAGE, int NOUT>
-__global__ void __launch_bounds__(kConsumerThreads + 32)
-transpose_tma_ws_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
-                        const TileOrder order, long long tiles) {
-    constexpr int TILE_BYTES = R * 128;
-    constexpr int TCOLS = 128 / ES;
-    constexpr int WORDS = ES > 4 ? ES / 4 : 1;
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char *base = reinterpret_cast<unsigned char *>(
-        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    unsigned char *A = base;
-    unsigned char *B = base + NSTAGE * TILE_BYTES;
-    uint64_t *full = reinterpret_cast<uint64_t *>(B + NOUT * TILE_BYTES);
-    uint64_t *empty = full + NSTAGE;
-    int2 *staged = reinterpret_cast<int2 *>(empty + NSTAGE);
-
-    const long long first = blockIdx.x;
-    const long long step = gridDim.x;
-    if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < NSTAGE; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kConsumerThreads / 32);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        fence_async_smem();
-    }
-    __syncthreads();
-
-    if (threadIdx.x >= kConsumerThreads) {
-        if (threadIdx.x == kConsumerThreads) {
-            bool ok = true;
-            int it = 0;
-            for (long long id = first; id < tiles; id += step, ++it) {
-                const int s = it % NSTAGE;
-                int tx, ty;
-                order.coords(static_cast<unsigned int>(id), tx, ty);
-                if (it >= NSTAGE) {
-                    ok = mbar_wait(&empty[s], ((it / NSTAGE) - 1) & 1);
-                    if (!ok) break;
-                }
-                staged[s] = make_int2(tx, ty);
-                mbar_expect_tx(&full[s], TILE_BYTES);
-                tma_load_2d(A + s * TILE_BYTES, &in_map, tx * (TCOLS * WORDS), ty * R, &full[s]);
-            }
-            if (!ok) atomicAdd(&g_wait_timeouts, 1u);
-        }
-        return;
-    }
-
-    bool ok = true;
-    int it = 0;
-    for (long long id = first; id < tiles; id += step, ++it) {
-        const int s = it % NSTAGE;
-        const int b = it % NOUT;
-        if (threadIdx.x == 0) tma_wait_read<NOUT - 1>();  // the store that last read B[b] has drained
-        ok = mbar_wait(&full[s], (it / NSTAGE) & 1);
-        if (!bar_and(1, kConsumerThreads, ok)) { ok = false; break; }
-        int2 cur = make_int2(0, 0);
-        if (threadIdx.x == 0) cur = staged[s];
-
-        transpose_tile<ES, R, kConsumerThreads>(A + s * TILE_BYTES, B + b * TILE_BYTES);
-        fence_async_smem();
-        __syncwarp();
-        if ((threadIdx.x & 31) == 0) mbar_arrive(&empty[s]);  // this warp has read its part of A[s]
-        bar_sync(1, kConsumerThreads);
-
-        if (threadIdx.x == 0) {
-            tma_store_2d(&out_map, cur.y * (R * WORDS), cur.x * TCOLS, B + b * TILE_BYTES);
-            tma_commit();
-        }
-    }
-    if (threadIdx.x == 0) {
-        if (!ok) atomicAdd(&g_wait_timeouts, 1u);
-        tma_wait_all();
-    }
-}
-
 // The same pipeline over a stack of 2-D problems: up to three further axes (batch
 // axes) select the 2-D slice, tile numbers run slice by slice, and the tensor maps
 // are five-dimensional with a box depth of 1 along the batch axes.  This serves
@@ -634,27 +529,6 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     const bool auto_split = ES >= 4 || !aligned;
     const int forced = b2k::env_int("B2K_TRANSPOSE_SPLIT", -1);
     const bool split = forced < 0 ? auto_split : forced != 0;
-    if (b2k::env_int("B2K_TRANSPOSE_WS", 0) != 0) {
-        constexpr int WS_SMEM = (NSTAGE + NOUT) * R * 128 + NSTAGE * 24 + 1024;
-        auto ws = transpose_tma_ws_kernel<ES, R, NSTAGE, NOUT>;
-        static std::once_flag ws_once;
-        static cudaError_t ws_status = cudaSuccess;
-        std::call_once(ws_once, [&] {
-            ws_status = cudaFuncSetAttribute(ws, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
-        });
-        if (ws_status != cudaSuccess) return b2k::check_cuda(ws_status, "transpose smem attribute");
-        const int ws_per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 2);
-        int64_t ws_grid = static_cast<int64_t>(b2k::sm_count()) * (ws_per_sm < 1 ? 1 : ws_per_sm);
-        if (ws_grid > tiles) ws_grid = tiles;
-        int ws_panel = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
-        if (ws_panel < 1 || ws_panel > tiles_x) ws_panel = static_cast<int>(tiles_x);
-        const TileOrder ws_order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), ws_panel};
-        ws<<<static_cast<unsigned>(ws_grid), kConsumerThreads + 32, WS_SMEM, stream>>>(in_map, out_map, ws_order,
-                                                                                      static_cast<long long>(tiles));
-        b2k::note_launch();
-        B2K_RETURN_IF_LAUNCH_FAILED("b2k_transpose2d (tma) launch");
-        return B2K_OK;
-    }
     auto kernel = split ? transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>
                         : transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>;
     static std::once_flag once;

@@ -364,9 +364,7 @@ struct Segment {
 };
 
 constexpr int kFillWarps = 8;
-constexpr int kPitch32 = 33;  // words per staged row of 32 f32 values
-constexpr int kPitch64 = 17;  // doubles per staged row of 16 f64 values
-constexpr int kStageBytes = 32 * kPitch64 * 8;  // >= 32*kPitch32*4
+constexpr int kStageBytes = 32 * 128;  // 32 rows of 128 bytes per warp
 
 template <typename T, int DRAW>
 __device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
@@ -383,20 +381,28 @@ __device__ __forceinline__ T draw_one(uint64_t &s0, uint64_t &s1) {
 
 // One segment for the 32 generators [base, base+32) of this warp.
 //
-// Every lane draws CHUNK values into its own padded row of the warp's staging
-// tile (row pitch of an odd number of banks: conflict-free), then the warp
-// writes the tile out row-wise.  Full tiles whose output rows are 16-byte
-// aligned leave as 128-bit stores, four rows of 128 bytes per instruction;
-// ragged tiles (last generators, last columns, odd counts) leave one row of
-// scalars per instruction.
+// Every lane draws a chunk of 128 bytes (32 f32 / 16 f64 values) into its own row of
+// the warp's staging tile, 16 bytes at a time, then the warp writes the tile out
+// row-wise.  Rows are 128 bytes with the 16-byte pieces XOR-swizzled by the row
+// number (piece p of row r sits at piece p ^ (r & 7)), so both the lanes' 128-bit
+// stores (eight rows, one piece each per quarter-warp) and the 128-bit loads of the
+// flush (one row, eight pieces per quarter-warp) are free of bank conflicts.  Full
+// tiles whose output rows are 16-byte aligned leave as 128-bit stores, four rows of
+// 128 bytes per instruction; ragged tiles (last generators, last columns, odd
+// counts) leave one row of scalars per instruction.
+template <typename T>
+__device__ __forceinline__ T *stage_slot(unsigned char *stage, int row, int col) {
+    constexpr int PER = 16 / sizeof(T);
+    return reinterpret_cast<T *>(stage + row * 128 + (((col / PER) ^ (row & 7)) << 4)) + (col % PER);
+}
+
 template <typename T, int DRAW, int UNROLL>
 __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool live, int64_t base,
-                                             int64_t n, const Segment &seg, void *stage) {
-    constexpr int CHUNK = sizeof(T) == 4 ? 32 : 16;
-    constexpr int PITCH = sizeof(T) == 4 ? kPitch32 : kPitch64;
+                                             int64_t n, const Segment &seg, void *stage_ptr) {
+    constexpr int CHUNK = 128 / sizeof(T);
     constexpr int ROWS_PER_STORE = 32 / CHUNK;
-    constexpr int PER_LANE = 16 / sizeof(T);        // items in one 128-bit store
-    T *buf = static_cast<T *>(stage);
+    constexpr int PER = 16 / sizeof(T);             // items in one 128-bit piece
+    unsigned char *stage = static_cast<unsigned char *>(stage_ptr);
     T *out = static_cast<T *>(seg.out);
     const int lane = threadIdx.x & 31;
     const bool rows_full = base + 32 <= n;
@@ -405,49 +411,49 @@ __device__ __forceinline__ void fill_segment(uint64_t &s0, uint64_t &s1, bool li
     for (int64_t c0 = 0; c0 < seg.count; c0 += CHUNK) {
         const int m = (seg.count - c0 < CHUNK) ? static_cast<int>(seg.count - c0) : CHUNK;
         if (live) {
-            T *row = buf + lane * PITCH;
             if (m == CHUNK) {
                 // uniforms are short integer chains: unroll deep to overlap generators;
                 // normals are long libdevice chains: unroll little to keep registers free
                 constexpr int U = (DRAW == B2K_UNIFORM_F32 || DRAW == B2K_UNIFORM_F64) ? 16 : UNROLL;
-#pragma unroll U
-                for (int i = 0; i < CHUNK; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
+                constexpr int PIECES_UNROLLED = U / PER > 0 ? U / PER : 1;
+                unsigned char *row = stage + lane * 128;
+                const int swizzle = (lane & 7) << 4;
+#pragma unroll PIECES_UNROLLED
+                for (int p = 0; p < 8; ++p) {
+                    union {
+                        uint4 raw;
+                        T v[PER];
+                    } piece;
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) piece.v[k] = draw_one<T, DRAW>(s0, s1);
+                    *reinterpret_cast<uint4 *>(row + ((p << 4) ^ swizzle)) = piece.raw;
+                }
             } else {
-                for (int i = 0; i < m; ++i) row[i] = draw_one<T, DRAW>(s0, s1);
+                for (int i = 0; i < m; ++i) *stage_slot<T>(stage, lane, i) = draw_one<T, DRAW>(s0, s1);
             }
         }
         __syncwarp();
         if (vector_ok && m == CHUNK) {
             // lane -> (row within a group of four, 16-byte piece of that row)
             const int sub = lane >> 3, piece = lane & 7;
-            const T *src = buf + sub * PITCH + piece * PER_LANE;
-            T *dst = out + (base + sub) * seg.count + c0 + piece * PER_LANE;
+            T *dst = out + (base + sub) * seg.count + c0 + piece * PER;
             const int64_t dst_step = 4 * seg.count;
 #pragma unroll
             for (int r = 0; r < 32; r += 4) {
-                if constexpr (sizeof(T) == 4) {
-                    float4 v;
-                    v.x = src[0]; v.y = src[1]; v.z = src[2]; v.w = src[3];
-                    __stcs(reinterpret_cast<float4 *>(dst), v);
-                } else {
-                    double2 v;
-                    v.x = src[0]; v.y = src[1];
-                    __stcs(reinterpret_cast<double2 *>(dst), v);
-                }
-                src += 4 * PITCH;
+                const int row = r + sub;
+                const uint4 v = *reinterpret_cast<const uint4 *>(stage + row * 128 + ((piece ^ (row & 7)) << 4));
+                __stcs(reinterpret_cast<uint4 *>(dst), v);
                 dst += dst_step;
             }
         } else {
             const int col = lane % CHUNK;
             const int sub = lane / CHUNK;
             if (col < m) {
-                const T *src = buf + sub * PITCH + col;
                 T *dst = out + (base + sub) * seg.count + c0 + col;
                 const int64_t dst_step = static_cast<int64_t>(ROWS_PER_STORE) * seg.count;
                 const int64_t rows_here = n - base - sub;  // rows this lane may still write
                 for (int r = 0; r < 32 && r < rows_here; r += ROWS_PER_STORE) {
-                    *dst = *src;
-                    src += ROWS_PER_STORE * PITCH;
+                    *dst = *stage_slot<T>(stage, r + sub, col);
                     dst += dst_step;
                 }
             }
@@ -471,7 +477,7 @@ __device__ __forceinline__ void run_segment(uint64_t &s0, uint64_t &s1, bool liv
 template <int MINBLOCKS, int UNROLL>
 __global__ void __launch_bounds__(kFillWarps * 32, MINBLOCKS)
 xoro_fill_kernel(ulonglong2 *__restrict__ states, int64_t n, Segment seg0, Segment seg1) {
-    __shared__ __align__(16) unsigned char stage_all[kFillWarps][kStageBytes];
+    __shared__ __align__(128) unsigned char stage_all[kFillWarps][kStageBytes];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     void *stage = stage_all[warp];
     const int64_t groups = (n + 31) / 32;
