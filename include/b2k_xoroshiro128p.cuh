@@ -38,12 +38,20 @@ struct xoroshiro128p_generator {
         *reinterpret_cast<ulonglong2 *>(states + index) = make_ulonglong2(s0, s1);
     }
 
-    /* random.py:97-115: returns s0+s1 of the state before the update */
+    /* random.py:97-115: returns s0+s1 of the state before the update.  The two
+     * rotations and the shift are spelled as 32-bit funnel shifts (one instruction
+     * per output word): rotl(x, 55) = halves swapped then rotated by 23,
+     * rotl(x, 36) = halves swapped then rotated by 4. */
     __device__ __forceinline__ uint64_t next() {
         const uint64_t out = s0 + s1;
-        s1 ^= s0;
-        s0 = ((s0 << 55) | (s0 >> 9)) ^ s1 ^ (s1 << 14);
-        s1 = (s1 << 36) | (s1 >> 28);
+        const uint32_t a_lo = static_cast<uint32_t>(s0), a_hi = static_cast<uint32_t>(s0 >> 32);
+        const uint32_t b_lo = static_cast<uint32_t>(s1) ^ a_lo, b_hi = static_cast<uint32_t>(s1 >> 32) ^ a_hi;
+        const uint32_t r_hi = __funnelshift_l(a_hi, a_lo, 23), r_lo = __funnelshift_l(a_lo, a_hi, 23);
+        const uint32_t n0_lo = r_lo ^ b_lo ^ (b_lo << 14);
+        const uint32_t n0_hi = r_hi ^ b_hi ^ __funnelshift_l(b_lo, b_hi, 14);
+        const uint32_t n1_hi = __funnelshift_l(b_hi, b_lo, 4), n1_lo = __funnelshift_l(b_lo, b_hi, 4);
+        s0 = (static_cast<uint64_t>(n0_hi) << 32) | n0_lo;
+        s1 = (static_cast<uint64_t>(n1_hi) << 32) | n1_lo;
         return out;
     }
     /* random.py:146-156.  (x >> 11) * 2^-53 is exact in float64, so rounding the
