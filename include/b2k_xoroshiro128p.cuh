@@ -43,8 +43,8 @@ struct xoroshiro128p_generator {
      * per output word): rotl(x, 55) = halves swapped then rotated by 23,
      * rotl(x, 36) = halves swapped then rotated by 4. */
     __device__ __forceinline__ uint64_t next() {
-        const uint64_t out = s0 + s1;
         const uint32_t a_lo = static_cast<uint32_t>(s0), a_hi = static_cast<uint32_t>(s0 >> 32);
+        const uint64_t out = s0 + s1;
         const uint32_t b_lo = static_cast<uint32_t>(s1) ^ a_lo, b_hi = static_cast<uint32_t>(s1 >> 32) ^ a_hi;
         const uint32_t r_hi = __funnelshift_l(a_hi, a_lo, 23), r_lo = __funnelshift_l(a_lo, a_hi, 23);
         const uint32_t n0_lo = r_lo ^ b_lo ^ (b_lo << 14);
