@@ -224,6 +224,49 @@ class ShardedReduce:
         return host_fold(op, host, dtype.type(init))
 
 
+def gather_partial_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
+    """All ranks' partial result rows (raw ``uint8`` bytes, same length on every
+    rank) stacked into a ``[world, nbytes]`` tensor on every rank: ONE collective."""
+    dist, world, _ = _world(group)
+    if world == 1:
+        return partial.reshape(1, -1)
+    stacked = torch.empty(world * partial.numel(), dtype=torch.uint8, device=partial.device)
+    if partial.is_cuda:
+        dist.all_gather_into_tensor(stacked, partial.contiguous(), group=group)
+    else:
+        dist.all_gather(list(stacked.view(world, -1).unbind(0)), partial.contiguous(), group=group)
+    return stacked.view(world, -1)
+
+
+class ShardedReduceAxis:
+    """``Reduce(fn).along_axis`` over a matrix whose ROWS are sharded by contiguous
+    range across the ranks of a process group.  Axis 1 (one result per row) needs
+    no exchange: every rank returns the results of its own rows.  Axis 0 (one result
+    per column): every rank reduces its rows, one all-gather stacks the partial rows
+    and the stack is reduced along axis 0 by the same kernel, which also folds
+    ``init`` in once; the full result is returned on every rank."""
+
+    def __init__(self, functor):
+        self._local = Reduce(functor)
+
+    def __call__(self, local_rows, axis, init=0, stream=0, group=None):
+        from .api import auto_device
+        from .devicearray import DeviceNDArray, _c_strides
+        dtype = np.dtype(local_rows.dtype)
+        op = self._local._compile(dtype)
+        if isinstance(op, str):
+            raise NotImplementedError("sharded axis-wise reduction supports the precompiled table ops only")
+        if axis % 2 == 1:
+            return self._local.along_axis(local_rows, 1, init=init, stream=stream)
+        darr, _ = auto_device(local_rows, stream=stream)
+        partial = self._local.along_axis(darr, 0, init=op_identity(op, dtype), stream=stream)
+        stacked = gather_partial_rows(partial._bytes_view(), group=group)
+        world, cols = stacked.shape[0], partial.shape[0]
+        rows = DeviceNDArray((world, cols), _c_strides((world, cols), dtype.itemsize), dtype, stream=stream,
+                             gpu_data=(stacked.view(-1), 0))
+        return self._local.along_axis(rows, 0, init=init, stream=stream)
+
+
 def op_name(op: int) -> str:
     return OP_NAMES[op]
 
@@ -249,5 +292,5 @@ def sharded_cast(src_local, src_format, dst_format, out=None, saturate=1, stream
     return cast(src_local, src_format, dst_format, out=out, saturate=saturate, stream=stream)
 
 
-__all__ = ["PeerMailboxes", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
+__all__ = ["PeerMailboxes", "ShardedReduceAxis", "gather_partial_rows", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
            "create_sharded_xoroshiro128p_states", "sharded_cast", "op_name"]

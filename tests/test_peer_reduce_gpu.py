@@ -126,6 +126,15 @@ def test_wait_that_runs_out_sets_status_and_returns():
     mine.close(); theirs.close()
 
 
+def test_row_sharded_axis_reduce_in_a_world_of_one():
+    full = np.random.default_rng(9).integers(-2 ** 31, 2 ** 31, size=(1000, 70), dtype=np.int32)
+    red = sharded.ShardedReduceAxis(lambda a, b: a + b)
+    with np.errstate(over="ignore"):
+        assert red(full, 0, init=5).copy_to_host().tobytes() == (np.add.reduce(full, axis=0, dtype=np.int32)
+                                                                 + np.int32(5)).tobytes()
+        assert red(full, 1).copy_to_host().tobytes() == np.add.reduce(full, axis=1, dtype=np.int32).tobytes()
+
+
 def test_argument_checks():
     L = _lib.lib()
     init = np.zeros(1, dtype=np.int32)
@@ -174,6 +183,17 @@ def _rank_main(rank, world, port, errors):
                     assert abs(nccl - want) <= 1e-12 * np.abs(whole).sum()
                 else:
                     assert fused == want == nccl, (name, dt, fused, nccl, want)
+        # a row-sharded matrix reduced along both axes
+        full = np.random.default_rng(9).integers(-2 ** 31, 2 ** 31, size=(4099, 260), dtype=np.int32)
+        lo, hi = sharded.shard_bounds(full.shape[0], world, rank)
+        for fn, ufunc in ((lambda a, b: a + b, np.add), (lambda a, b: max(a, b), np.maximum)):
+            red = sharded.ShardedReduceAxis(fn)
+            cols = red(full[lo:hi], 0, init=3).copy_to_host()
+            with np.errstate(over="ignore"):
+                want = ufunc(ufunc.reduce(full, axis=0, dtype=np.int32), np.int32(3), dtype=np.int32)
+                want_rows = ufunc(ufunc.reduce(full[lo:hi], axis=1, dtype=np.int32), np.int32(3), dtype=np.int32)
+            assert cols.tobytes() == want.tobytes()
+            assert red(full[lo:hi], 1, init=3).copy_to_host().tobytes() == want_rows.tobytes()
         dist.barrier()
         boxes.close()
         dist.destroy_process_group()

@@ -121,6 +121,28 @@ def _body_cast(rank, world):
     assert sum(sizes) == n
 
 
+def _body_axis_rows(rank, world):
+    # rows sharded by contiguous range; the stacked partial rows folded along axis 0
+    # must give the column results of the whole matrix (NumPy stands in for the kernel)
+    from numba_cuda_b200 import _lib, sharded
+    rng = np.random.default_rng(5)
+    full = rng.integers(-2 ** 31, 2 ** 31, size=(1001, 37), dtype=np.int32)
+    lo, hi = sharded.shard_bounds(full.shape[0], world, rank)
+    for ufunc, op in ((np.add, _lib.ADD), (np.maximum, _lib.MAX), (np.bitwise_xor, _lib.XOR)):
+        ident = sharded.op_identity(op, np.int32)
+        with np.errstate(over="ignore"):
+            partial = ufunc(ufunc.reduce(full[lo:hi], axis=0, dtype=np.int32), ident, dtype=np.int32)
+        stacked = sharded.gather_partial_rows(torch.from_numpy(partial.view(np.uint8).copy()))
+        assert tuple(stacked.shape) == (world, 37 * 4)
+        rows = stacked.numpy().view(np.int32)
+        with np.errstate(over="ignore"):
+            got = ufunc.reduce(rows, axis=0, dtype=np.int32)
+            want = ufunc.reduce(full, axis=0, dtype=np.int32)
+        assert got.tobytes() == want.tobytes()
+        # rank order is preserved: row r of the stack is rank r's partial
+        assert rows[rank].tobytes() == partial.tobytes()
+
+
 def _body_world_mismatch(rank, world):
     from numba_cuda_b200 import sharded
     with pytest.raises(ValueError):
@@ -168,6 +190,10 @@ def test_rng_shards_concatenate_to_single_stream():
 
 def test_cast_shards_are_aligned_and_complete():
     _run("_body_cast")
+
+
+def test_row_sharded_axis_reduce_combines_with_one_gather():
+    _run("_body_axis_rows")
 
 
 def test_bad_rank_is_rejected():
