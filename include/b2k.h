@@ -196,6 +196,11 @@ B2K_API int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, int
 B2K_API int b2k_assign(void *dst_dev, const void *src_dev, int ndim, const int64_t *shape,
                        const int64_t *dst_strides, const int64_t *src_strides, int64_t itemsize,
                        void *stream);
+/* The same with ONE source item of 1..16 bytes read from host memory at call time
+ * and carried to the kernel in its parameters (d_arr[key] = scalar): no staging
+ * copy, nothing for the caller to keep alive. */
+B2K_API int b2k_fill(void *dst_dev, int ndim, const int64_t *shape, const int64_t *dst_strides,
+                     const void *value_host, int64_t itemsize, void *stream);
 
 /* ---- xoroshiro128p ------------------------------------------------------
  * b2k_xoroshiro128p_init replaces init_xoroshiro128p_states_cpu + the H2D copy

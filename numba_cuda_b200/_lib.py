@@ -46,6 +46,7 @@ SIGNATURES = {
     "b2k_reduce_axis_scratch_bytes": (_i64, [_i64, _i64, _i32, _i32]),
     "b2k_reduce_axis": (_i32, [_i32, _i32, _vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
     "b2k_assign": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "b2k_fill": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp]),
     "b2k_xoroshiro128p_tables_bytes": (_i64, []),
     "b2k_xoroshiro128p_build_tables": (_i32, [_vp, _i64, _vp]),
     "b2k_xoroshiro128p_init": (_i32, [_vp, _i64, _u64, _u64, _vp, _i64, _vp]),

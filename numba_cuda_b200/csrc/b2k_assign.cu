@@ -25,6 +25,7 @@
 //  * the TMA tile transpose of b2k_transpose_tma.cu, as a stack of 2-D problems,
 //    when such a permutation also meets the tensor-map alignment rules.
 #include <algorithm>
+#include <cstring>
 
 #include "b2k_internal.cuh"
 
@@ -37,6 +38,9 @@ struct Axes {
     int64_t len[kMaxAxes];        // in units
     int64_t dst_step[kMaxAxes];   // bytes
     int64_t src_step[kMaxAxes];   // bytes, 0 = broadcast
+    // b2k_fill: the one source item travels in the kernel parameters; kernels that
+    // are handed a null source read from here instead
+    alignas(16) unsigned char value[16];
 };
 
 template <typename Index>
@@ -63,6 +67,7 @@ template <typename U, typename Index>
 __global__ void __launch_bounds__(kDirectThreads)
 assign_direct_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
                      const __grid_constant__ Axes ax, uint64_t total) {
+    if (src == nullptr) src = ax.value;
     const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kDirectThreads * kDirectUnroll) + threadIdx.x;
     U value[kDirectUnroll];
     int64_t doff[kDirectUnroll];
@@ -88,6 +93,7 @@ template <typename S, typename Index>
 __global__ void __launch_bounds__(kDirectThreads)
 assign_fill_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
                    const __grid_constant__ Axes ax, uint64_t total) {
+    if (src == nullptr) src = ax.value;
     constexpr int REP = 16 / sizeof(S);
     const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kDirectThreads * kDirectUnroll) + threadIdx.x;
 #pragma unroll
@@ -119,6 +125,7 @@ __global__ void __launch_bounds__(kDirectThreads)
 assign_repeat_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
                      const __grid_constant__ Axes ax, uint64_t total, uint64_t units_per_chunk, int64_t repeat_step,
                      int64_t repeat_len) {
+    if (src == nullptr) src = ax.value;
     const uint64_t g = static_cast<uint64_t>(blockIdx.x) * kDirectThreads + threadIdx.x;
     if (g >= total) return;
     int64_t doff, soff;
@@ -240,6 +247,7 @@ template <typename U>
 int launch_repeat(void *dst, const void *src, const Axes &ax, int b, cudaStream_t stream) {
     // the other axes keep their order; the chunks of axis b become the slowest axis
     Axes rest{};
+    memcpy(rest.value, ax.value, sizeof rest.value);
     const int64_t chunks = (ax.len[b] + kRepeatRows - 1) / kRepeatRows;
     rest.n = ax.n;
     rest.len[0] = chunks;
@@ -292,8 +300,30 @@ int launch_fill(void *dst, const void *src, const Axes &ax, uint64_t total, bool
 
 }  // namespace
 
+namespace {
+int assign_impl(void *dst, const void *src, const void *value_host, int ndim, const int64_t *shape,
+                const int64_t *dst_strides, const int64_t *src_strides, int64_t itemsize, void *stream);
+}  // namespace
+
 extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *shape, const int64_t *dst_strides,
                           const int64_t *src_strides, int64_t itemsize, void *stream) {
+    if (ndim > 0 && !src_strides) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null shape or strides");
+    return assign_impl(dst, src, nullptr, ndim, shape, dst_strides, src_strides, itemsize, stream);
+}
+
+extern "C" int b2k_fill(void *dst, int ndim, const int64_t *shape, const int64_t *dst_strides, const void *value_host,
+                        int64_t itemsize, void *stream) {
+    if (!value_host) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_fill: null value");
+    if (itemsize < 1 || itemsize > 16)
+        return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_fill: items of 1..16 bytes (got %lld)", static_cast<long long>(itemsize));
+    if (ndim < 0 || ndim > 32) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_fill: ndim %d outside 0..32", ndim);
+    const int64_t zeros[32] = {};
+    return assign_impl(dst, nullptr, value_host, ndim, shape, dst_strides, zeros, itemsize, stream);
+}
+
+namespace {
+int assign_impl(void *dst, const void *src, const void *value_host, int ndim, const int64_t *shape,
+                const int64_t *dst_strides, const int64_t *src_strides, int64_t itemsize, void *stream) {
     if (ndim < 0 || ndim > 32) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: ndim %d outside 0..32", ndim);
     if (itemsize <= 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: itemsize must be positive");
     if (ndim > 0 && (!shape || !dst_strides || !src_strides))
@@ -313,7 +343,7 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
                              static_cast<long long>(shape[k]));
         axes[n++] = Axis{shape[k], dst_strides[k], src_strides[k]};
     }
-    if (!dst || !src) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null pointer");
+    if (!dst || (!src && !value_host)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null pointer");
 
     // densest destination axis last; equal strides keep their given order
     std::stable_sort(axes, axes + n, [](const Axis &a, const Axis &b) { return iabs64(a.ds) > iabs64(b.ds); });
@@ -335,6 +365,7 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
     int64_t unit = 16;
     auto fits = [&](int64_t u) {
         if (axes[n - 1].len % u) return false;
+        // (a null source stands for the 16-byte aligned value in the kernel parameters)
         if (reinterpret_cast<uintptr_t>(dst) % u || reinterpret_cast<uintptr_t>(src) % u) return false;
         for (int k = 0; k + 1 < n; ++k)
             if (axes[k].ds % u || axes[k].ss % u) return false;
@@ -350,6 +381,7 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
 
     Axes ax{};
     ax.n = n;
+    if (value_host) memcpy(ax.value, value_host, static_cast<size_t>(itemsize));
     uint64_t total = 1;
     bool narrow = true;
     for (int k = 0; k < n; ++k) {
@@ -445,3 +477,4 @@ extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *s
     default: return launch_unit<uint8_t>(dst, src, ax, total, narrow, q, st);
     }
 }
+}  // namespace

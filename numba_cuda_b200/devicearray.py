@@ -350,6 +350,11 @@ class DeviceNDArray:
             host = np.asarray(value)
             if host.dtype != self.dtype:
                 host = host.astype(self.dtype)
+            if host.ndim == 0 and 0 < self.dtype.itemsize <= 16:
+                fill_strided(lhs._ptr, lhs.shape, lhs.strides, host, stream)
+                if synchronous:
+                    torch.cuda.current_stream().synchronize()
+                return
             rhs = _upload(host, stream)
         if rhs.ndim > lhs.ndim:
             raise ValueError("Can't assign %s-D array to %s-D self" % (rhs.ndim, lhs.ndim))
@@ -425,6 +430,20 @@ _TORCH_DTYPES = {
     "<f2": torch.float16, "<f4": torch.float32, "<f8": torch.float64, "|b1": torch.bool,
     "<c8": torch.complex64, "<c16": torch.complex128, "bfloat16": torch.bfloat16,
 }
+
+
+def fill_strided(dst_ptr, shape, dst_strides, value: np.ndarray, stream=0):
+    """``dst[idx] = value`` for one item of at most 16 bytes: one ``b2k_fill``
+    launch, the item travels in the kernel parameters."""
+    import ctypes
+    from . import _lib
+    nd = len(shape)
+    if any(int(n) == 0 for n in shape):
+        return
+    arr = ctypes.c_int64 * max(nd, 1)
+    raw = value.tobytes()
+    _lib.check(_lib.lib().b2k_fill(dst_ptr, nd, arr(*[int(v) for v in shape]), arr(*[int(v) for v in dst_strides]),
+                                   raw, len(raw), stream_ptr(stream)))
 
 
 def _upload(host: np.ndarray, stream=0) -> "DeviceNDArray":

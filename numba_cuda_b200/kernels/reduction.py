@@ -112,7 +112,7 @@ class _Scratch:
                 with torch.cuda.stream(_torch_stream(stream)):
                     scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
                     result = torch.zeros(16, dtype=torch.uint8, device="cuda")
-                entry = (scratch, result, nbytes)
+                entry = (scratch, result, nbytes, torch.zeros(16, dtype=torch.uint8, pin_memory=True))
                 cls._pool[key] = entry
             return entry
 
@@ -179,10 +179,12 @@ class Reduce:
         if darr.strides[0] != darr.dtype.itemsize:
             darr = _gather_contiguous(darr, stream)
 
-        scratch, slot, scratch_bytes = _Scratch.get(stream)
+        scratch, slot, scratch_bytes, landing = _Scratch.get(stream)
         if res is not None:
             dres, _ = auto_device(res, stream=stream)
-            check_array_compatibility(dres[:1], _OneItem(arr.dtype))
+            if not (dres.ndim == 1 and dres.shape[0] >= 1 and dres.dtype == arr.dtype):
+                # the reference copies partials[:1] into res[:1] (reduction.py:260-261)
+                check_array_compatibility(dres[:1], _OneItem(arr.dtype))
             out_ptr = dres._ptr
         else:
             out_ptr = slot.data_ptr()
@@ -198,10 +200,15 @@ class Reduce:
                 out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
         if res is not None:
             return None
-        host = np.empty(1, dtype=arr.dtype)
-        with torch.cuda.stream(_torch_stream(stream)):
-            torch.from_numpy(host.view(np.uint8)).copy_(slot[: arr.dtype.itemsize])
-        return host[0]
+        # one item back through a page-locked landing buffer, ordered on the call's stream
+        ts = _torch_stream(stream)
+        if torch.cuda.current_stream() == ts:
+            landing.copy_(slot, non_blocking=True)
+        else:
+            with torch.cuda.stream(ts):
+                landing.copy_(slot, non_blocking=True)
+        ts.synchronize()
+        return landing.numpy()[: arr.dtype.itemsize].view(arr.dtype)[0]
 
 
     def along_axis(self, arr, axis, res=None, init=0, stream=0):

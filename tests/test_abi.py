@@ -64,6 +64,12 @@ def test_argument_errors_are_reported_on_host():
     assert b"destination stride 0" in L.b2k_last_error()
     assert L.b2k_assign(None, 2048, 2, arr2(4, 4), arr2(16, 4), arr2(16, 4), 4, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_assign(None, None, 2, arr2(4, 0), arr2(16, 4), arr2(16, 4), 4, None) == 0          # empty
+    four = np.float32(1.5).tobytes()
+    assert L.b2k_fill(1024, 2, arr2(4, 4), arr2(16, 4), None, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_fill(1024, 2, arr2(4, 4), arr2(16, 4), four, 17, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_fill(None, 2, arr2(4, 4), arr2(16, 4), four, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_fill(1024, 2, arr2(4, 4), arr2(0, 4), four, 4, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_fill(None, 2, arr2(0, 4), arr2(16, 4), four, 4, None) == 0                        # empty
     assert L.b2k_reduce_axis(_lib.ADD, 99, 1024, 4, 4, 16, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, 4, 4, 16, 2, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_reduce_axis(_lib.ADD, _lib.F32, 1024, -4, 4, 16, 0, init.ctypes.data, 2048, None, 0, None) == _lib.ERR_INVALID_ARG

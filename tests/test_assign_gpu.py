@@ -105,6 +105,25 @@ def test_setitem_errors_follow_the_reference():
         dev[4, 0] = 1.0
 
 
+def test_fill_entry_point_every_item_size_and_alignment():
+    # b2k_fill: the item travels in the kernel parameters; dense, strided and byte-offset targets
+    import torch
+    L = _lib.lib()
+    for item in (1, 2, 3, 4, 8, 12, 16):
+        value = np.random.default_rng(item).integers(0, 256, size=item, dtype=np.uint8)
+        for offset in (0, 1, 4, 16):
+            buf = torch.zeros(offset + 7 * 48 * item + 64, dtype=torch.uint8, device="cuda")
+            arr2 = ctypes.c_int64 * 2
+            # 7 rows of 40 items inside rows of 48 items
+            rc = L.b2k_fill(buf.data_ptr() + offset, 2, arr2(7, 40), arr2(48 * item, item), value.tobytes(), item, None)
+            assert rc == 0, L.b2k_last_error()
+            host = buf.cpu().numpy()
+            want = np.zeros_like(host)
+            view = want[offset:offset + 7 * 48 * item].reshape(7, 48, item)
+            view[:, :40, :] = value
+            assert host.tobytes() == want.tobytes(), (item, offset)
+
+
 def test_setitem_with_stream():
     s = cuda.stream()
     host = _filled((33, 65), np.float64, 5)
