@@ -538,14 +538,22 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
     if (!rc.valid)
         return b2k::fail(B2K_ERR_UNSUPPORTED, "xoroshiro128p: jump recurrence self-check failed");
 
-    State u[128];
-    basis_states(seed, u, 128);
-    Basis basis;
-    for (int j = 0; j < 128; ++j) {
-        basis.w[j][0] = static_cast<uint32_t>(u[j].s0);
-        basis.w[j][1] = static_cast<uint32_t>(u[j].s0 >> 32);
-        basis.w[j][2] = static_cast<uint32_t>(u[j].s1);
-        basis.w[j][3] = static_cast<uint32_t>(u[j].s1 >> 32);
+    // the 128 basis states of the seed (16 k generator steps): kept per thread for the
+    // last seed, since shards and repeated initialisations reuse it
+    thread_local bool basis_known = false;
+    thread_local uint64_t basis_seed = 0;
+    thread_local Basis basis;
+    if (!basis_known || basis_seed != seed) {
+        State u[128];
+        basis_states(seed, u, 128);
+        for (int j = 0; j < 128; ++j) {
+            basis.w[j][0] = static_cast<uint32_t>(u[j].s0);
+            basis.w[j][1] = static_cast<uint32_t>(u[j].s0 >> 32);
+            basis.w[j][2] = static_cast<uint32_t>(u[j].s1);
+            basis.w[j][3] = static_cast<uint32_t>(u[j].s1 >> 32);
+        }
+        basis_seed = seed;
+        basis_known = true;
     }
     Poly4 p_low{{static_cast<uint32_t>(rc.p_low.lo), static_cast<uint32_t>(rc.p_low.lo >> 32),
                  static_cast<uint32_t>(rc.p_low.hi), static_cast<uint32_t>(rc.p_low.hi >> 32)}};
