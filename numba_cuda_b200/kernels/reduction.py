@@ -215,8 +215,11 @@ class Reduce:
         """Reduce a 2-D array along ``axis`` (0: over rows, one result per column;
         1: over columns, one result per row).  ``init`` is folded into every
         result, as ``__call__`` folds it into its one.  Returns a 1-D device array
-        (``res`` if given).  The reference stops at 1-D arrays
-        (reduction.py:217-218); table ops only."""
+        (``res`` if given).  C-contiguous arrays of more than two axes are reduced
+        along one axis too and give an array of the remaining shape.  The reference
+        stops at 1-D arrays (reduction.py:217-218); table ops only."""
+        if arr.ndim > 2:
+            return self._along_axis_nd(arr, axis, res, init, stream)
         if arr.ndim != 2:
             raise TypeError("only support 2D array")
         if axis not in (0, 1, -1, -2):
@@ -257,6 +260,50 @@ class Reduce:
         _lib.check(L.b2k_reduce_axis(op, _DTYPE_CODES[dtype], darr._ptr, rows, cols, pitch, axis,
                                      init_host.ctypes.data, dres._ptr, scratch.data_ptr() if need else None,
                                      need, stream_ptr(stream)))
+        return dres
+
+
+    def _along_axis_nd(self, arr, axis, res, init, stream):
+        """One axis of a C-contiguous N-D array: the axes before it fold into an outer
+        count, the axes behind it into an inner run.  inner == 1 or outer == 1 is one
+        matrix reduction; otherwise every outer slab is a (length x inner) matrix
+        reduced along its rows."""
+        from ..api import device_array
+        nd = arr.ndim
+        if not -nd <= axis < nd:
+            raise ValueError("axis %r is out of bounds for an array of %d axes" % (axis, nd))
+        axis %= nd
+        darr, _ = auto_device(arr, stream=stream)
+        if not darr.flags["C_CONTIGUOUS"]:
+            raise ValueError("arrays of more than two axes must be C-contiguous")
+        dtype, item = np.dtype(darr.dtype), np.dtype(darr.dtype).itemsize
+        shape = darr.shape
+        outer = int(np.prod(shape[:axis], dtype=np.int64))
+        length = shape[axis]
+        inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+        out_shape = shape[:axis] + shape[axis + 1:]
+        if res is None:
+            dres = device_array(out_shape, dtype, stream=stream)
+        else:
+            dres, _ = auto_device(res, stream=stream, copy=False)
+            if np.dtype(dres.dtype) != dtype:
+                raise TypeError("incompatible dtype: %s vs. %s" % (dres.dtype, dtype))
+            if tuple(dres.shape) != tuple(out_shape) or not dres.flags["C_CONTIGUOUS"]:
+                raise ValueError("incompatible shape: res must be a C-contiguous array of shape %s" % (out_shape,))
+        if outer * inner == 0:
+            return dres
+        flat = dres._sub((outer * inner,), (item,), 0)
+        if inner == 1:
+            self.along_axis(darr._sub((outer, length), (length * item, item), 0), 1, res=flat, init=init, stream=stream)
+        elif outer == 1:
+            self.along_axis(darr._sub((length, inner), (inner * item, item), 0), 0, res=flat, init=init, stream=stream)
+        else:
+            if outer > 4096:
+                raise NotImplementedError("more than 4096 outer slabs: permute the reduced axis to the front first")
+            slab = length * inner * item
+            for o in range(outer):
+                self.along_axis(darr._sub((length, inner), (inner * item, item), o * slab), 0,
+                                res=flat._sub((inner,), (item,), o * inner * item), init=init, stream=stream)
         return dres
 
 

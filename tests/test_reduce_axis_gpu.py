@@ -133,6 +133,27 @@ def test_results_are_reproducible_and_res_is_used():
         assert res.copy_to_host().tobytes() == a.tobytes()
 
 
+@pytest.mark.parametrize("shape", [(5, 6, 7), (3, 1, 9), (2, 3, 4, 5), (40, 33, 17), (1, 50, 64), (64, 50, 1)])
+def test_one_axis_of_an_nd_array(shape):
+    host = _data(shape, np.int32, 11)
+    dev = cuda.to_device(host)
+    for axis in range(-1, len(shape)):
+        got = REDUCERS["add"].along_axis(dev, axis, init=3).copy_to_host()
+        with np.errstate(over="ignore"):
+            want = np.add.reduce(host, axis=axis, dtype=np.int32) + np.int32(3)
+        assert got.shape == want.shape and got.tobytes() == want.tobytes()
+    f = _data(shape, np.float64, 12)
+    got = REDUCERS["max"].along_axis(cuda.to_device(f), 1, init=-np.inf).copy_to_host()
+    assert got.tobytes() == f.max(axis=1).tobytes()
+    out = cuda.device_array(shape[:1] + shape[2:], dtype=np.int32)
+    assert REDUCERS["xor"].along_axis(dev, 1, res=out) is out
+    assert out.copy_to_host().tobytes() == np.bitwise_xor.reduce(host, axis=1).tobytes()
+    with pytest.raises(ValueError, match="out of bounds"):
+        REDUCERS["add"].along_axis(dev, len(shape))
+    with pytest.raises(ValueError, match="C-contiguous"):
+        REDUCERS["add"].along_axis(cuda.to_device(np.zeros((4, 6, 8), dtype=np.int32))[:, ::2], 0)
+
+
 def test_argument_errors():
     r = REDUCERS["add"]
     with pytest.raises(TypeError, match="only support 2D array"):
