@@ -20,8 +20,8 @@
 //  * repeat: the source repeats along a slower axis (one row assigned to every
 //    row): each thread reads its unit once and stores it to 16 rows;
 //  * tiled: when the source is dense along a DIFFERENT axis q than the destination
-//    (axis permutations), square tiles over (destination axis p, source axis q)
-//    go through shared memory so that both sides see coalesced accesses;
+//    (axis permutations), tiles over (destination axis p, source axis q) go
+//    through shared memory so that both sides see coalesced accesses;
 //  * the TMA tile transpose of b2k_transpose_tma.cu, as a stack of 2-D problems,
 //    when such a permutation also meets the tensor-map alignment rules.
 #include <algorithm>
@@ -144,13 +144,85 @@ assign_repeat_kernel(unsigned char *__restrict__ dst, const unsigned char *__res
 }
 
 // Tiles over (axis p = ax.n-1, the fastest in the destination; axis q, the densest
-// in the source).  Blocks enumerate (other axes..., q tiles, p tiles).  TILE = 64
-// for units up to 4 bytes (16 loads in flight per thread), 32 for wider units.
+// in the source): TQ units along q by TP units along p.  Blocks enumerate (other
+// axes..., q tiles, p tiles).  Throughput follows the bytes a thread has in flight
+// between the two barriers, so 1- and 2-byte units get 128x64 tiles (32 loads per
+// thread).
 constexpr int kTiledThreads = 256;
 
-template <typename U, typename Index, int TILE>
+template <typename U>
+struct TileShape {
+    static constexpr int TQ = sizeof(U) <= 2 ? 128 : (sizeof(U) == 4 ? 64 : 32);
+    static constexpr int TP = sizeof(U) <= 4 ? 64 : 32;
+    // row pitch in units: one bank (4 bytes) more than the row for units up to 4
+    // bytes, one unit more for wider ones, so column reads spread over the banks
+    static constexpr int PITCH = TQ + (sizeof(U) <= 4 ? 4 / sizeof(U) : 1);
+};
+
+template <typename U, typename Index>
 __global__ void __launch_bounds__(kTiledThreads)
 assign_tiled_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                    const __grid_constant__ Axes ax, int q, int64_t tiles_p, int64_t tiles_q) {
+    constexpr int TQ = TileShape<U>::TQ, TP = TileShape<U>::TP, PITCH = TileShape<U>::PITCH;
+    __shared__ U cell[TP * PITCH];
+    const int p = ax.n - 1;
+    // block -> (rest, tq, tp)
+    uint64_t b = blockIdx.x;
+    const int64_t tp = static_cast<int64_t>(b % static_cast<uint64_t>(tiles_p));
+    b /= static_cast<uint64_t>(tiles_p);
+    const int64_t tq = static_cast<int64_t>(b % static_cast<uint64_t>(tiles_q));
+    Index rest = static_cast<Index>(b / static_cast<uint64_t>(tiles_q));
+    int64_t dbase = 0, sbase = 0;
+#pragma unroll
+    for (int k = kMaxAxes - 1; k >= 0; --k) {
+        if (k < ax.n && k != p && k != q) {
+            const Index len = static_cast<Index>(ax.len[k]);
+            const Index quo = rest / len;
+            const Index i = rest - quo * len;
+            rest = quo;
+            dbase += static_cast<int64_t>(i) * ax.dst_step[k];
+            sbase += static_cast<int64_t>(i) * ax.src_step[k];
+        }
+    }
+    const int64_t p0 = tp * TP, q0 = tq * TQ;
+    const int64_t np = ax.len[p] - p0, nq = ax.len[q] - q0;  // extent left along each tile axis
+    // load: lanes along q (dense in the source), rows along p
+    {
+        constexpr int ROWS = kTiledThreads / TQ, PASSES = TP / ROWS;
+        const int tx = threadIdx.x % TQ, ty = threadIdx.x / TQ;
+        const unsigned char *from = src + sbase + p0 * ax.src_step[p] + (q0 + tx) * ax.src_step[q];
+        const int64_t row_step = ax.src_step[p];
+        U held[PASSES];
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const int row = ty + j * ROWS;
+            if (tx < nq && row < np) held[j] = *reinterpret_cast<const U *>(from + row * row_step);
+        }
+        // all loads are issued before the first shared-memory store waits for one
+        asm volatile("" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) cell[(ty + j * ROWS) * PITCH + tx] = held[j];
+    }
+    __syncthreads();
+    // store: lanes along p (dense in the destination), rows along q
+    {
+        constexpr int ROWS = kTiledThreads / TP, PASSES = TQ / ROWS;
+        const int tx = threadIdx.x % TP, ty = threadIdx.x / TP;
+        unsigned char *to = dst + dbase + (p0 + tx) * ax.dst_step[p] + q0 * ax.dst_step[q];
+        const int64_t row_step = ax.dst_step[q];
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const int row = ty + j * ROWS;
+            if (tx < np && row < nq) *reinterpret_cast<U *>(to + row * row_step) = cell[tx * PITCH + row];
+        }
+    }
+}
+
+// Square tiles of TILE x TILE units for units of 4 bytes and more (the rectangular
+// form above, instantiated at 64x64, compiled to a slower kernel for them).
+template <typename U, typename Index, int TILE>
+__global__ void __launch_bounds__(kTiledThreads)
+assign_tiled_square_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
                     const __grid_constant__ Axes ax, int q, int64_t tiles_p, int64_t tiles_q) {
     // a row pitch of TILE + 1 units keeps the column reads of 4-byte units conflict-free
     __shared__ U cell[TILE][TILE + 1];
@@ -212,21 +284,29 @@ int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool
     unsigned char *d = static_cast<unsigned char *>(dst);
     const unsigned char *s = static_cast<const unsigned char *>(src);
     if (q >= 0) {
-        constexpr int TILE = sizeof(U) <= 4 ? 64 : 32;
+        constexpr bool SQUARE = sizeof(U) >= 4;
+        constexpr int TP = SQUARE ? (sizeof(U) == 4 ? 64 : 32) : TileShape<U>::TP;
+        constexpr int TQ = SQUARE ? TP : TileShape<U>::TQ;
         const int p = ax.n - 1;
-        const int64_t tiles_p = (ax.len[p] + TILE - 1) / TILE;
-        const int64_t tiles_q = (ax.len[q] + TILE - 1) / TILE;
+        const int64_t tiles_p = (ax.len[p] + TP - 1) / TP;
+        const int64_t tiles_q = (ax.len[q] + TQ - 1) / TQ;
         uint64_t rest = 1;
         for (int k = 0; k < ax.n; ++k)
             if (k != p && k != q) rest *= static_cast<uint64_t>(ax.len[k]);
         const uint64_t blocks = rest * static_cast<uint64_t>(tiles_p) * static_cast<uint64_t>(tiles_q);
         if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many tiles");
-        if (narrow_index)
-            assign_tiled_kernel<U, uint32_t, TILE><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
-                d, s, ax, q, tiles_p, tiles_q);
-        else
-            assign_tiled_kernel<U, uint64_t, TILE><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
-                d, s, ax, q, tiles_p, tiles_q);
+        const unsigned grid = static_cast<unsigned>(blocks);
+        if constexpr (SQUARE) {
+            if (narrow_index)
+                assign_tiled_square_kernel<U, uint32_t, TP><<<grid, kTiledThreads, 0, stream>>>(d, s, ax, q, tiles_p, tiles_q);
+            else
+                assign_tiled_square_kernel<U, uint64_t, TP><<<grid, kTiledThreads, 0, stream>>>(d, s, ax, q, tiles_p, tiles_q);
+        } else {
+            if (narrow_index)
+                assign_tiled_kernel<U, uint32_t><<<grid, kTiledThreads, 0, stream>>>(d, s, ax, q, tiles_p, tiles_q);
+            else
+                assign_tiled_kernel<U, uint64_t><<<grid, kTiledThreads, 0, stream>>>(d, s, ax, q, tiles_p, tiles_q);
+        }
     } else {
         const uint64_t per_block = kDirectThreads * kDirectUnroll;
         const uint64_t blocks = (total + per_block - 1) / per_block;

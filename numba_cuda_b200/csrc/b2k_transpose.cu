@@ -104,6 +104,16 @@ extern "C" int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, 
         if (rc != B2K_ERR_UNSUPPORTED) return rc;
     }
 
+    // Items of up to 4 bytes: the 64x64 tiles of the strided-assignment kernels measured
+    // 15-25 % faster than the 32x32 tiles below (out[j, i] = in[i, j] is an assignment
+    // whose source strides are swapped).
+    if ((itemsize == 1 || itemsize == 2 || itemsize == 4) && b2k::env_int("B2K_TRANSPOSE_VIA_ASSIGN", 1) != 0) {
+        const int64_t shape[2] = {cols, rows};
+        const int64_t dst_steps[2] = {out_stride0, out_stride1};
+        const int64_t src_steps[2] = {in_stride1, in_stride0};
+        return b2k_assign(out_dev, in_dev, 2, shape, dst_steps, src_steps, itemsize, stream);
+    }
+
     const int64_t base_in = static_cast<int64_t>(reinterpret_cast<uintptr_t>(in_dev));
     const int64_t base_out = static_cast<int64_t>(reinterpret_cast<uintptr_t>(out_dev));
     auto fits = [&](int64_t a) {
