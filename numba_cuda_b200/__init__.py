@@ -16,9 +16,9 @@ fallback: without the library or without a GPU the calls raise.
 """
 from . import _lib, bf16, casts, fp8, kernels, random, sharded  # noqa: F401
 from .api import (as_cuda_array, auto_device, default_stream, device_array, device_array_like,  # noqa: F401
-                  external_stream, is_available, is_bfloat16_supported, is_cuda_array,
+                  event, event_elapsed_time, external_stream, is_available, is_bfloat16_supported, is_cuda_array,
                   is_fp8_supported, pinned_array, pinned_array_like, stream, synchronize, to_device)
-from .devicearray import DeviceNDArray, Stream  # noqa: F401
+from .devicearray import DeviceNDArray, Event, Stream  # noqa: F401
 from .kernels import reduction as _reduction, transpose as _transpose  # noqa: F401
 from .kernels.reduction import Reduce
 

@@ -9,7 +9,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .devicearray import (DeviceNDArray, Stream, _c_strides, _f_strides, from_cuda_array_interface,
+from .devicearray import (DeviceNDArray, Event, Stream, _c_strides, _f_strides, from_cuda_array_interface,
                           stream_ptr)
 
 
@@ -40,6 +40,17 @@ def stream() -> Stream:
     """A new CUDA stream."""
     _require_cuda()
     return Stream()
+
+
+def event(timing=True) -> Event:
+    """A new CUDA event (api.py ``event``)."""
+    _require_cuda()
+    return Event(timing=timing)
+
+
+def event_elapsed_time(evtstart: Event, evtend: Event) -> float:
+    """Milliseconds between two recorded events (api.py ``event_elapsed_time``)."""
+    return evtstart.elapsed_time(evtend)
 
 
 def default_stream() -> Stream:
@@ -169,7 +180,8 @@ def auto_device(obj, stream=0, copy=True):
 
 
 __all__ = [
-    "is_available", "is_bfloat16_supported", "is_fp8_supported", "synchronize", "stream",
+    "is_available", "is_bfloat16_supported", "is_fp8_supported", "synchronize", "stream", "event",
+    "event_elapsed_time",
     "default_stream", "external_stream", "device_array", "device_array_like", "to_device",
     "is_cuda_array", "as_cuda_array", "pinned_array", "pinned_array_like", "auto_device", "stream_ptr",
     "strides_like",

@@ -57,6 +57,31 @@ class Stream:
         return f"<b200 CUDA stream {self.handle:#x}>"
 
 
+class Event:
+    """A CUDA event (numba/cuda/cudadrv/driver.py ``Event``: ``record(stream=0)``,
+    ``query()``, ``synchronize()``, ``wait(stream=0)``, ``elapsed_time(evtend)``),
+    for timing the library calls the way numba-cuda users time kernels."""
+
+    def __init__(self, timing=True):
+        self._ev = torch.cuda.Event(enable_timing=bool(timing))
+
+    def record(self, stream=0):
+        self._ev.record(_torch_stream(stream))
+
+    def query(self) -> bool:
+        return self._ev.query()
+
+    def synchronize(self) -> None:
+        self._ev.synchronize()
+
+    def wait(self, stream=0) -> None:
+        _torch_stream(stream).wait_event(self._ev)
+
+    def elapsed_time(self, evtend: "Event") -> float:
+        """Milliseconds from this event to ``evtend``."""
+        return self._ev.elapsed_time(evtend._ev)
+
+
 def stream_ptr(stream) -> int:
     """0 / Stream / torch stream / raw pointer -> cudaStream_t value."""
     if stream is None or (isinstance(stream, int) and stream == 0):

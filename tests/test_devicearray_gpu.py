@@ -159,3 +159,17 @@ def test_device_array_like_of_views_and_transposes():
     like = cuda.device_array_like(d_t)
     assert like.shape == d_t.shape and like.strides == (40, 8)
     assert like.flags["C_CONTIGUOUS"] and not like.flags["F_CONTIGUOUS"]
+
+
+def test_events_time_a_library_call():
+    start, end = cuda.event(), cuda.event()
+    x = cuda.to_device(np.ones(1 << 22, dtype=np.float32))
+    s = cuda.stream()
+    start.record(s)
+    total = cuda.reduce(lambda a, b: a + b)(x, stream=s)
+    end.record(s)
+    end.synchronize()
+    assert total == np.float32(1 << 22) and end.query()
+    ms = cuda.event_elapsed_time(start, end)
+    assert 0.0 < ms < 1000.0 and ms == start.elapsed_time(end)
+    end.wait(s)                                  # enqueue-only; must not raise
