@@ -276,6 +276,173 @@ assign_tiled_square_kernel(unsigned char *__restrict__ dst, const unsigned char 
     }
 }
 
+// Single bytes, source dense along q and destination dense along p, any pitches:
+// the tiled kernel above would move one byte per lane.  Here a CTA moves a tile of
+// 128 x 128 bytes with 32-bit global accesses on both sides although no row is
+// aligned:
+//   1. every source row segment is read as the ALIGNED words that cover it (33 at
+//      most, coalesced; 17 loads in flight per lane) into R, with the row's byte
+//      offset s = address mod 4 noted beside it;
+//   2. threads transpose 4 x 4 byte blocks: four unaligned 4-byte groups are cut out
+//      of R with a funnel shift by the row's offset, permuted in registers and
+//      written to T (rows = q, bytes = p) as aligned words;
+//   3. every destination row segment is written as aligned words cut out of T with a
+//      funnel shift by the destination offset; the partial words at the two ends
+//      go out as single bytes.
+// Words of step 1 that are not wholly inside the source's address extent
+// [src_lo, src_hi) are put together from single bytes, so nothing outside the
+// array is touched.  Pitches in words (34 for R, 33 for T) make the 32-bit accesses
+// of steps 1-3 bank-conflict free (lanes: 8 column blocks x 4 row blocks in step 2).
+constexpr int kByteTile = 128;
+constexpr int kRawPitch = 34, kTurnedPitch = 33;
+
+__device__ __forceinline__ uint32_t load_covering_word(const unsigned char *word, const unsigned char *lo,
+                                                       const unsigned char *hi) {
+    if (word >= lo && word + 4 <= hi) return *reinterpret_cast<const uint32_t *>(word);
+    uint32_t v = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+        if (word + b >= lo && word + b < hi) v |= static_cast<uint32_t>(word[b]) << (8 * b);
+    return v;
+}
+
+template <typename Index>
+__global__ void __launch_bounds__(kTiledThreads)
+assign_byte_tiles_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                         const __grid_constant__ Axes ax, int q, int64_t tiles_p, int64_t tiles_q,
+                         const unsigned char *src_lo, const unsigned char *src_hi) {
+    __shared__ uint32_t raw[kByteTile * kRawPitch];
+    __shared__ uint32_t turned[kByteTile * kTurnedPitch];
+    __shared__ unsigned char offset_of_row[kByteTile];
+    const int p = ax.n - 1;
+    uint64_t blk = blockIdx.x;
+    const int64_t tp = static_cast<int64_t>(blk % static_cast<uint64_t>(tiles_p));
+    blk /= static_cast<uint64_t>(tiles_p);
+    const int64_t tq = static_cast<int64_t>(blk % static_cast<uint64_t>(tiles_q));
+    Index rest = static_cast<Index>(blk / static_cast<uint64_t>(tiles_q));
+    int64_t dbase = 0, sbase = 0;
+#pragma unroll
+    for (int k = kMaxAxes - 1; k >= 0; --k) {
+        if (k < ax.n && k != p && k != q) {
+            const Index len = static_cast<Index>(ax.len[k]);
+            const Index quo = rest / len;
+            const Index i = rest - quo * len;
+            rest = quo;
+            dbase += static_cast<int64_t>(i) * ax.dst_step[k];
+            sbase += static_cast<int64_t>(i) * ax.src_step[k];
+        }
+    }
+    const int64_t p0 = tp * kByteTile, q0 = tq * kByteTile;
+    const int np = static_cast<int>(ax.len[p] - p0 < kByteTile ? ax.len[p] - p0 : kByteTile);
+    const int nq = static_cast<int>(ax.len[q] - q0 < kByteTile ? ax.len[q] - q0 : kByteTile);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int ROWS_PER_WARP = kByteTile / (kTiledThreads / 32);  // 16
+
+    // 1. source rows -> raw (aligned covering words)
+    {
+        const unsigned char *tile = src + sbase + p0 * ax.src_step[p] + q0;
+        const int64_t row_step = ax.src_step[p];
+        uint32_t held[ROWS_PER_WARP + 1];
+        // Tiles whose covering words all lie inside the source extent (all but those
+        // holding the array's first or last bytes) take plain predicated loads, which
+        // the compiler can keep in flight together; the others check every word.
+        const unsigned char *end_a = tile, *end_b = tile + (np - 1) * row_step;
+        const unsigned char *lowest = end_a < end_b ? end_a : end_b, *highest = end_a < end_b ? end_b : end_a;
+        const bool interior = lowest - 3 >= src_lo && highest + nq + 7 <= src_hi;
+        if (interior) {
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) {
+                const int r = warp * ROWS_PER_WARP + i;
+                const unsigned char *first = tile + r * row_step;
+                const int s = static_cast<int>(reinterpret_cast<uintptr_t>(first) & 3u);
+                held[i] = 0u;
+                if (r < np && 4 * lane < s + nq) held[i] = *reinterpret_cast<const uint32_t *>(first - s + 4 * lane);
+            }
+            const int r = warp * ROWS_PER_WARP + (lane & (ROWS_PER_WARP - 1));
+            const unsigned char *first = tile + r * row_step;
+            const int s = static_cast<int>(reinterpret_cast<uintptr_t>(first) & 3u);
+            held[ROWS_PER_WARP] = 0u;
+            if (lane < ROWS_PER_WARP && r < np && 4 * 32 < s + nq)
+                held[ROWS_PER_WARP] = *reinterpret_cast<const uint32_t *>(first - s + 4 * 32);
+            if (lane < ROWS_PER_WARP) offset_of_row[r] = static_cast<unsigned char>(s);
+        } else {
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) {
+                const int r = warp * ROWS_PER_WARP + i;
+                const unsigned char *first = tile + r * row_step;
+                const int s = static_cast<int>(reinterpret_cast<uintptr_t>(first) & 3u);
+                const bool needed = r < np && 4 * lane < s + nq;
+                held[i] = needed ? load_covering_word(first - s + 4 * lane, src_lo, src_hi) : 0u;
+            }
+            // the 33rd word of a row exists when the row starts inside a word
+            const int r = warp * ROWS_PER_WARP + (lane & (ROWS_PER_WARP - 1));
+            const unsigned char *first = tile + r * row_step;
+            const int s = static_cast<int>(reinterpret_cast<uintptr_t>(first) & 3u);
+            const bool needed = lane < ROWS_PER_WARP && r < np && 4 * 32 < s + nq;
+            held[ROWS_PER_WARP] = needed ? load_covering_word(first - s + 4 * 32, src_lo, src_hi) : 0u;
+            if (lane < ROWS_PER_WARP) offset_of_row[r] = static_cast<unsigned char>(s);
+        }
+        asm volatile("" ::: "memory");  // all loads issued before the first store waits
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) raw[(warp * ROWS_PER_WARP + i) * kRawPitch + lane] = held[i];
+        if (lane < ROWS_PER_WARP) raw[(warp * ROWS_PER_WARP + lane) * kRawPitch + 32] = held[ROWS_PER_WARP];
+    }
+    __syncthreads();
+
+    // 2. 4 x 4 byte blocks: raw (rows p) -> turned (rows q)
+    {
+        const int col_block_lo = lane & 7, row_block_lo = lane >> 3;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int cb = it * 8 + col_block_lo;    // bytes 4cb .. 4cb+3 of the source rows
+            const int rb = warp * 4 + row_block_lo;  // source rows 4rb .. 4rb+3
+            uint32_t x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = 4 * rb + i;
+                const int o = offset_of_row[r] + 4 * cb;
+                const uint32_t *words = raw + r * kRawPitch + (o >> 2);
+                x[i] = __funnelshift_r(words[0], words[1], 8 * (o & 3));
+            }
+            const uint32_t t0 = __byte_perm(x[0], x[1], 0x5140), t1 = __byte_perm(x[2], x[3], 0x5140);
+            const uint32_t t2 = __byte_perm(x[0], x[1], 0x7362), t3 = __byte_perm(x[2], x[3], 0x7362);
+            uint32_t *out = turned + (4 * cb) * kTurnedPitch + rb;
+            out[0 * kTurnedPitch] = __byte_perm(t0, t1, 0x5410);
+            out[1 * kTurnedPitch] = __byte_perm(t0, t1, 0x7632);
+            out[2 * kTurnedPitch] = __byte_perm(t2, t3, 0x5410);
+            out[3 * kTurnedPitch] = __byte_perm(t2, t3, 0x7632);
+        }
+    }
+    __syncthreads();
+
+    // 3. turned -> destination rows (aligned words, single bytes at the ends)
+    {
+        unsigned char *tile = dst + dbase + q0 * ax.dst_step[q] + p0;
+        const int64_t row_step = ax.dst_step[q];
+        const unsigned char *turned_bytes = reinterpret_cast<const unsigned char *>(turned);
+        auto put = [&](int j, int k) {
+            unsigned char *first = tile + j * row_step;
+            const int t = static_cast<int>(reinterpret_cast<uintptr_t>(first) & 3u);
+            const int o = 4 * k - t;  // row byte position of the word's first byte
+            if (o + 4 <= 0 || o >= np) return;
+            if (o >= 0 && o + 4 <= np) {
+                const uint32_t *words = turned + j * kTurnedPitch + (o >> 2);
+                *reinterpret_cast<uint32_t *>(first + o) = __funnelshift_r(words[0], words[1], 8 * (o & 3));
+            } else {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (o + b >= 0 && o + b < np) first[o + b] = turned_bytes[j * (kTurnedPitch * 4) + o + b];
+            }
+        };
+#pragma unroll 4
+        for (int i = 0; i < ROWS_PER_WARP; ++i) {
+            const int j = warp * ROWS_PER_WARP + i;
+            if (j < nq) put(j, lane);
+        }
+        if (lane < ROWS_PER_WARP && warp * ROWS_PER_WARP + lane < nq) put(warp * ROWS_PER_WARP + lane, 32);
+    }
+}
+
 int64_t iabs64(int64_t v) { return v < 0 ? -v : v; }
 
 template <typename U>
@@ -318,6 +485,34 @@ int launch_unit(void *dst, const void *src, const Axes &ax, uint64_t total, bool
             assign_direct_kernel<U, uint64_t><<<static_cast<unsigned>(blocks), kDirectThreads, 0, stream>>>(
                 d, s, ax, total);
     }
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
+    return B2K_OK;
+}
+
+int launch_byte_tiles(void *dst, const void *src, const Axes &ax, uint64_t total, int q, cudaStream_t stream) {
+    const int p = ax.n - 1;
+    const int64_t tiles_p = (ax.len[p] + kByteTile - 1) / kByteTile;
+    const int64_t tiles_q = (ax.len[q] + kByteTile - 1) / kByteTile;
+    uint64_t rest = 1;
+    bool narrow = total <= 0xFFFFFFFFull;
+    const unsigned char *lo = static_cast<const unsigned char *>(src), *hi = lo + 1;
+    for (int k = 0; k < ax.n; ++k) {
+        if (k != p && k != q) rest *= static_cast<uint64_t>(ax.len[k]);
+        if (ax.len[k] > 0xFFFFFFFFll) narrow = false;
+        const int64_t span = (ax.len[k] - 1) * ax.src_step[k];
+        if (span < 0) lo += span; else hi += span;
+    }
+    const uint64_t blocks = rest * static_cast<uint64_t>(tiles_p) * static_cast<uint64_t>(tiles_q);
+    if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many tiles");
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    if (narrow)
+        assign_byte_tiles_kernel<uint32_t><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
+            d, s, ax, q, tiles_p, tiles_q, lo, hi);
+    else
+        assign_byte_tiles_kernel<uint64_t><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
+            d, s, ax, q, tiles_p, tiles_q, lo, hi);
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
     return B2K_OK;
@@ -554,7 +749,11 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
     case 8: return launch_unit<uint2>(dst, src, ax, total, narrow, q, st);
     case 4: return launch_unit<uint32_t>(dst, src, ax, total, narrow, q, st);
     case 2: return launch_unit<uint16_t>(dst, src, ax, total, narrow, q, st);
-    default: return launch_unit<uint8_t>(dst, src, ax, total, narrow, q, st);
+    default:
+        if (q >= 0 && ax.src_step[q] == 1 && ax.dst_step[n - 1] == 1 && ax.len[q] >= 32 && ax.len[n - 1] >= 32 &&
+            b2k::env_int("B2K_ASSIGN_BYTE_TILES", 1) != 0)
+            return launch_byte_tiles(dst, src, ax, total, q, st);
+        return launch_unit<uint8_t>(dst, src, ax, total, narrow, q, st);
     }
 }
 }  // namespace

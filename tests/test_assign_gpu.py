@@ -169,6 +169,26 @@ def test_permute_of_a_strided_view_into_a_given_array_and_errors():
         permute(dev, (2, 0, 1), cuda.device_array((40, 20, 30), dtype=np.int32))
 
 
+def test_byte_permutations_on_unaligned_views():
+    # 1-byte items: views that start at every byte offset and run with odd pitches, reversed rows
+    host = _filled((300, 523), np.uint8, 9)
+    dev = cuda.to_device(host)
+    for r0, c0, rows, cols in ((0, 0, 300, 523), (1, 1, 255, 401), (3, 2, 129, 130), (2, 3, 64, 33), (5, 7, 290, 500)):
+        view, dview = host[r0:r0 + rows, c0:c0 + cols], dev[r0:r0 + rows, c0:c0 + cols]
+        assert permute(dview, (1, 0)).copy_to_host().tobytes() == view.T.copy().tobytes()
+        out = cuda.device_array((cols + 3, rows + 5), dtype=np.uint8)          # odd destination pitch too
+        out[:] = 0
+        permute(dview, (1, 0), out[1:cols + 1, 2:rows + 2])
+        want = np.zeros((cols + 3, rows + 5), dtype=np.uint8)
+        want[1:cols + 1, 2:rows + 2] = view.T
+        assert out.copy_to_host().tobytes() == want.tobytes()
+    flipped = dev[::-1, 5:205]
+    assert permute(flipped, (1, 0)).copy_to_host().tobytes() == host[::-1, 5:205].T.copy().tobytes()
+    cube = _filled((7, 131, 197), np.int8, 10)
+    assert permute(cuda.to_device(cube), (0, 2, 1)).copy_to_host().tobytes() == cube.transpose(0, 2, 1).copy().tobytes()
+    assert permute(cuda.to_device(cube), (2, 1, 0)).copy_to_host().tobytes() == cube.transpose(2, 1, 0).copy().tobytes()
+
+
 def test_large_permutations_through_both_kernels():
     # (batch, rows, cols) -> (batch, cols, rows): tiles; (a, b, c) -> (b, a, c): direct, wide units
     host = _filled((8, 1000, 1100), np.float32, 8)

@@ -109,7 +109,10 @@ def test_small_shapes_every_itemsize(itemsize):
     (4096 * 8, 4, np.uint32), (300, 4104, np.uint16), (264, 136, np.uint16), (528, 1040, np.uint8),
     (1024, 2048, np.uint8), (514, 258, np.uint64), (520, 130, np.complex128), (1000, 2000, np.float32),
     (2049, 4100, np.float32), (1999, 3000, np.float64), (4097, 1032, np.uint16), (777, 1008, np.int8),
-    (1024, 2048, np.uint16), (448, 320, np.uint16), (1088, 960, np.int16), (640, 1152, np.uint8)])
+    (1024, 2048, np.uint16), (448, 320, np.uint16), (1088, 960, np.int16), (640, 1152, np.uint8),
+    # single bytes on pitches that rule out the TMA path: the aligned-word byte tiles
+    (777, 1001, np.uint8), (1001, 515, np.int8), (130, 4099, np.uint8), (4099, 130, np.bool_), (33, 35, np.uint8),
+    (129, 131, np.uint8), (255, 257, np.int8), (2047, 2049, np.uint8)])
 def test_tma_tile_path_shapes(rows, cols, dtype):
     rng = np.random.default_rng(rows * 7 + cols)
     a = rng.integers(0, 1 << 30, size=(rows, cols)).astype(dtype)
