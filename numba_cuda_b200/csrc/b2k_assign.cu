@@ -22,8 +22,12 @@
 //  * tiled: when the source is dense along a DIFFERENT axis q than the destination
 //    (axis permutations), tiles over (destination axis p, source axis q) go
 //    through shared memory so that both sides see coalesced accesses;
+//  * byte tiles: the same for single bytes, with 32-bit global accesses on rows of
+//    any alignment (covering words, funnel shifts, 4 x 4 byte blocks in registers);
 //  * the TMA tile transpose of b2k_transpose_tma.cu, as a stack of 2-D problems,
 //    when such a permutation also meets the tensor-map alignment rules.
+//
+// b2k_fill is the same machinery for one source item handed over by value.
 #include <algorithm>
 #include <cstring>
 
