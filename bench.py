@@ -540,6 +540,11 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
         ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [n], [4], [0], 4), iters, warm)
         res["n2_assign_fill_scalar_f32_2p28"] = dict(_roof(n * 4, ms, peak), note="write-only: 4 B per item",
                                                      spot_check=bool((b[-4096:] == a[0]).all()))
+        nbytes = n * 4 - 64
+        ms, _ = timed(lambda: assign(b.data_ptr() + 1, a.data_ptr(), [nbytes], [1], [1], 1), iters, warm)
+        res["n2_assign_copy_shifted_one_byte"] = dict(
+            _roof(nbytes * 2, ms, peak), note="destination one byte off the source's alignment",
+            spot_check=bool(torch.equal(b.view(torch.uint8)[1:4097], a.view(torch.uint8)[:4096])))
         rows = 16384 >> scale
         ms, _ = timed(lambda: assign(b.data_ptr(), a.data_ptr(), [rows // 2, 16384], [2 * 65536, 4], [2 * 65536, 4], 4),
                       iters, warm)

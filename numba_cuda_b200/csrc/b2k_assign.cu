@@ -19,6 +19,9 @@
 //    per-row fills): the unit is replicated into 16-byte stores;
 //  * repeat: the source repeats along a slower axis (one row assigned to every
 //    row): each thread reads its unit once and stores it to 16 rows;
+//  * runs: dense runs whose two sides are aligned differently (a slice shifted by
+//    one item, rows of an odd pitch) move as aligned 16-byte destination chunks
+//    fed from the two covering source words, shifted in registers;
 //  * tiled: when the source is dense along a DIFFERENT axis q than the destination
 //    (axis permutations), tiles over (destination axis p, source axis q) go
 //    through shared memory so that both sides see coalesced accesses;
@@ -447,6 +450,82 @@ assign_byte_tiles_kernel(unsigned char *__restrict__ dst, const unsigned char *_
     }
 }
 
+// Dense runs whose two sides are not aligned alike (a slice that starts one item in,
+// rows of an odd pitch): the unit chosen by the host would shrink to the item or a
+// byte.  Here a thread owns one ALIGNED 16-byte chunk of a destination run: it loads
+// the two aligned 16-byte source words that cover the chunk's bytes, shifts them by
+// the run's misalignment (a word select plus a funnel shift), and stores 16 bytes.
+// The partial chunks at the two ends of a run are copied byte by byte, and so is a
+// chunk whose covering words would reach outside the source's address extent
+// [src_lo, src_hi).  `ax` holds the axes other than the run axis.
+constexpr int kRunThreads = 256;
+constexpr int kRunUnroll = 2;
+
+template <typename Index>
+__global__ void __launch_bounds__(kRunThreads)
+assign_runs_kernel(unsigned char *__restrict__ dst, const unsigned char *__restrict__ src,
+                   const __grid_constant__ Axes ax, uint64_t total, int64_t run_bytes, uint64_t chunks_per_run,
+                   const unsigned char *src_lo, const unsigned char *src_hi) {
+    const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kRunThreads * kRunUnroll) + threadIdx.x;
+    uint4 lo_word[kRunUnroll], hi_word[kRunUnroll];
+    unsigned char *to[kRunUnroll];
+    const unsigned char *from[kRunUnroll];
+    int64_t pos0[kRunUnroll];
+    int mode[kRunUnroll];  // 0: nothing, 1: aligned words in lo/hi, 2: byte by byte
+#pragma unroll
+    for (int j = 0; j < kRunUnroll; ++j) {
+        const uint64_t g = base + static_cast<uint64_t>(j) * kRunThreads;
+        mode[j] = 0;
+        if (g >= total) continue;
+        const Index run = static_cast<Index>(g / chunks_per_run);
+        const int64_t chunk = static_cast<int64_t>(g - static_cast<uint64_t>(run) * chunks_per_run);
+        int64_t doff, soff;
+        locate<Index>(ax, run, doff, soff);
+        unsigned char *d = dst + doff;
+        const unsigned char *s = src + soff;
+        const int64_t p0 = 16 * chunk - static_cast<int64_t>(reinterpret_cast<uintptr_t>(d) & 15u);
+        if (p0 >= run_bytes) continue;
+        to[j] = d;
+        from[j] = s;
+        pos0[j] = p0;
+        mode[j] = 2;
+        if (p0 >= 0 && p0 + 16 <= run_bytes) {
+            const unsigned char *first = s + p0;
+            const unsigned char *aligned = first - (reinterpret_cast<uintptr_t>(first) & 15u);
+            if (aligned >= src_lo && aligned + 32 <= src_hi) {
+                lo_word[j] = *reinterpret_cast<const uint4 *>(aligned);
+                hi_word[j] = *reinterpret_cast<const uint4 *>(aligned + 16);
+                mode[j] = 1;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kRunUnroll; ++j) {
+        if (mode[j] == 1) {
+            const unsigned int m = static_cast<unsigned int>(reinterpret_cast<uintptr_t>(from[j] + pos0[j]) & 15u);
+            const uint32_t w[8] = {lo_word[j].x, lo_word[j].y, lo_word[j].z, lo_word[j].w,
+                                   hi_word[j].x, hi_word[j].y, hi_word[j].z, hi_word[j].w};
+            uint32_t u[6], t[5];
+#pragma unroll
+            for (int i = 0; i < 6; ++i) u[i] = (m & 8u) ? w[i + 2] : w[i];
+#pragma unroll
+            for (int i = 0; i < 5; ++i) t[i] = (m & 4u) ? u[i + 1] : u[i];
+            const unsigned int shift = (m & 3u) * 8u;
+            uint4 v;
+            v.x = __funnelshift_r(t[0], t[1], shift);
+            v.y = __funnelshift_r(t[1], t[2], shift);
+            v.z = __funnelshift_r(t[2], t[3], shift);
+            v.w = __funnelshift_r(t[3], t[4], shift);
+            *reinterpret_cast<uint4 *>(to[j] + pos0[j]) = v;
+        } else if (mode[j] == 2) {
+            for (int b = 0; b < 16; ++b) {
+                const int64_t pos = pos0[j] + b;
+                if (pos >= 0 && pos < run_bytes) to[j][pos] = from[j][pos];
+            }
+        }
+    }
+}
+
 int64_t iabs64(int64_t v) { return v < 0 ? -v : v; }
 
 template <typename U>
@@ -517,6 +596,44 @@ int launch_byte_tiles(void *dst, const void *src, const Axes &ax, uint64_t total
     else
         assign_byte_tiles_kernel<uint64_t><<<static_cast<unsigned>(blocks), kTiledThreads, 0, stream>>>(
             d, s, ax, q, tiles_p, tiles_q, lo, hi);
+    b2k::note_launch();
+    B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
+    return B2K_OK;
+}
+
+int launch_runs(void *dst, const void *src, const Axes &ax, cudaStream_t stream) {
+    // the fastest axis (dense on both sides, in bytes after scaling by the unit) is the run
+    const int n = ax.n;
+    const int64_t run_bytes = ax.len[n - 1] * ax.dst_step[n - 1];
+    Axes outer{};
+    outer.n = n - 1;
+    uint64_t runs = 1;
+    bool narrow = true;
+    const unsigned char *lo = static_cast<const unsigned char *>(src), *hi = lo + run_bytes;
+    for (int k = 0; k + 1 < n; ++k) {
+        outer.len[k] = ax.len[k];
+        outer.dst_step[k] = ax.dst_step[k];
+        outer.src_step[k] = ax.src_step[k];
+        runs *= static_cast<uint64_t>(ax.len[k]);
+        if (ax.len[k] > 0xFFFFFFFFll) narrow = false;
+        const int64_t span = (ax.len[k] - 1) * ax.src_step[k];
+        if (span < 0) lo += span; else hi += span;
+    }
+    if (runs > 0xFFFFFFFFull) narrow = false;
+    const uint64_t chunks_per_run = static_cast<uint64_t>((run_bytes + 15) / 16 + 1);
+    if (runs > (uint64_t(1) << 62) / chunks_per_run) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many chunks");
+    const uint64_t total = runs * chunks_per_run;
+    const uint64_t per_block = kRunThreads * kRunUnroll;
+    const uint64_t blocks = (total + per_block - 1) / per_block;
+    if (blocks > 0x7FFFFFFFull) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_assign: too many chunks");
+    unsigned char *d = static_cast<unsigned char *>(dst);
+    const unsigned char *s = static_cast<const unsigned char *>(src);
+    if (narrow)
+        assign_runs_kernel<uint32_t><<<static_cast<unsigned>(blocks), kRunThreads, 0, stream>>>(
+            d, s, outer, total, run_bytes, chunks_per_run, lo, hi);
+    else
+        assign_runs_kernel<uint64_t><<<static_cast<unsigned>(blocks), kRunThreads, 0, stream>>>(
+            d, s, outer, total, run_bytes, chunks_per_run, lo, hi);
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_assign launch");
     return B2K_OK;
@@ -695,6 +812,16 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
             default: return launch_fill<uint8_t>(dst, src, fill, units, narrow, st);
             }
         }
+    }
+
+    // Both sides dense along the fastest axis, but their alignments kept the unit
+    // below 16 bytes: long runs go through aligned 16-byte chunks all the same.
+    if (src && unit < 16 && ax.src_step[n - 1] == unit && ax.dst_step[n - 1] == unit &&
+        ax.len[n - 1] * unit >= 128 && b2k::env_int("B2K_ASSIGN_RUNS", 1) != 0) {
+        bool repeats = false;  // (a repeated source has its own kernel below)
+        for (int k = 0; k + 1 < n; ++k)
+            if (ax.src_step[k] == 0 && ax.len[k] >= 2 * kRepeatRows) repeats = true;
+        if (!repeats) return launch_runs(dst, src, ax, st);
     }
 
     // The source repeats along a slower axis and both sides are dense along the

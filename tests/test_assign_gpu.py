@@ -169,6 +169,32 @@ def test_permute_of_a_strided_view_into_a_given_array_and_errors():
         permute(dev, (2, 0, 1), cuda.device_array((40, 20, 30), dtype=np.int32))
 
 
+@pytest.mark.parametrize("dtype", [np.uint8, np.int16, np.float32, np.float64, REC])
+def test_copies_between_differently_aligned_runs(dtype):
+    # a[i:] = b[j:] for every pair of small offsets: the two sides of each run are aligned differently
+    n = 5000
+    src = _filled((n,), dtype, 13)
+    dsrc = cuda.to_device(src)
+    for i in (0, 1, 2, 3, 5, 15, 16, 17):
+        for j in (0, 1, 4, 7, 16, 33):
+            length = n - 40 - max(i, j)
+            host = _filled((n,), dtype, 14)
+            dev = cuda.to_device(host)
+            dev[i:i + length] = dsrc[j:j + length]
+            host[i:i + length] = src[j:j + length]
+            assert dev.copy_to_host().tobytes() == host.tobytes(), (i, j)
+    # rows of an odd pitch into rows of another odd pitch, short and long rows
+    for rows, cols in ((37, 1001), (300, 129), (5, 4097)):
+        a, b = _filled((rows, cols + 3), dtype, 15), _filled((rows, cols + 6), dtype, 16)
+        da, db = cuda.to_device(a), cuda.to_device(b)
+        db[:, 5:5 + cols] = da[:, 2:2 + cols]
+        b[:, 5:5 + cols] = a[:, 2:2 + cols]
+        assert db.copy_to_host().tobytes() == b.tobytes()
+        db[::-1, 1:1 + cols] = da[:, 0:cols]
+        b[::-1, 1:1 + cols] = a[:, 0:cols]
+        assert db.copy_to_host().tobytes() == b.tobytes()
+
+
 def test_byte_permutations_on_unaligned_views():
     # 1-byte items: views that start at every byte offset and run with odd pitches, reversed rows
     host = _filled((300, 523), np.uint8, 9)
