@@ -236,3 +236,57 @@ def test_c_abi_argument_checks():
     buf = torch.zeros(64, dtype=torch.uint8, device="cuda")
     rc = L.b2k_assign(buf.data_ptr(), buf.data_ptr() + 32, 1, arr3(4, 0, 0), arr3(0, 0, 0), arr3(4, 0, 0), 4, None)
     assert rc < 0 and b"destination stride 0" in L.b2k_last_error()
+
+
+def test_randomised_assignments_and_permutations_match_numpy():
+    # seeded differential test over every kernel the dispatcher can pick: random ranks,
+    # shapes, slices (steps of either sign), broadcasts, item sizes and byte offsets
+    rng = np.random.default_rng(2024)
+    dtypes = [np.uint8, np.int16, np.float32, np.float64, np.complex128, REC]
+
+    def random_view_key(shape):
+        key = []
+        for n in shape:
+            kind = rng.integers(0, 4)
+            if kind == 0 or n < 4:
+                key.append(slice(None))
+            else:
+                start = int(rng.integers(0, n // 2))
+                stop = int(rng.integers(start + 1, n + 1))
+                step = int(rng.choice([1, 1, 2, 3, -1, -2]))
+                key.append(slice(start, stop, step) if step > 0 else slice(stop - 1, start - 1 if start > 0 else None, step))
+        return tuple(key)
+
+    for case in range(160):
+        dtype = dtypes[int(rng.integers(0, len(dtypes)))]
+        nd = int(rng.integers(1, 5))
+        big = rng.integers(0, 3) == 0
+        shape = tuple(int(x) for x in rng.integers(1, 70 if big else 14, size=nd))
+        if big and nd >= 2:
+            shape = shape[:-2] + (int(rng.integers(33, 300)), int(rng.integers(33, 300)))
+        host = _filled(shape, dtype, 1000 + case)
+        dev = cuda.to_device(host)
+        key = random_view_key(shape)
+        target_shape = host[key].shape
+        mode = int(rng.integers(0, 4))
+        if mode == 0:      # scalar
+            value = _filled((), dtype, 2000 + case)[()]
+            dev[key] = value
+            host[key] = value
+        elif mode == 1:    # broadcast of trailing axes, some of length 1
+            vshape = tuple(n if rng.integers(0, 3) else 1 for n in target_shape[int(rng.integers(0, len(target_shape) + 1)):])
+            value = _filled(vshape, dtype, 3000 + case)
+            dev[key] = value
+            host[key] = value
+        elif mode == 2:    # from a strided device view of another array
+            other = _filled(tuple(2 * n + 3 for n in target_shape), dtype, 4000 + case)
+            okey = tuple(slice(int(rng.integers(0, 3)), None, 2) for _ in target_shape)
+            okey = tuple(slice(k.start, k.start + 2 * n, 2) for k, n in zip(okey, target_shape))
+            dev[key] = cuda.to_device(other)[okey]
+            host[key] = other[okey]
+        else:              # permutation of a view into a fresh array
+            axes = tuple(int(x) for x in rng.permutation(nd))
+            got = permute(dev[key], axes).copy_to_host()
+            assert got.tobytes() == host[key].transpose(axes).copy().tobytes(), (case, shape, key, axes)
+            continue
+        assert dev.copy_to_host().tobytes() == host.tobytes(), (case, shape, key, mode, np.dtype(dtype))
