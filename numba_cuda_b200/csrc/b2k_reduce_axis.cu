@@ -44,34 +44,39 @@ constexpr int kMaxChunks = 1024;
 constexpr int64_t kMaxTickets = 4096;
 constexpr int64_t kTicketRegion = kMaxTickets * 4;
 
-template <typename T, int V>
+// V items; packs of whole 32-bit words can also be addressed as words, which is how
+// the loads fill them and how 8- and 16-bit items are folded (a plain array of small
+// items would live in one register per item).
+template <typename T, int V, bool WORDS = (V * sizeof(T)) % 4 == 0>
 struct Pack {
     T e[V];
+};
+template <typename T, int V>
+struct Pack<T, V, true> {
+    union {
+        T e[V];
+        uint32_t w[V * sizeof(T) / 4];
+    };
 };
 
 template <typename T, int V>
 __device__ __forceinline__ Pack<T, V> load_pack(const unsigned char *p) {
     constexpr int BYTES = V * sizeof(T);
-    if constexpr (V == 1) {
-        Pack<T, 1> r;
+    Pack<T, V> r;
+    if constexpr (BYTES % 4 != 0) {
+        static_assert(V == 1, "a pack is one item or 4, 8 or 16 bytes");
         r.e[0] = *reinterpret_cast<const T *>(p);
-        return r;
+    } else if constexpr (BYTES == 16) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3])
+                     : "l"(p));
+    } else if constexpr (BYTES == 8) {
+        asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(r.w[0]), "=r"(r.w[1]) : "l"(p));
     } else {
-        static_assert(BYTES == 16 || BYTES == 8 || BYTES == 4, "a pack is one item or 4, 8 or 16 bytes");
-        union {
-            uint32_t w[BYTES / 4];
-            Pack<T, V> v;
-        } u;
-        if constexpr (BYTES == 16)
-            asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(u.w[0]), "=r"(u.w[1]), "=r"(u.w[2]), "=r"(u.w[3])
-                         : "l"(p));
-        else if constexpr (BYTES == 8)
-            asm volatile("ld.global.nc.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(u.w[0]), "=r"(u.w[1]) : "l"(p));
-        else
-            asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(u.w[0]) : "l"(p));
-        return u.v;
+        static_assert(BYTES == 4, "a pack is one item or 4, 8 or 16 bytes");
+        asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(r.w[0]) : "l"(p));
     }
+    return r;
 }
 
 // 8- and 16-bit items, four or two to a 32-bit word: the per-byte / per-halfword
@@ -85,7 +90,12 @@ struct WordWise {
 template <typename T, typename Op>
 __device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
     constexpr bool bytes = sizeof(T) == 1, is_signed = std::is_signed<T>::value;
-    if constexpr (std::is_same<Op, OpAdd>::value) return bytes ? __vadd4(a, b) : __vadd2(a, b);
+    if constexpr (std::is_same<Op, OpAdd>::value) {
+        // per-item wrap-around add inside a word: add the low bits of every item, then
+        // put the top bits back with a carry-less xor
+        constexpr uint32_t TOP = bytes ? 0x80808080u : 0x80008000u;
+        return ((a & ~TOP) + (b & ~TOP)) ^ ((a ^ b) & TOP);
+    }
     else if constexpr (std::is_same<Op, OpAnd>::value) return a & b;
     else if constexpr (std::is_same<Op, OpOr>::value) return a | b;
     else if constexpr (std::is_same<Op, OpXor>::value) return a ^ b;
@@ -98,17 +108,8 @@ __device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
 template <typename T, typename Op, int V>
 __device__ __forceinline__ void fold_into(Pack<T, V> &acc, const Pack<T, V> &v) {
     if constexpr (WordWise<T, Op>::value && (V * sizeof(T)) % 4 == 0) {
-        constexpr int WORDS = V * sizeof(T) / 4;
-        union Words {
-            Pack<T, V> items;
-            uint32_t w[WORDS];
-        };
-        Words a, b;
-        a.items = acc;
-        b.items = v;
 #pragma unroll
-        for (int k = 0; k < WORDS; ++k) a.w[k] = apply_word<T, Op>(a.w[k], b.w[k]);
-        acc = a.items;
+        for (int k = 0; k < static_cast<int>(V * sizeof(T) / 4); ++k) acc.w[k] = apply_word<T, Op>(acc.w[k], v.w[k]);
     } else {
 #pragma unroll
         for (int k = 0; k < V; ++k) acc.e[k] = Op::template apply<T>(acc.e[k], v.e[k]);
