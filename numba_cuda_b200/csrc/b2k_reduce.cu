@@ -76,6 +76,16 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
 constexpr int kMaxPeers = 16;
 constexpr int kMailboxWords = 2 * kMaxPeers * 2;  // [parity][writer]{value, flag}, 64-bit words
 
+// Folds the eight words of a 32-byte vector into a word of running results.
+template <typename T, typename Op>
+__device__ __forceinline__ uint32_t fold_words(uint32_t acc, const Bits256 &raw) {
+    acc = apply_word<T, Op>(acc, apply_word<T, Op>(raw.lo.x, raw.lo.y));
+    acc = apply_word<T, Op>(acc, apply_word<T, Op>(raw.lo.z, raw.lo.w));
+    acc = apply_word<T, Op>(acc, apply_word<T, Op>(raw.hi.x, raw.hi.y));
+    acc = apply_word<T, Op>(acc, apply_word<T, Op>(raw.hi.z, raw.hi.w));
+    return acc;
+}
+
 struct PeerLink {
     unsigned long long *mailbox[kMaxPeers];  // mailbox of every rank (own one included)
     int world;
@@ -176,23 +186,44 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) acc[u] = Op::template identity<T>();
 
-    for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
-        const Bits256 *p = xv + c * CHUNK + threadIdx.x;
-        Bits256 raw[UNROLL];
+    if constexpr (WordWise<T, Op>::value) {
+        // 8- and 16-bit integers: every slot keeps a word of four / two running results
+        // and folds the vectors a word at a time; the items meet after the loops
+        uint32_t packed[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(p + u * THREADS);
+        for (int u = 0; u < UNROLL; ++u) packed[u] = identity_word<T, Op>();
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+            const Bits256 *p = xv + c * CHUNK + threadIdx.x;
+            Bits256 raw[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            acc[u] = fold_vector<T, Op>(acc[u], raw[u].lo);
-            acc[u] = fold_vector<T, Op>(acc[u], raw[u].hi);
+            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(p + u * THREADS);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) packed[u] = fold_words<T, Op>(packed[u], raw[u]);
         }
-    }
-    // vectors past the last whole chunk, spread over the grid
-    for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
-         v += static_cast<int64_t>(gridDim.x) * THREADS) {
-        const Bits256 raw = load_stream32(xv + v);
-        acc[0] = fold_vector<T, Op>(acc[0], raw.lo);
-        acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
+        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
+             v += static_cast<int64_t>(gridDim.x) * THREADS)
+            packed[0] = fold_words<T, Op>(packed[0], load_stream32(xv + v));
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) acc[u] = fold_word<T, Op>(acc[u], packed[u]);
+    } else {
+        for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+            const Bits256 *p = xv + c * CHUNK + threadIdx.x;
+            Bits256 raw[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(p + u * THREADS);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                acc[u] = fold_vector<T, Op>(acc[u], raw[u].lo);
+                acc[u] = fold_vector<T, Op>(acc[u], raw[u].hi);
+            }
+        }
+        // vectors past the last whole chunk, spread over the grid
+        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
+             v += static_cast<int64_t>(gridDim.x) * THREADS) {
+            const Bits256 raw = load_stream32(xv + v);
+            acc[0] = fold_vector<T, Op>(acc[0], raw.lo);
+            acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
+        }
     }
     if (blockIdx.x == 0) {  // fewer than 32 scalars on each side
         if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);

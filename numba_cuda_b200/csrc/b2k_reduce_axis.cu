@@ -79,32 +79,6 @@ __device__ __forceinline__ Pack<T, V> load_pack(const unsigned char *p) {
     return r;
 }
 
-// 8- and 16-bit items, four or two to a 32-bit word: the per-byte / per-halfword
-// video instructions fold a whole word at once (add wraps per item, as the scalar op
-// does); products have no such form.
-template <typename T, typename Op>
-struct WordWise {
-    static constexpr bool value = std::is_integral<T>::value && sizeof(T) < 4 && !std::is_same<Op, OpMul>::value;
-};
-
-template <typename T, typename Op>
-__device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
-    constexpr bool bytes = sizeof(T) == 1, is_signed = std::is_signed<T>::value;
-    if constexpr (std::is_same<Op, OpAdd>::value) {
-        // per-item wrap-around add inside a word: add the low bits of every item, then
-        // put the top bits back with a carry-less xor
-        constexpr uint32_t TOP = bytes ? 0x80808080u : 0x80008000u;
-        return ((a & ~TOP) + (b & ~TOP)) ^ ((a ^ b) & TOP);
-    }
-    else if constexpr (std::is_same<Op, OpAnd>::value) return a & b;
-    else if constexpr (std::is_same<Op, OpOr>::value) return a | b;
-    else if constexpr (std::is_same<Op, OpXor>::value) return a ^ b;
-    else if constexpr (std::is_same<Op, OpMax>::value)
-        return bytes ? (is_signed ? __vmaxs4(a, b) : __vmaxu4(a, b)) : (is_signed ? __vmaxs2(a, b) : __vmaxu2(a, b));
-    else
-        return bytes ? (is_signed ? __vmins4(a, b) : __vminu4(a, b)) : (is_signed ? __vmins2(a, b) : __vminu2(a, b));
-}
-
 template <typename T, typename Op, int V>
 __device__ __forceinline__ void fold_into(Pack<T, V> &acc, const Pack<T, V> &v) {
     if constexpr (WordWise<T, Op>::value && (V * sizeof(T)) % 4 == 0) {

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 namespace b2k_reduce_ops {
 
 // ---- ops -----------------------------------------------------------------
@@ -95,6 +97,48 @@ __device__ __forceinline__ int64_t shuffle_xor(int64_t v, int mask) {
 __device__ __forceinline__ uint64_t shuffle_xor(uint64_t v, int mask) {
     return static_cast<uint64_t>(
         __shfl_xor_sync(0xffffffffu, static_cast<unsigned long long>(v), mask));
+}
+
+// ---- word-wise folds of small integers --------------------------------------
+// 8- and 16-bit items, four or two to a 32-bit word: the per-byte / per-halfword
+// video instructions fold a whole word at once (add wraps per item, as the scalar op
+// does); products have no such form.
+template <typename T, typename Op>
+struct WordWise {
+    static constexpr bool value = std::is_integral<T>::value && sizeof(T) < 4 && !std::is_same<Op, OpMul>::value;
+};
+
+template <typename T, typename Op>
+__device__ __forceinline__ uint32_t apply_word(uint32_t a, uint32_t b) {
+    constexpr bool bytes = sizeof(T) == 1, is_signed = std::is_signed<T>::value;
+    if constexpr (std::is_same<Op, OpAdd>::value) {
+        // per-item wrap-around add inside a word: add the low bits of every item, then
+        // put the top bits back with a carry-less xor
+        constexpr uint32_t TOP = bytes ? 0x80808080u : 0x80008000u;
+        return ((a & ~TOP) + (b & ~TOP)) ^ ((a ^ b) & TOP);
+    }
+    else if constexpr (std::is_same<Op, OpAnd>::value) return a & b;
+    else if constexpr (std::is_same<Op, OpOr>::value) return a | b;
+    else if constexpr (std::is_same<Op, OpXor>::value) return a ^ b;
+    else if constexpr (std::is_same<Op, OpMax>::value)
+        return bytes ? (is_signed ? __vmaxs4(a, b) : __vmaxu4(a, b)) : (is_signed ? __vmaxs2(a, b) : __vmaxu2(a, b));
+    else
+        return bytes ? (is_signed ? __vmins4(a, b) : __vminu4(a, b)) : (is_signed ? __vmins2(a, b) : __vminu2(a, b));
+}
+
+// The identity of Op replicated into every item of a word, and the fold of a word's
+// items into one item.
+template <typename T, typename Op>
+__device__ __forceinline__ uint32_t identity_word() {
+    const uint32_t one = static_cast<uint32_t>(static_cast<typename UnsignedOf<T>::type>(Op::template identity<T>()));
+    return sizeof(T) == 1 ? one * 0x01010101u : one * 0x00010001u;
+}
+template <typename T, typename Op>
+__device__ __forceinline__ T fold_word(T acc, uint32_t w) {
+#pragma unroll
+    for (int k = 0; k < static_cast<int>(4 / sizeof(T)); ++k)
+        acc = Op::template apply<T>(acc, static_cast<T>(w >> (8 * sizeof(T) * k)));
+    return acc;
 }
 
 }  // namespace b2k_reduce_ops
