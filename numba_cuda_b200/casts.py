@@ -74,8 +74,9 @@ def cast(src, src_format, dst_format, out=None, saturate=saturation_t.SATFINITE,
     """Convert every element of ``src`` (host or device array holding
     ``src_format`` items) to ``dst_format``; returns a device array of the same
     shape.  Round-to-nearest-even pairs: f32 <-> bf16 / e4m3 / e5m2 / f16,
-    f64 -> bf16, e8m0 -> bf16 / f32.  With ``rounding``: f32 -> bf16 toward zero,
-    +inf or -inf; f32 / bf16 -> e8m0 toward zero or +inf."""
+    f64 / bf16 -> e4m3 / e5m2, f64 -> bf16, e8m0 -> bf16 / f32.  With ``rounding``:
+    f32 -> bf16 toward zero, +inf or -inf; f32 / f64 / bf16 -> e8m0 toward zero or
+    +inf."""
     s, d = _format_code(src_format), _format_code(dst_format)
     dsrc, _ = auto_device(src, stream=stream)
     if dsrc.dtype.itemsize != _ITEMSIZE[s]:
@@ -110,9 +111,39 @@ def cvt_float_to_fp8(x, saturate, fp8_interpretation):
 
 def cvt_float2_to_fp8x2(x, saturate, fp8_interpretation):
     """(float32, float32) -> uint16 holding two codes, ``x[0]`` in the low byte."""
-    codes = cvt_float_to_fp8(np.asarray(x, dtype=np.float32).reshape(2), saturate, fp8_interpretation)
+    return _pack2(cvt_float_to_fp8(np.asarray(x, dtype=np.float32).reshape(2), saturate, fp8_interpretation))
+
+
+def _pair(x, dtype):
+    pair = np.asarray(x, dtype=dtype).reshape(-1)
+    if pair.size != 2:
+        raise ValueError("a two-element value is expected")
+    return pair
+
+
+def _pack2(codes) -> np.uint16:
     lo, hi = (int(v) for v in codes.copy_to_host())
     return np.uint16(lo | (hi << 8))
+
+
+def cvt_double_to_fp8(x, saturate, fp8_interpretation):
+    """float64 -> fp8 code (cuda_fp8.py:3269-3302): one rounding straight from the
+    double, not through float32."""
+    d = _lib.FMT_E5M2 if int(fp8_interpretation) == fp8_interpretation_t.E5M2 else _lib.FMT_E4M3
+    return _scalar_or_bulk(x, _lib.FMT_F64, d, saturate)
+
+
+def cvt_double2_to_fp8x2(x, saturate, fp8_interpretation):
+    """(float64, float64) -> uint16 holding two codes, ``x[0]`` in the low byte
+    (cuda_fp8.py:3305-3338)."""
+    return _pack2(cvt_double_to_fp8(_pair(x, np.float64), saturate, fp8_interpretation))
+
+
+def cvt_bfloat16raw_to_fp8(x, saturate, fp8_interpretation):
+    """bfloat16 (raw ``uint16`` bits or ml_dtypes values) -> fp8 code
+    (cuda_fp8.py:3413-3446)."""
+    d = _lib.FMT_E5M2 if int(fp8_interpretation) == fp8_interpretation_t.E5M2 else _lib.FMT_E4M3
+    return _scalar_or_bulk(x, _lib.FMT_BF16, d, saturate)
 
 
 # ---- fp8 value types: construct from float (SATFINITE) and convert back --------
@@ -186,6 +217,22 @@ def cvt_bfloat16raw_to_e8m0(x, saturate, rounding):
     return _scalar_or_bulk(x, _lib.FMT_BF16, _lib.FMT_E8M0, saturate, _e8m0_rounding(rounding))
 
 
+def cvt_double_to_e8m0(x, saturate, rounding):
+    """float64 -> E8M0 code (cuda_fp8.py:3557-3590)."""
+    return _scalar_or_bulk(x, _lib.FMT_F64, _lib.FMT_E8M0, saturate, _e8m0_rounding(rounding))
+
+
+def cvt_float2_to_e8m0x2(x, saturate, rounding):
+    """(float32, float32) -> uint16 holding two E8M0 codes, ``x[0]`` in the low
+    byte (cuda_fp8.py:3521-3554)."""
+    return _pack2(cvt_float_to_e8m0(_pair(x, np.float32), saturate, rounding))
+
+
+def cvt_double2_to_e8m0x2(x, saturate, rounding):
+    """(float64, float64) -> uint16 holding two E8M0 codes (cuda_fp8.py:3593-3626)."""
+    return _pack2(cvt_double_to_e8m0(_pair(x, np.float64), saturate, rounding))
+
+
 def cvt_e8m0_to_bf16raw(codes):
     """E8M0 code -> bfloat16 (``2**(code-127)``; code 0 is the bf16 denormal 2**-127)."""
     return _scalar_or_bulk(codes, _lib.FMT_E8M0, _lib.FMT_BF16)
@@ -210,5 +257,7 @@ __all__ = [
     "float32_to_bfloat16", "float32_to_bfloat16_rn", "bfloat16_to_float32",
     "cudaRoundMode", "float32_to_bfloat16_rz", "float32_to_bfloat16_rd", "float32_to_bfloat16_ru",
     "float64_to_bfloat16", "cvt_float_to_e8m0", "cvt_bfloat16raw_to_e8m0", "cvt_e8m0_to_bf16raw",
+    "cvt_double_to_fp8", "cvt_double2_to_fp8x2", "cvt_bfloat16raw_to_fp8", "cvt_double_to_e8m0",
+    "cvt_float2_to_e8m0x2", "cvt_double2_to_e8m0x2",
     "fp8_e8m0_to_float32", "float32_to_float16", "float16_to_float32",
 ]

@@ -380,6 +380,83 @@ struct F16ToF32 {
     __device__ static OutS one(InS h) { return f16bits_to_f32(h); }
 };
 
+// f64 -> fp8: __nv_cvt_double_to_fp8 (cuda_fp8.hpp:119-229), which is integer code on
+// the device too (there is no cvt from f64 to fp8), so NaN signs and payload bits come
+// out as that code makes them.  All its thresholds and the rounding decision depend on
+// the low 32 bits of the double only through "is any of them set", so the same steps
+// run here on the high word with that one sticky bit folded into its last place.
+template <bool E5M2, bool SAT>
+struct F64ToFp8 {
+    using InS = double; using OutS = uint8_t;
+    __device__ static OutS one(InS x) {
+        constexpr uint32_t kMant = E5M2 ? 2u : 3u;               // stored mantissa bits
+        constexpr int kBias = E5M2 ? 15 : 7;
+        constexpr uint32_t kHalfMinDenorm = E5M2 ? 0x3EE00000u : 0x3F500000u;  // 2^-17 / 2^-10
+        constexpr uint32_t kMinNorm = E5M2 ? 0x3F100000u : 0x3F900000u;        // 2^-14 / 2^-6
+        // magnitudes above this no longer round to the largest finite value
+        constexpr uint32_t kOverflowAbove = E5M2 ? 0x40EDFFFFu : 0x407D0000u;
+        constexpr uint32_t kHalf = 1u << (19u - kMant);          // half an fp8 ulp in the high word
+
+        const uint32_t lo = static_cast<uint32_t>(__double2loint(x));
+        const uint32_t hi = static_cast<uint32_t>(__double2hiint(x));
+        const uint32_t bits = hi | (lo != 0u ? 1u : 0u);
+        const uint32_t mag = bits & 0x7FFFFFFFu;
+        const uint32_t sign = (hi >> 24) & 0x80u;
+        uint32_t mant = (hi >> (20u - kMant)) & ((1u << kMant) - 1u);
+        uint32_t code;
+        if (mag <= kHalfMinDenorm) {
+            code = 0u;
+        } else if (mag > 0x7FF00000u) {                          // NaN
+            code = E5M2 ? (0x7Eu | mant) : 0x7Fu;
+        } else if (mag > kOverflowAbove) {                       // too large, infinities included
+            code = SAT ? (E5M2 ? 0x7Bu : 0x7Eu) : (E5M2 ? 0x7Cu : 0x7Fu);
+        } else {
+            const int e8 = static_cast<int>((hi >> 20) & 0x7FFu) - 1023 + kBias;
+            if (mag >= kMinNorm) {
+                code = (static_cast<uint32_t>(e8) << kMant) | mant;
+                const uint32_t dropped = bits & ((kHalf << 1) - 1u);
+                if (dropped > kHalf || (dropped == kHalf && (mant & 1u))) ++code;
+            } else {
+                const uint32_t shift = static_cast<uint32_t>(1 - e8);
+                mant |= 1u << kMant;
+                code = mant >> shift;
+                const uint32_t dropped = (bits | (1u << 20)) & ((kHalf << (shift + 1u)) - 1u);
+                const uint32_t mid = kHalf << shift;
+                if (dropped > mid || (dropped == mid && (code & 1u))) ++code;
+            }
+        }
+        return static_cast<OutS>(code | sign);
+    }
+};
+// bf16 -> fp8: __nv_cvt_bfloat16raw_to_fp8 (cuda_fp8.hpp:442-450) = the bits moved into
+// the top half of a float, then the float conversion.
+template <bool E5M2, bool SAT>
+struct Bf16ToFp8 {
+    using InS = uint16_t; using OutS = uint8_t;
+    __device__ static OutS one(InS h) {
+        return F32ToFp8<E5M2, SAT>::one(__uint_as_float(static_cast<uint32_t>(h) << 16));
+    }
+};
+// f64 -> e8m0: __nv_cvt_double_to_e8m0 (cuda_fp8.hpp:772-806).  The double is rounded
+// to float "to odd" (a sticky bit for everything discarded lands in the last place),
+// so that the directed rounding of the float conversion sees all of the double.
+template <bool UP, bool SAT>
+struct F64ToE8m0 {
+    using InS = double; using OutS = uint8_t;
+    __device__ static OutS one(InS x) {
+        float f;
+        double d;
+        asm("cvt.rn.f32.f64 %0, %1;" : "=f"(f) : "d"(x));
+        asm("cvt.f64.f32 %0, %1;" : "=d"(d) : "f"(f));
+        uint32_t u = __float_as_uint(f);
+        const bool not_nan = (u << 1) <= 0xFF000000u;
+        if (x > 0.0 && d > x) --u;
+        if (x < 0.0 && d < x) --u;
+        if (d != x && not_nan) u |= 1u;
+        return F32ToE8m0<UP, SAT>::one(__uint_as_float(u));
+    }
+};
+
 template <int BYTES> struct VecOf;
 template <> struct VecOf<4> { using type = uint32_t; };
 template <> struct VecOf<8> { using type = uint2; };
@@ -477,7 +554,8 @@ extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const v
     cudaStream_t s = b2k::as_stream(stream);
     const bool sat = saturate != 0;
     // the nearest-even pairs of b2k_cast
-    if (rounding == B2K_ROUND_NEAREST && src <= B2K_FMT_E5M2 && dst <= B2K_FMT_E5M2)
+    if (rounding == B2K_ROUND_NEAREST && src <= B2K_FMT_E5M2 && dst <= B2K_FMT_E5M2 &&
+        !(src == B2K_FMT_BF16 && dst >= B2K_FMT_E4M3))
         return b2k_cast(src, dst, saturate, in_dev, out_dev, n, stream);
     if (src == B2K_FMT_F32 && dst == B2K_FMT_BF16) {
         if (rounding == B2K_ROUND_ZERO) return launch_generic<F32ToBf16Mode<1>>(in_dev, out_dev, n, s);
@@ -499,6 +577,27 @@ extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const v
                            : launch_generic<Bf16ToE8m0<true, false>>(in_dev, out_dev, n, s);
         return sat ? launch_generic<Bf16ToE8m0<false, true>>(in_dev, out_dev, n, s)
                    : launch_generic<Bf16ToE8m0<false, false>>(in_dev, out_dev, n, s);
+    }
+    if (src == B2K_FMT_F64 && dst == B2K_FMT_E8M0 && e8_mode) {
+        if (up) return sat ? launch_generic<F64ToE8m0<true, true>>(in_dev, out_dev, n, s)
+                           : launch_generic<F64ToE8m0<true, false>>(in_dev, out_dev, n, s);
+        return sat ? launch_generic<F64ToE8m0<false, true>>(in_dev, out_dev, n, s)
+                   : launch_generic<F64ToE8m0<false, false>>(in_dev, out_dev, n, s);
+    }
+    if (rounding == B2K_ROUND_NEAREST && (dst == B2K_FMT_E4M3 || dst == B2K_FMT_E5M2)) {
+        const bool e5 = dst == B2K_FMT_E5M2;
+        if (src == B2K_FMT_F64) {
+            if (e5) return sat ? launch_generic<F64ToFp8<true, true>>(in_dev, out_dev, n, s)
+                               : launch_generic<F64ToFp8<true, false>>(in_dev, out_dev, n, s);
+            return sat ? launch_generic<F64ToFp8<false, true>>(in_dev, out_dev, n, s)
+                       : launch_generic<F64ToFp8<false, false>>(in_dev, out_dev, n, s);
+        }
+        if (src == B2K_FMT_BF16) {
+            if (e5) return sat ? launch_generic<Bf16ToFp8<true, true>>(in_dev, out_dev, n, s)
+                               : launch_generic<Bf16ToFp8<true, false>>(in_dev, out_dev, n, s);
+            return sat ? launch_generic<Bf16ToFp8<false, true>>(in_dev, out_dev, n, s)
+                       : launch_generic<Bf16ToFp8<false, false>>(in_dev, out_dev, n, s);
+        }
     }
     if (rounding == B2K_ROUND_NEAREST) {
         if (src == B2K_FMT_E8M0 && dst == B2K_FMT_BF16) return launch_generic<E8m0ToBf16>(in_dev, out_dev, n, s);

@@ -34,18 +34,27 @@ RN, RZ, RU, RD = 0, 1, 2, 3   # cudaRoundMode order: nearest, zero, +inf, -inf
 OPS = {"add": 0, "mul": 1, "max": 2, "min": 3}
 
 
-def build(force: bool = False) -> None:
-    """Compile the C restatement and, where the reference tree exists, the
-    reference-header checker.  Building the checker is not using it."""
+def _older(target: str, *sources: str) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def build(force: bool = False, reference_root: str | None = None) -> None:
+    """Compile the C restatement and, when the location of a reference source
+    tree is given (argument or ``B2K_REFERENCE_ROOT``), the reference-header
+    checker.  Without a location a prebuilt ``_ref/`` is kept as it is.
+    Building the checker is not using it."""
     target = os.path.join(_HERE, "libb2k_oracle.so")
     src = os.path.join(_HERE, "b2k_oracle.c")
-    stale = (not os.path.exists(target)) or os.path.getmtime(target) < os.path.getmtime(src)
-    if force or stale:
-        subprocess.run(["make", "-C", _HERE, "libb2k_oracle.so", "CC=gcc"], check=True,
+    if force or _older(target, src, os.path.join(_HERE, "Makefile")):
+        subprocess.run(["make", "-B", "-C", _HERE, "libb2k_oracle.so", "CC=gcc"], check=True,
                        capture_output=True)
-    ref_root = os.environ.get("B2K_REFERENCE_ROOT", "/root/reference")
+    ref_root = reference_root or os.environ.get("B2K_REFERENCE_ROOT")
     ref_so = os.path.join(_HERE, "_ref", "libb2k_ref_headers.so")
-    if os.path.isdir(ref_root) and (force or not os.path.exists(ref_so)):
+    if ref_root and os.path.isdir(ref_root) and (
+            force or _older(ref_so, os.path.join(_HERE, "ref_headers_shim.cpp"))):
         subprocess.run(["make", "-C", _HERE, "ref", "CXX=g++", f"REFERENCE_ROOT={ref_root}"],
                        check=True, capture_output=True)
 
@@ -85,6 +94,10 @@ def lib() -> ctypes.CDLL:
     L.oracle_f32_to_e8m0.restype = ctypes.c_uint8
     L.oracle_e8m0_to_bf16.argtypes = [ctypes.c_uint8]
     L.oracle_e8m0_to_bf16.restype = ctypes.c_uint16
+    L.oracle_bf16_to_fp8.argtypes = [ctypes.c_uint16, i32, i32]
+    L.oracle_bf16_to_fp8.restype = ctypes.c_uint8
+    L.oracle_f64_to_e8m0.argtypes = [ctypes.c_double, i32, i32]
+    L.oracle_f64_to_e8m0.restype = ctypes.c_uint8
     L.oracle_cast_ex.argtypes = [i32, i32, i32, i32, vp, vp, i64]
     L.oracle_cast_ex.restype = i32
     L.oracle_fold_f64.argtypes = [vp, i64, ctypes.c_double, i32]
@@ -128,6 +141,20 @@ def ref_headers() -> ctypes.CDLL:
     L.ref_cvt_bfloat16raw_to_e8m0.restype = ctypes.c_uint8
     L.ref_cvt_e8m0_to_bf16raw.argtypes = [ctypes.c_uint8]
     L.ref_cvt_e8m0_to_bf16raw.restype = ctypes.c_uint16
+    L.ref_cvt_bfloat16raw_to_fp8.argtypes = [ctypes.c_uint16, i32, i32]
+    L.ref_cvt_bfloat16raw_to_fp8.restype = ctypes.c_uint8
+    L.ref_cvt_double_to_e8m0.argtypes = [ctypes.c_double, i32, i32]
+    L.ref_cvt_double_to_e8m0.restype = ctypes.c_uint8
+    for name, scalar in (("ref_cvt_double2_to_fp8x2", ctypes.c_double), ("ref_cvt_float2_to_fp8x2", ctypes.c_float),
+                         ("ref_cvt_bfloat16raw2_to_fp8x2", ctypes.c_uint16),
+                         ("ref_cvt_float2_to_e8m0x2", ctypes.c_float), ("ref_cvt_double2_to_e8m0x2", ctypes.c_double),
+                         ("ref_cvt_bfloat162raw_to_e8m0x2", ctypes.c_uint16)):
+        fn = getattr(L, name)
+        fn.argtypes = [scalar, scalar, i32, i32]
+        fn.restype = ctypes.c_uint16
+    L.ref_bulk_f64_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
+    L.ref_bulk_bf16_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
+    L.ref_bulk_f64_to_e8m0.argtypes = [vp, vp, i64, i32, i32, i32]
     L.ref_bulk_f32_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
     L.ref_bulk_fp8_to_f32.argtypes = [vp, vp, i64, i32, i32]
     L.ref_bulk_f32_to_bf16.argtypes = [vp, vp, i64, i32]
@@ -151,12 +178,31 @@ _KIND = {("uniform", np.dtype(np.float32)): 0, ("uniform", np.dtype(np.float64))
          ("normal", np.dtype(np.float32)): 2, ("normal", np.dtype(np.float64)): 3}
 
 
-def fill(states: np.ndarray, dist: str, dtype, count: int) -> np.ndarray:
-    """out[t, i] = i-th draw of generator t; advances ``states`` in place."""
+def fill(states: np.ndarray, dist: str, dtype, count: int, threads: int = 1) -> np.ndarray:
+    """out[t, i] = i-th draw of generator t; advances ``states`` in place.
+    Generators are independent, so ``threads`` > 1 (0 = all cores) splits them
+    into contiguous slices that run side by side (the C call releases the GIL)."""
     dtype = np.dtype(dtype)
-    out = np.empty((states.shape[0], count), dtype=dtype)
+    n = states.shape[0]
+    out = np.zeros((n, count), dtype=dtype)   # zeros: pages are touched before the timed loops
     assert states.flags.c_contiguous and states.dtype.itemsize == 16
-    lib().oracle_xoro_fill(_ptr(states), states.shape[0], _KIND[(dist, dtype)], _ptr(out), count)
+    kind = _KIND[(dist, dtype)]
+    if threads == 0:
+        threads = os.cpu_count() or 1
+    threads = max(1, min(threads, n // 4096 or 1))
+    if threads == 1:
+        lib().oracle_xoro_fill(_ptr(states), n, kind, _ptr(out), count)
+        return out
+    import concurrent.futures
+    L = lib()
+    bounds = np.linspace(0, n, threads + 1).astype(np.int64)
+
+    def piece(k):
+        lo, hi = int(bounds[k]), int(bounds[k + 1])
+        L.oracle_xoro_fill(_ptr(states) + 16 * lo, hi - lo, kind, _ptr(out) + lo * count * dtype.itemsize, count)
+
+    with concurrent.futures.ThreadPoolExecutor(threads) as pool:
+        list(pool.map(piece, range(threads)))
     return out
 
 
@@ -203,7 +249,7 @@ def cast_ex(x: np.ndarray, src: int, dst: int, sat: int = 1, mode: int = RN) -> 
     return out
 
 
-def ref_cast(x: np.ndarray, src: int, dst: int, sat: int = 1, threads: int = 0) -> np.ndarray:
+def ref_cast(x: np.ndarray, src: int, dst: int, sat: int = 1, threads: int = 0, mode: int = RZ) -> np.ndarray:
     """Bulk cast with the reference's own vendored-header host code."""
     R = ref_headers()
     x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
@@ -216,6 +262,12 @@ def ref_cast(x: np.ndarray, src: int, dst: int, sat: int = 1, threads: int = 0) 
         R.ref_bulk_f32_to_fp8(_ptr(x), _ptr(out), x.size, sat, dst - 2, threads)
     elif src in (E4M3, E5M2) and dst == F32:
         R.ref_bulk_fp8_to_f32(_ptr(x), _ptr(out), x.size, src - 2, threads)
+    elif src == F64 and dst in (E4M3, E5M2):
+        R.ref_bulk_f64_to_fp8(_ptr(x), _ptr(out), x.size, sat, dst - 2, threads)
+    elif src == BF16 and dst in (E4M3, E5M2):
+        R.ref_bulk_bf16_to_fp8(_ptr(x), _ptr(out), x.size, sat, dst - 2, threads)
+    elif src == F64 and dst == E8M0:
+        R.ref_bulk_f64_to_e8m0(_ptr(x), _ptr(out), x.size, sat, mode, threads)
     else:
         raise ValueError(f"unsupported cast {src}->{dst}")
     return out

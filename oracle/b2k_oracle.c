@@ -377,9 +377,37 @@ ORACLE_API uint16_t oracle_e8m0_to_bf16(uint8_t e) {
     return (uint16_t)((uint16_t)e << 7);
 }
 
-/* Bulk form of the above.  Formats: 0 f32, 1 bf16, 4 f64, 6 e8m0. */
+/* cuda_fp8.hpp:442-470: bf16 bits -> fp8 goes through float (a 16-bit left shift,
+ * exact) and then the float encoder. */
+ORACLE_API uint8_t oracle_bf16_to_fp8(uint16_t h, int sat, int interp) {
+    return oracle_f32_to_fp8(oracle_bf16_to_f32(h), sat, interp);
+}
+
+/* cuda_fp8.hpp:772-806: f64 -> E8M0.  The double is rounded to float "to odd"
+ * (the sticky bit of everything discarded is kept in the last place), then the
+ * float encoder runs; its directed rounding therefore sees every discarded bit. */
+ORACLE_API uint8_t oracle_f64_to_e8m0(double x, int sat, int mode) {
+    float f = (float)x;
+    double back = (double)f;
+    uint32_t u;
+    memcpy(&u, &f, sizeof u);
+    int not_nan = ((u << 1) <= 0xFF000000u);
+    if (x > 0.0 && back > x) u--;
+    if (x < 0.0 && back < x) u--;
+    if (back != x && not_nan) u |= 1u;
+    memcpy(&f, &u, sizeof f);
+    return oracle_f32_to_e8m0(f, sat, mode);
+}
+
+/* Bulk form of the above.  Formats: 0 f32, 1 bf16, 2 e4m3, 3 e5m2, 4 f64, 6 e8m0. */
 ORACLE_API int oracle_cast_ex(int src, int dst, int sat, int mode, const void *in, void *out, int64_t n) {
-    if (src == 0 && dst == 1) {
+    if (src == 4 && (dst == 2 || dst == 3)) {
+        for (int64_t i = 0; i < n; ++i) ((uint8_t *)out)[i] = oracle_f64_to_fp8(((const double *)in)[i], sat, dst - 2);
+    } else if (src == 1 && (dst == 2 || dst == 3)) {
+        for (int64_t i = 0; i < n; ++i) ((uint8_t *)out)[i] = oracle_bf16_to_fp8(((const uint16_t *)in)[i], sat, dst - 2);
+    } else if (src == 4 && dst == 6) {
+        for (int64_t i = 0; i < n; ++i) ((uint8_t *)out)[i] = oracle_f64_to_e8m0(((const double *)in)[i], sat, mode);
+    } else if (src == 0 && dst == 1) {
         for (int64_t i = 0; i < n; ++i) ((uint16_t *)out)[i] = oracle_f32_to_bf16_mode(((const float *)in)[i], mode);
     } else if (src == 4 && dst == 1) {
         for (int64_t i = 0; i < n; ++i) ((uint16_t *)out)[i] = oracle_f64_to_bf16(((const double *)in)[i]);

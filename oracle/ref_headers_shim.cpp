@@ -70,6 +70,48 @@ uint8_t ref_cvt_bfloat16raw_to_e8m0(uint16_t bits, int sat, int mode) {
                                                  mode == 2 ? cudaRoundPosInf : cudaRoundZero);
 }
 uint16_t ref_cvt_e8m0_to_bf16raw(uint8_t e) { return __nv_cvt_e8m0_to_bf16raw((__nv_fp8_storage_t)e).x; }
+// __nv_cvt_bfloat16raw_to_fp8 (cuda_fp8.hpp:442-450)
+uint8_t ref_cvt_bfloat16raw_to_fp8(uint16_t bits, int sat, int interp) {
+    __nv_bfloat16_raw r; r.x = bits;
+    return (uint8_t)__nv_cvt_bfloat16raw_to_fp8(r, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                                interp ? __NV_E5M2 : __NV_E4M3);
+}
+// __nv_cvt_double_to_e8m0 (cuda_fp8.hpp:797-806)
+uint8_t ref_cvt_double_to_e8m0(double x, int sat, int mode) {
+    return (uint8_t)__nv_cvt_double_to_e8m0(x, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                            mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
+// the two-element forms: x in the low byte, y in the high byte
+uint16_t ref_cvt_double2_to_fp8x2(double x, double y, int sat, int interp) {
+    double2 v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_double2_to_fp8x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                               interp ? __NV_E5M2 : __NV_E4M3);
+}
+uint16_t ref_cvt_float2_to_fp8x2(float x, float y, int sat, int interp) {
+    float2 v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_float2_to_fp8x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                              interp ? __NV_E5M2 : __NV_E4M3);
+}
+uint16_t ref_cvt_bfloat16raw2_to_fp8x2(uint16_t x, uint16_t y, int sat, int interp) {
+    __nv_bfloat162_raw v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_bfloat16raw2_to_fp8x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                                    interp ? __NV_E5M2 : __NV_E4M3);
+}
+uint16_t ref_cvt_float2_to_e8m0x2(float x, float y, int sat, int mode) {
+    float2 v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_float2_to_e8m0x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                               mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
+uint16_t ref_cvt_double2_to_e8m0x2(double x, double y, int sat, int mode) {
+    double2 v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_double2_to_e8m0x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                                mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
+uint16_t ref_cvt_bfloat162raw_to_e8m0x2(uint16_t x, uint16_t y, int sat, int mode) {
+    __nv_bfloat162_raw v; v.x = x; v.y = y;
+    return (uint16_t)__nv_cvt_bfloat162raw_to_e8m0x2(v, sat ? __NV_SATFINITE : __NV_NOSAT,
+                                                     mode == 2 ? cudaRoundPosInf : cudaRoundZero);
+}
 
 }  // extern "C"
 
@@ -103,6 +145,19 @@ void ref_bulk_f32_to_bf16(const float* in, uint16_t* out, int64_t n, int threads
 void ref_bulk_bf16_to_f32(const uint16_t* in, float* out, int64_t n, int threads) {
     parallel_for(n, threads, [=](int64_t lo, int64_t hi) {
         for (int64_t i = lo; i < hi; ++i) out[i] = ref_bfloat162float(in[i]); });
+}
+
+void ref_bulk_f64_to_fp8(const double* in, uint8_t* out, int64_t n, int sat, int interp, int threads) {
+    parallel_for(n, threads, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) out[i] = ref_cvt_double_to_fp8(in[i], sat, interp); });
+}
+void ref_bulk_bf16_to_fp8(const uint16_t* in, uint8_t* out, int64_t n, int sat, int interp, int threads) {
+    parallel_for(n, threads, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) out[i] = ref_cvt_bfloat16raw_to_fp8(in[i], sat, interp); });
+}
+void ref_bulk_f64_to_e8m0(const double* in, uint8_t* out, int64_t n, int sat, int mode, int threads) {
+    parallel_for(n, threads, [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) out[i] = ref_cvt_double_to_e8m0(in[i], sat, mode); });
 }
 
 }  // extern "C"

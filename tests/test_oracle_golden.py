@@ -183,3 +183,29 @@ def test_directed_rounding_f64_and_e8m0_match_reference_headers(cast_gold):
     assert L.oracle_f32_to_e8m0(over, 0, oracle.RU) == 0xFF and L.oracle_f32_to_e8m0(over, 1, oracle.RU) == 0xFE
     half = L.oracle_e8m0_to_bf16(126)
     assert L.oracle_bf16_to_e8m0(half, 0, oracle.RZ) == 126 and L.oracle_bf16_to_e8m0(half, 0, oracle.RU) == 126
+
+
+@pytest.mark.skipif(not oracle.have_ref_headers(), reason="reference-header checker not built")
+def test_double_and_bf16raw_sources_match_reference_headers():
+    """cvt_double_to_fp8, cvt_bfloat16raw_to_fp8, cvt_double_to_e8m0: restatement vs the
+    vendored headers, plus the known answers of tests/cudapy/test_fp8_bindings.py:421-447,
+    :463-496, :521-539."""
+    rng = np.random.default_rng(12)
+    x = np.concatenate([rng.standard_normal(1 << 17) * np.exp2(rng.uniform(-30, 30, 1 << 17)),
+                        rng.integers(0, 2 ** 64, size=1 << 17, dtype=np.uint64).view(np.float64)])
+    h = np.arange(1 << 16, dtype=np.uint16)
+    for dst in (oracle.E4M3, oracle.E5M2):
+        for sat in (0, 1):
+            assert oracle.cast_ex(x, oracle.F64, dst, sat).tobytes() == oracle.ref_cast(x, oracle.F64, dst, sat).tobytes()
+            assert oracle.cast_ex(h, oracle.BF16, dst, sat).tobytes() == oracle.ref_cast(h, oracle.BF16, dst, sat).tobytes()
+    wide = np.concatenate([x, rng.standard_normal(1 << 16) * np.exp2(rng.uniform(-140, 140, 1 << 16))])
+    for sat in (0, 1):
+        for mode in (oracle.RZ, oracle.RU):
+            assert oracle.cast_ex(wide, oracle.F64, oracle.E8M0, sat, mode).tobytes() == \
+                oracle.ref_cast(wide, oracle.F64, oracle.E8M0, sat, mode=mode).tobytes()
+    L = oracle.lib()
+    assert [L.oracle_f64_to_fp8(1e300, s, i) for s, i in ((0, 1), (1, 1), (0, 0), (1, 0))] == [0x7C, 0x7B, 0x7F, 0x7E]
+    raw = L.oracle_e8m0_to_bf16(254)
+    assert [L.oracle_bf16_to_fp8(raw, s, i) for s, i in ((0, 1), (1, 1), (0, 0), (1, 0))] == [0x7C, 0x7B, 0x7F, 0x7E]
+    over = float(np.nextafter(np.float64(2.0 ** 127), np.float64(np.inf)))
+    assert L.oracle_f64_to_e8m0(over, 0, oracle.RU) == 0xFF and L.oracle_f64_to_e8m0(over, 1, oracle.RU) == 0xFE
