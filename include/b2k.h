@@ -14,8 +14,9 @@
  *   - every call returns an int status: 0 = ok, negative = argument error found
  *     on the host before any launch (B2K_ERR_*), positive = a cudaError_t;
  *   - calls are asynchronous on `stream` and never synchronise;
- *   - the library allocates no device memory; scratch is passed in by the caller
- *     (sizes from the *_scratch_bytes functions);
+ *   - scratch is passed in by the caller (sizes from the *_scratch_bytes
+ *     functions); the library allocates device memory in one place only:
+ *     b2k_peer_mailbox_create (512 bytes per communicator, synchronous);
  *   - b2k_last_error() gives a thread-local message for the last failure.
  */
 #ifndef B2K_H_
@@ -90,6 +91,22 @@ B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* The same with flags.  The kernel is launched with the programmatic-dependent-launch
+ * attribute; back-to-back reductions on one stream therefore overlap their launch
+ * latencies, and results, scratch and mailboxes are still touched strictly in stream
+ * order.
+ *   B2K_REDUCE_INPUT_READY : the caller promises that x_dev[0..n) was complete before
+ *       the kernel that precedes this call on the stream began (it is not produced or
+ *       modified by that kernel -- in particular it does not contain the previous
+ *       reduction's out_dev).  The reduction may then read its input while the tail
+ *       of the preceding kernel (a reduction's last block, its cross-GPU exchange) is
+ *       still running: a stream of independent reductions runs as a pipeline.
+ *       Without the flag the kernel touches nothing before its predecessor is done. */
+#define B2K_REDUCE_INPUT_READY 1u
+B2K_API int b2k_reduce_ex(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
+                          void *out_dev, void *scratch_dev, int64_t scratch_bytes, unsigned flags,
+                          void *stream);
+
 /* Reduction of a rows x cols matrix along one axis with a table op:
  *   axis 0: out_dev[j] = op(fold_i x[i, j], *init_host)   (cols outputs)
  *   axis 1: out_dev[i] = op(fold_j x[i, j], *init_host)   (rows outputs)
@@ -107,16 +124,32 @@ B2K_API int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, 
                             int64_t pitch_bytes, int axis, const void *init_host, void *out_dev,
                             void *scratch_dev, int64_t scratch_bytes, void *stream);
 
+/* A batch of `batch` matrices (matrix_stride_bytes apart) reduced along axis 0 in ONE
+ * launch: out_dev[b * cols + j] = op(fold_i x[b, i, j], *init_host).  This is the
+ * reduction of the middle axis of a C-contiguous (batch, rows, cols) array, the step
+ * after the 1-D reduce of numba/cuda/kernels/reduction.py:217-218 like b2k_reduce_axis.
+ * batch <= 65535.  Scratch rules as for b2k_reduce_axis, size from
+ * b2k_reduce_cols_batched_scratch_bytes. */
+B2K_API int64_t b2k_reduce_cols_batched_scratch_bytes(int64_t batch, int64_t rows, int64_t cols, int dtype);
+B2K_API int b2k_reduce_cols_batched(int op, int dtype, const void *x_dev, int64_t batch, int64_t rows,
+                                    int64_t cols, int64_t pitch_bytes, int64_t matrix_stride_bytes,
+                                    const void *init_host, void *out_dev, void *scratch_dev,
+                                    int64_t scratch_bytes, void *stream);
+
 /* cuda.reduce with an arbitrary user function.  `expr` is a C++ expression over
  * the operands `a` and `b` (the Python layer obtains it by tracing the user's
  * function); the reduce kernel is compiled around it at run time with NVRTC for
  * sm_100a and cached per (device, dtype, expression).  Replaces the reference's
  * JIT compilation of the functor (numba/cuda/kernels/reduction.py:15-21, :185-192).
- * Integer operands are widened to 64 bits inside the expression and truncated on
- * store, float32 literals-with-integers promote to double, as numba types them.
+ * Integer operands are widened to 64 bits inside the expression (`a` and `b` are
+ * unsigned long long for unsigned items, long long for signed ones; B2K_ILIT gives a
+ * long long, so the caller casts where numba's rule "signed if either side is" asks
+ * for it) and truncated on store; float32 literals-with-integers promote to double.
  * Helpers available to the expression: b2k_floordiv, b2k_mod (Python semantics),
  * b2k_truediv, b2k_abs, B2K_ILIT(integer literal), B2K_INF, B2K_NAN.
- * n must be >= 1 (the caller returns init for an empty array).  The op must be
+ * n must be >= 1 (the caller returns init for an empty array).  init_host may be
+ * NULL: the bare fold of the items is written (such a function has no identity
+ * element, so partial results of shards are combined without one).  The op must be
  * associative and commutative, as the reference requires. */
 B2K_API int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int64_t n,
                             const void *init_host, void *out_dev, void *scratch_dev,
@@ -126,15 +159,23 @@ B2K_API int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int6
  * reference, which has no distributed layer).  For an array sharded over up to
  * b2k_peer_max_world() GPUs of one NVLink domain: every rank calls
  * b2k_reduce_peer on its shard with the same `epoch` (1, 2, 3, ... per call of a
- * communicator); the block that finishes the local fold stores the rank's value
- * into a mailbox in every peer's memory, waits (at most timeout_ns, 0 = 2 s)
- * for the peers' values of this epoch in its own mailbox, folds them in rank
- * order, folds *init_host in and writes out_dev[0] -- the same result on every
- * rank.  If a peer's value does not arrive in time, *status_dev is set to 1 and
- * the kernel returns (no hang).
+ * communicator; its low 32 bits must not be zero); the block that finishes the
+ * local fold stores the rank's value into a mailbox in every peer's memory, waits
+ * (at most timeout_ns, 0 = 2 s) for the peers' values of this epoch in its own
+ * mailbox, folds them in rank order, folds *init_host in and writes out_dev[0] --
+ * the same result on every rank.
  *   mailboxes : host array of `world` device pointers, entry r = rank r's mailbox
  *               as visible from this process (own: from b2k_peer_mailbox_create;
  *               others: b2k_peer_mailbox_open of the handle that rank exported).
+ *   status_dev: three 64-bit words in device memory, 8-byte aligned.  [0] is set to
+ *               1 when a peer's value did not arrive in time (the kernel then writes
+ *               the fold of nothing but *init_host and returns: no hang; the other
+ *               ranks may have completed normally, so after a timeout the ranks hold
+ *               DIFFERENT results and have to agree on the host what to do).  [1] and
+ *               [2] receive the GPU's nanosecond timer when the local fold was done
+ *               and when the last peer value had been seen: their difference is what
+ *               the exchange cost this rank, launch skew between the ranks included.
+ *   flags     : as for b2k_reduce_ex.
  * The mailbox helpers allocate/map b2k_peer_mailbox_bytes() bytes once per
  * communicator; handles are b2k_peer_handle_bytes() bytes and travel between
  * processes by any host channel. */
@@ -149,7 +190,7 @@ B2K_API int b2k_peer_mailbox_close(void *peer_mailbox_dev);
 B2K_API int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                             void *out_dev, void *scratch_dev, int64_t scratch_bytes,
                             void *const *mailboxes, int world, int rank, uint64_t epoch,
-                            uint64_t timeout_ns, int *status_dev, void *stream);
+                            uint64_t timeout_ns, void *status_dev, unsigned flags, void *stream);
 
 /* The same reduction for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Meant for hosts whose device memory belongs to
@@ -182,6 +223,12 @@ B2K_API int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, int
                     int64_t in_stride0, int64_t in_stride1,
                     int64_t out_stride0, int64_t out_stride1,
                     int64_t itemsize, void *stream);
+
+/* Diagnostic: how many bounded waits of the TMA transpose kernels have run out on the
+ * current device since the library was loaded (0 in a healthy run; a kernel whose
+ * wait runs out counts it, drains its copies and returns instead of hanging).
+ * Synchronises the device. */
+B2K_API int b2k_transpose_wait_timeouts(unsigned int *count_out);
 
 /* ---- strided assignment --------------------------------------------------
  * Replaces the per-ndim JIT-compiled element kernel behind

@@ -19,6 +19,8 @@ FMT_F32, FMT_BF16, FMT_E4M3, FMT_E5M2, FMT_F64, FMT_F16, FMT_E8M0 = range(7)
 ROUND_NEAREST, ROUND_ZERO, ROUND_POS_INF, ROUND_MIN_INF = range(4)
 UNIFORM_F32, UNIFORM_F64, NORMAL_F32, NORMAL_F64 = range(4)
 
+REDUCE_INPUT_READY = 1
+
 ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_ALIGNMENT, ERR_SCRATCH, ERR_TOO_LARGE = -1, -2, -3, -4, -5
 
 #: every symbol include/b2k.h declares, with (restype, argtypes)
@@ -29,6 +31,7 @@ SIGNATURES = {
     "b2k_launch_count": (_i64, []),
     "b2k_reduce_scratch_bytes": (_i64, []),
     "b2k_reduce": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
+    "b2k_reduce_ex": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, ctypes.c_uint, _vp]),
     "b2k_reduce_expr": (_i32, [ctypes.c_char_p, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp]),
     "b2k_reduce_noalloc_max_elements": (_i64, []),
     "b2k_reduce_noalloc": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp]),
@@ -41,10 +44,13 @@ SIGNATURES = {
     "b2k_peer_mailbox_open": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "b2k_peer_mailbox_close": (_i32, [_vp]),
     "b2k_reduce_peer": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, ctypes.POINTER(_vp), _i32, _i32,
-                               _u64, _u64, _vp, _vp]),
+                               _u64, _u64, _vp, ctypes.c_uint, _vp]),
     "b2k_transpose2d": (_i32, [_vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp]),
+    "b2k_transpose_wait_timeouts": (_i32, [ctypes.POINTER(ctypes.c_uint)]),
     "b2k_reduce_axis_scratch_bytes": (_i64, [_i64, _i64, _i32, _i32]),
     "b2k_reduce_axis": (_i32, [_i32, _i32, _vp, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "b2k_reduce_cols_batched_scratch_bytes": (_i64, [_i64, _i64, _i64, _i32]),
+    "b2k_reduce_cols_batched": (_i32, [_i32, _i32, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "b2k_assign": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _i64, _vp]),
     "b2k_fill": (_i32, [_vp, _i32, _vp, _vp, _vp, _i64, _vp]),
     "b2k_xoroshiro128p_tables_bytes": (_i64, []),
@@ -54,12 +60,6 @@ SIGNATURES = {
     "b2k_cast": (_i32, [_i32, _i32, _i32, _vp, _vp, _i64, _vp]),
     "b2k_cast_ex": (_i32, [_i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp]),
 }
-#: diagnostics that are exported but not part of the public header
-_EXTRA = {
-    "b2k_transpose_wait_timeouts": (_i32, [ctypes.POINTER(ctypes.c_uint)]),
-}
-
-
 class B2KError(RuntimeError):
     """A libb2k call failed; ``status`` is the ABI status (negative = argument
     error found on the host, positive = a cudaError_t)."""
@@ -76,7 +76,7 @@ def lib() -> ctypes.CDLL:
             f"{LIB_PATH} is missing: numba_cuda_b200 has no CPU fallback. "
             "Build it with `python -m numba_cuda_b200._build` (needs nvcc).")
     L = ctypes.CDLL(LIB_PATH)
-    for name, (res, args) in {**SIGNATURES, **_EXTRA}.items():
+    for name, (res, args) in SIGNATURES.items():
         fn = getattr(L, name)
         fn.restype = res
         fn.argtypes = args

@@ -5,9 +5,6 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
-#include <mutex>
-#include <string>
-#include <unordered_map>
 
 #include "b2k_internal.cuh"
 
@@ -33,34 +30,26 @@ int check_cuda(cudaError_t e, const char *what) {
 
 void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-int sm_count() {
-    static std::mutex mu;
-    static int cached[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    std::lock_guard<std::mutex> lock(mu);
-    if (cached[dev] == 0) {
-        int n = 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-        cached[dev] = n;
-    }
-    return cached[dev];
+int current_device() {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
 }
 
-int env_int(const char *name, int fallback) {
-    // The environment is read once per name; callers may pass different
-    // fallbacks for the same name, so only the parsed variable is cached.
-    static std::mutex mu;
-    static std::unordered_map<std::string, std::pair<bool, int>> seen;
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = seen.find(name);
-    if (it == seen.end()) {
-        const char *v = getenv(name);
-        const bool set = v && *v;
-        it = seen.emplace(name, std::make_pair(set, set ? atoi(v) : 0)).first;
+int sm_count() {
+    static std::atomic<int> cached[kMaxDevices];
+    const int dev = current_device();
+    if (dev < 0 || dev >= kMaxDevices) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return it->second.first ? it->second.second : fallback;
+    return n;
+}
+
+int env_read(const char *name) {
+    const char *v = getenv(name);
+    return (v && *v) ? atoi(v) : INT_MIN;
 }
 
 }  // namespace b2k

@@ -817,7 +817,7 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
     // Both sides dense along the fastest axis, but their alignments kept the unit
     // below 16 bytes: long runs go through aligned 16-byte chunks all the same.
     if (src && unit < 16 && ax.src_step[n - 1] == unit && ax.dst_step[n - 1] == unit &&
-        ax.len[n - 1] * unit >= 128 && b2k::env_int("B2K_ASSIGN_RUNS", 1) != 0) {
+        ax.len[n - 1] * unit >= 128 && B2K_ENV_INT("B2K_ASSIGN_RUNS", 1) != 0) {
         bool repeats = false;  // (a repeated source has its own kernel below)
         for (int k = 0; k + 1 < n; ++k)
             if (ax.src_step[k] == 0 && ax.len[k] >= 2 * kRepeatRows) repeats = true;
@@ -843,7 +843,7 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
 
     // Source densest along another axis q than the destination (an axis permutation).
     int q = -1;
-    if (n >= 2 && b2k::env_int("B2K_ASSIGN_TILED", 1) != 0) {
+    if (n >= 2 && B2K_ENV_INT("B2K_ASSIGN_TILED", 1) != 0) {
         int best = -1;
         for (int k = 0; k < n; ++k) {
             if (ax.src_step[k] == 0) continue;
@@ -859,7 +859,7 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
     // three further axes: a stack of 2-D transposes for the TMA tile kernel.
     if (q >= 0 && n <= 5 && ax.dst_step[n - 1] == unit && ax.src_step[q] == unit && ax.len[q] >= 32 &&
         ax.len[n - 1] >= 32 && total * static_cast<uint64_t>(unit) >= (1u << 20) &&
-        b2k::env_int("B2K_ASSIGN_TMA", 1) != 0) {
+        B2K_ENV_INT("B2K_ASSIGN_TMA", 1) != 0) {
         int64_t blen[3], istep[3], ostep[3];
         int nb = 0;
         for (int k = n - 2; k >= 0; --k) {  // fastest batch axis first
@@ -882,7 +882,7 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
     case 2: return launch_unit<uint16_t>(dst, src, ax, total, narrow, q, st);
     default:
         if (q >= 0 && ax.src_step[q] == 1 && ax.dst_step[n - 1] == 1 && ax.len[q] >= 32 && ax.len[n - 1] >= 32 &&
-            b2k::env_int("B2K_ASSIGN_BYTE_TILES", 1) != 0)
+            B2K_ENV_INT("B2K_ASSIGN_BYTE_TILES", 1) != 0)
             return launch_byte_tiles(dst, src, ax, total, q, st);
         return launch_unit<uint8_t>(dst, src, ax, total, narrow, q, st);
     }

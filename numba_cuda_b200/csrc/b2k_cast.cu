@@ -279,7 +279,7 @@ int launch(const void *in, void *out, int64_t n, cudaStream_t stream) {
                            b2k::aligned_to<void>(out, sizeof(typename C::Out));
     const bool wide_ok = b2k::aligned_to<void>(in, sizeof(typename Eight<C>::In)) &&
                          b2k::aligned_to<void>(out, sizeof(typename Eight<C>::Out)) &&
-                         b2k::env_int("B2K_CAST_WIDE", 1) != 0;
+                         B2K_ENV_INT("B2K_CAST_WIDE", 1) != 0;
     if (wide_ok) {
         const int64_t items = n / 8;
         int64_t grid = (items + kThreads - 1) / kThreads;

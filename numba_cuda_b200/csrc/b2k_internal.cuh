@@ -4,6 +4,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <climits>
+#include <mutex>
+
 #include "../../include/b2k.h"
 
 namespace b2k {
@@ -16,8 +20,32 @@ int check_cuda(cudaError_t e, const char *what);
 void note_launch(int n = 1);
 // Streaming multiprocessors of the current device (cached per device).
 int sm_count();
-// Integer knob from the environment, read once per name (development aid).
-int env_int(const char *name, int fallback);
+// Integer knob from the environment (development aid): INT_MIN when unset.
+int env_read(const char *name);
+// Ordinal of the current device, or -1.
+int current_device();
+
+// Set-up that has to happen once on EVERY device a process uses (function
+// attributes such as the dynamic shared-memory limit belong to a device, not to
+// the process).  `run` remembers per device ordinal what `f` returned.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+    std::atomic<int> done[kMaxDevices];
+    cudaError_t status[kMaxDevices];
+    std::mutex mu;
+    template <typename F>
+    cudaError_t run(F &&f) {
+        const int dev = current_device();
+        if (dev < 0 || dev >= kMaxDevices) return f();
+        if (done[dev].load(std::memory_order_acquire)) return status[dev];
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[dev].load(std::memory_order_relaxed)) {
+            status[dev] = f();
+            done[dev].store(1, std::memory_order_release);
+        }
+        return status[dev];
+    }
+};
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -37,6 +65,14 @@ int transpose_tma_batched(const void *in, void *out, int64_t rows, int64_t cols,
                           const int64_t *out_batch_step, int64_t itemsize, cudaStream_t stream);
 
 }  // namespace b2k
+
+// A knob read from the environment ONCE per call site (a function-local static),
+// so that launch paths pay one load for it.
+#define B2K_ENV_INT(name, fallback)                                        \
+    ([&]() -> int {                                                        \
+        static const int v__ = b2k::env_read(name);                        \
+        return v__ == INT_MIN ? static_cast<int>(fallback) : v__;          \
+    }())
 
 #define B2K_RETURN_IF_LAUNCH_FAILED(what)                      \
     do {                                                       \

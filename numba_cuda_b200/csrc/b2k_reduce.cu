@@ -64,17 +64,24 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
 
 // ---- cross-GPU combine inside the kernel ------------------------------------------
 // When the array is sharded over several GPUs of one NVLink domain, the block that
-// finishes a GPU's local fold also does the exchange: it stores its value and then
-// a flag into a mailbox in every peer's memory (plain peer stores over NVLink),
-// waits until every peer's flag for this call has arrived in its own mailbox, and
-// folds the values in rank order.  No second launch and no library collective: the
-// cost is one NVLink round trip.  Flags carry the call's epoch and mailboxes are
-// double-buffered by epoch parity, so nothing is ever reset; a peer can be at most
-// one call ahead (it cannot finish call k+1 before this rank has published k+1).
-// The wait is bounded: when it runs out the block records an error status, writes
-// the identity-folded result and returns.
+// finishes a GPU's local fold also does the exchange: it stores its value into a
+// mailbox in every peer's memory (plain peer stores over NVLink), waits until every
+// peer's value for this call has arrived in its own mailbox, and folds the values in
+// rank order.  No second launch and no library collective.
+//
+// A value travels as 64-bit words that each carry 32 bits of payload under the low
+// 32 bits of the call's epoch: {epoch32, value bits 31..0} and, for 8-byte items,
+// {epoch32, value bits 63..32}.  A 64-bit store is single-copy atomic, so a word that
+// shows this call's epoch also shows its payload: no separate flag, and no release
+// fence between a value and its flag (a fence at system scope has to wait for the
+// remote write to be acknowledged -- a full NVLink round trip before the flag could
+// even leave).  The cost of the exchange is one one-way trip of one or two stores.
+// Mailboxes are double-buffered by epoch parity, so nothing is ever reset; a peer can
+// be at most one call ahead (it cannot finish call k+1 before this rank has published
+// k+1).  The wait is bounded: when it runs out the block records an error status,
+// writes the identity-folded result and returns.
 constexpr int kMaxPeers = 16;
-constexpr int kMailboxWords = 2 * kMaxPeers * 2;  // [parity][writer]{value, flag}, 64-bit words
+constexpr int kMailboxWords = 2 * kMaxPeers * 2;  // [parity][writer]{low word, high word}
 
 // Folds the eight words of a 32-byte vector into a word of running results.
 template <typename T, typename Op>
@@ -90,21 +97,15 @@ struct PeerLink {
     unsigned long long *mailbox[kMaxPeers];  // mailbox of every rank (own one included)
     int world;
     int rank;
-    unsigned long long epoch;               // same on every rank for one call; starts at 1
+    unsigned long long epoch;               // same on every rank for one call; low 32 bits never 0
     unsigned long long timeout_ns;
-    int *status;                             // set to 1 when a wait ran out
+    // [0] = 1 when a wait ran out; [1], [2] = %globaltimer (ns) when this GPU's local fold
+    // was complete and when every peer's value had been seen
+    unsigned long long *status;
 };
 
-__device__ __forceinline__ void store_release_sys(unsigned long long *p, unsigned long long v) {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
 __device__ __forceinline__ void store_relaxed_sys(unsigned long long *p, unsigned long long v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long *p) {
-    unsigned long long v;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
 }
 __device__ __forceinline__ unsigned long long load_relaxed_sys(const unsigned long long *p) {
     unsigned long long v;
@@ -118,9 +119,10 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 }
 
 // Runs in the last block of a GPU.  `local` is valid in thread 0.  Returns the fold
-// over all ranks (valid in thread 0).
+// over all ranks (valid in thread 0).  Thread p talks to rank p.
 template <typename T, typename Op, int THREADS>
 __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) {
+    constexpr int WORDS = sizeof(T) > 4 ? 2 : 1;
     __shared__ unsigned long long mine_bits;
     __shared__ unsigned long long peer_bits[kMaxPeers];
     __shared__ int all_arrived;
@@ -129,29 +131,40 @@ __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) 
         memcpy(&b, &local, sizeof(T));
         mine_bits = b;
         all_arrived = 1;
+        link.status[1] = global_timer_ns();
     }
     __syncthreads();
     const int slot_base = static_cast<int>(link.epoch & 1ull) * kMaxPeers;
+    const unsigned long long tag = (link.epoch & 0xFFFFFFFFull) << 32;
     if (threadIdx.x < link.world) {
         const int p = threadIdx.x;
-        // publish to peer p: value first, then the flag that releases it
+        // publish to rank p (this rank's own mailbox included: one code path)
         unsigned long long *theirs = link.mailbox[p] + 2 * (slot_base + link.rank);
-        store_relaxed_sys(theirs, mine_bits);
-        store_release_sys(theirs + 1, link.epoch);
-        // collect from peer p
+        store_relaxed_sys(theirs, tag | (mine_bits & 0xFFFFFFFFull));
+        if (WORDS == 2) store_relaxed_sys(theirs + 1, tag | (mine_bits >> 32));
+        // collect from rank p: spin for the first microseconds (the values of ranks
+        // that run in step arrive within one NVLink trip), then back off
         const unsigned long long *here = link.mailbox[link.rank] + 2 * (slot_base + p);
-        const unsigned long long t0 = global_timer_ns();
-        bool arrived = true;
-        while (load_acquire_sys(here + 1) != link.epoch) {
-            if (global_timer_ns() - t0 > link.timeout_ns) { arrived = false; break; }
-            __nanosleep(100);
+        unsigned long long w0 = 0, w1 = tag;
+        unsigned long long t0 = 0;
+        bool arrived = false;
+        for (unsigned int spin = 0;; ++spin) {
+            w0 = load_relaxed_sys(here);
+            if (WORDS == 2) w1 = load_relaxed_sys(here + 1);
+            if ((w0 >> 32) == (tag >> 32) && (w1 >> 32) == (tag >> 32)) { arrived = true; break; }
+            if (spin == 64) t0 = global_timer_ns();
+            if (spin > 64) {
+                if (global_timer_ns() - t0 > link.timeout_ns) break;
+                __nanosleep(spin < 4096 ? 20 : 200);
+            }
         }
-        if (arrived) peer_bits[p] = load_relaxed_sys(here);
+        if (arrived) peer_bits[p] = (w0 & 0xFFFFFFFFull) | (WORDS == 2 ? (w1 << 32) : 0ull);
         else atomicExch(&all_arrived, 0);
     }
     __syncthreads();
     T result = Op::template identity<T>();
     if (threadIdx.x == 0) {
+        link.status[2] = global_timer_ns();
         if (all_arrived) {
             for (int p = 0; p < link.world; ++p) {
                 T v;
@@ -159,7 +172,7 @@ __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) 
                 result = Op::template apply<T>(result, v);
             }
         } else {
-            *link.status = 1;
+            link.status[0] = 1;
         }
     }
     return result;
@@ -168,10 +181,23 @@ __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) 
 template <typename T, typename Op, int THREADS, int UNROLL, bool PEER>
 __global__ void __launch_bounds__(THREADS)
 reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
-              T *partials, unsigned int *ticket, const PeerLink link) {
+              T *partials, unsigned int *ticket, const int chunked, const int input_ready,
+              const PeerLink link) {
     constexpr int VEC = 32 / sizeof(T);
     __shared__ T slots[THREADS / 32];
     __shared__ bool is_last;
+
+    // Programmatic dependent launch: the next kernel on the stream may be scheduled
+    // as soon as every CTA of this one has started, and then waits below for this
+    // kernel to complete, with its memory visible, before it touches anything this
+    // kernel may still write.  When the caller has promised that the input was
+    // complete before the preceding kernel began (input_ready), that wait moves
+    // behind the load loop: the reads of reduction k+1 then overlap the last block
+    // and the cross-GPU exchange of reduction k, and only the scratch, the mailboxes
+    // and the result are touched in stream order.  Both instructions do nothing in a
+    // launch without the programmatic attribute.
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (!input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
     int64_t head = static_cast<int64_t>(((32u - (addr & 31u)) & 31u) / sizeof(T));
@@ -180,7 +206,10 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     const int64_t nvec = (n - head) / VEC;
     const int64_t tail_begin = head + nvec * VEC;
     constexpr int64_t CHUNK = static_cast<int64_t>(THREADS) * UNROLL;
-    const int64_t nchunks = nvec / CHUNK;
+    // short inputs skip the chunk loop: the grid-stride loop below spreads their
+    // vectors evenly over twice as many CTAs as there are whole chunks
+    const int64_t nchunks = chunked ? nvec / CHUNK : 0;
+    const int64_t gstride = static_cast<int64_t>(gridDim.x) * THREADS;
 
     T acc[UNROLL];
 #pragma unroll
@@ -200,9 +229,15 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) packed[u] = fold_words<T, Op>(packed[u], raw[u]);
         }
-        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
-             v += static_cast<int64_t>(gridDim.x) * THREADS)
-            packed[0] = fold_words<T, Op>(packed[0], load_stream32(xv + v));
+        int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+        for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
+            Bits256 raw[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(xv + v + u * gstride);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) packed[u] = fold_words<T, Op>(packed[u], raw[u]);
+        }
+        for (; v < nvec; v += gstride) packed[0] = fold_words<T, Op>(packed[0], load_stream32(xv + v));
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) acc[u] = fold_word<T, Op>(acc[u], packed[u]);
     } else {
@@ -218,13 +253,24 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
             }
         }
         // vectors past the last whole chunk, spread over the grid
-        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
-             v += static_cast<int64_t>(gridDim.x) * THREADS) {
+        int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+        for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
+            Bits256 raw[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(xv + v + u * gstride);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                acc[u] = fold_vector<T, Op>(acc[u], raw[u].lo);
+                acc[u] = fold_vector<T, Op>(acc[u], raw[u].hi);
+            }
+        }
+        for (; v < nvec; v += gstride) {
             const Bits256 raw = load_stream32(xv + v);
             acc[0] = fold_vector<T, Op>(acc[0], raw.lo);
             acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
         }
     }
+    if (input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (blockIdx.x == 0) {  // fewer than 32 scalars on each side
         if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);
         const int64_t t = tail_begin + threadIdx.x;
@@ -253,26 +299,44 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
 
 template <typename T, typename Op>
 int launch(const void *x, int64_t n, const void *init_host, void *out, void *scratch,
-           cudaStream_t stream, const PeerLink *link) {
+           cudaStream_t stream, const PeerLink *link, unsigned flags) {
     T init;
     memcpy(&init, init_host, sizeof(T));
-    // two persistent CTAs per SM measured best on B200; short inputs get one CTA per chunk
-    const int per_sm = b2k::env_int("B2K_REDUCE_CTAS_PER_SM", 2);
+    // two persistent CTAs per SM measured best on B200.  Inputs of fewer than eight
+    // chunks per CTA are not cut into chunks (a CTA would own one or two of them and
+    // the grid would be lopsided, or smaller than the GPU): their 32-byte vectors go
+    // round the grid, one CTA per THREADS vectors up to the same two CTAs per SM.
+    const int per_sm = B2K_ENV_INT("B2K_REDUCE_CTAS_PER_SM", 2);
     int64_t max_grid = static_cast<int64_t>(b2k::sm_count()) * per_sm;
     if (max_grid > kMaxGrid) max_grid = kMaxGrid;
     const int64_t chunk_bytes = static_cast<int64_t>(kThreads) * kUnroll * 32;
-    int64_t grid = (n * static_cast<int64_t>(sizeof(T)) + chunk_bytes - 1) / chunk_bytes;
+    const int64_t nbytes = n * static_cast<int64_t>(sizeof(T));
+    const int chunked = nbytes >= chunk_bytes * max_grid * B2K_ENV_INT("B2K_REDUCE_MIN_CHUNKS_PER_CTA", 8);
+    int64_t grid = chunked ? max_grid : (nbytes + kThreads * 32 - 1) / (kThreads * 32);
     if (grid < 1) grid = 1;
     if (grid > max_grid) grid = max_grid;
     auto *ticket = static_cast<unsigned int *>(scratch);
     auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const bool pdl = B2K_ENV_INT("B2K_REDUCE_PDL", 1) != 0;
+    cfg.numAttrs = pdl ? 1 : 0;
+    const int input_ready = (pdl && (flags & B2K_REDUCE_INPUT_READY)) ? 1 : 0;
+    cudaError_t err;
     if (link) {
-        reduce_kernel<T, Op, kThreads, kUnroll, true><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket, *link);
+        err = cudaLaunchKernelEx(&cfg, reduce_kernel<T, Op, kThreads, kUnroll, true>, static_cast<const T *>(x), n,
+                                 init, static_cast<T *>(out), partials, ticket, chunked, input_ready, *link);
     } else {
-        reduce_kernel<T, Op, kThreads, kUnroll, false><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
-            static_cast<const T *>(x), n, init, static_cast<T *>(out), partials, ticket, PeerLink{});
+        err = cudaLaunchKernelEx(&cfg, reduce_kernel<T, Op, kThreads, kUnroll, false>, static_cast<const T *>(x), n,
+                                 init, static_cast<T *>(out), partials, ticket, chunked, input_ready, PeerLink{});
     }
+    if (err != cudaSuccess) return b2k::check_cuda(err, "b2k_reduce launch");
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_reduce launch");
     return B2K_OK;
@@ -280,19 +344,19 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
 
 template <typename T>
 int dispatch_op(int op, const void *x, int64_t n, const void *init_host, void *out,
-                void *scratch, cudaStream_t stream, const PeerLink *link) {
+                void *scratch, cudaStream_t stream, const PeerLink *link, unsigned flags) {
     switch (op) {
-    case B2K_ADD: return launch<T, OpAdd>(x, n, init_host, out, scratch, stream, link);
-    case B2K_MUL: return launch<T, OpMul>(x, n, init_host, out, scratch, stream, link);
-    case B2K_MAX: return launch<T, OpMax>(x, n, init_host, out, scratch, stream, link);
-    case B2K_MIN: return launch<T, OpMin>(x, n, init_host, out, scratch, stream, link);
+    case B2K_ADD: return launch<T, OpAdd>(x, n, init_host, out, scratch, stream, link, flags);
+    case B2K_MUL: return launch<T, OpMul>(x, n, init_host, out, scratch, stream, link, flags);
+    case B2K_MAX: return launch<T, OpMax>(x, n, init_host, out, scratch, stream, link, flags);
+    case B2K_MIN: return launch<T, OpMin>(x, n, init_host, out, scratch, stream, link, flags);
     default: break;
     }
     if constexpr (!(std::is_same<T, float>::value || std::is_same<T, double>::value)) {
         switch (op) {
-        case B2K_AND: return launch<T, OpAnd>(x, n, init_host, out, scratch, stream, link);
-        case B2K_OR: return launch<T, OpOr>(x, n, init_host, out, scratch, stream, link);
-        case B2K_XOR: return launch<T, OpXor>(x, n, init_host, out, scratch, stream, link);
+        case B2K_AND: return launch<T, OpAnd>(x, n, init_host, out, scratch, stream, link, flags);
+        case B2K_OR: return launch<T, OpOr>(x, n, init_host, out, scratch, stream, link, flags);
+        case B2K_XOR: return launch<T, OpXor>(x, n, init_host, out, scratch, stream, link, flags);
         default: break;
         }
     }
@@ -316,7 +380,8 @@ extern "C" {
 int64_t b2k_reduce_scratch_bytes(void) { return kTicketBytes + 8 * static_cast<int64_t>(kMaxGrid); }
 
 static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
-                       void *scratch_dev, int64_t scratch_bytes, void *stream, const PeerLink *link) {
+                       void *scratch_dev, int64_t scratch_bytes, void *stream, const PeerLink *link,
+                       unsigned flags) {
     const size_t size = dtype_size(dtype);
     if (size == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown dtype %d", dtype);
     if (op < B2K_ADD || op > B2K_XOR) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: unknown op %d", op);
@@ -332,23 +397,30 @@ static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const vo
         return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce: scratch must be 256-byte aligned");
     cudaStream_t s = b2k::as_stream(stream);
     switch (dtype) {
-    case B2K_I8: return dispatch_op<int8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_I16: return dispatch_op<int16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_I32: return dispatch_op<int32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_I64: return dispatch_op<int64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_U8: return dispatch_op<uint8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_U16: return dispatch_op<uint16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_U32: return dispatch_op<uint32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_U64: return dispatch_op<uint64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
-    default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link);
+    case B2K_I8: return dispatch_op<int8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_I16: return dispatch_op<int16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_I32: return dispatch_op<int32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_I64: return dispatch_op<int64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_U8: return dispatch_op<uint8_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_U16: return dispatch_op<uint16_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_U32: return dispatch_op<uint32_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_U64: return dispatch_op<uint64_t>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    case B2K_F32: return dispatch_op<float>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
+    default: return dispatch_op<double>(op, x_dev, n, init_host, out_dev, scratch_dev, s, link, flags);
     }
 }
 
 
 int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
-    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr);
+    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr, 0u);
+}
+
+int b2k_reduce_ex(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
+                  void *scratch_dev, int64_t scratch_bytes, unsigned flags, void *stream) {
+    if (flags & ~static_cast<unsigned>(B2K_REDUCE_INPUT_READY))
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_ex: unknown flag bits 0x%x", flags);
+    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr, flags);
 }
 
 // ---- mailboxes for the in-kernel cross-GPU combine -----------------------------------
@@ -393,12 +465,17 @@ int b2k_peer_mailbox_close(void *peer_mailbox_dev) {
 
 int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
                     void *scratch_dev, int64_t scratch_bytes, void *const *mailboxes, int world, int rank,
-                    uint64_t epoch, uint64_t timeout_ns, int *status_dev, void *stream) {
+                    uint64_t epoch, uint64_t timeout_ns, void *status_dev, unsigned flags, void *stream) {
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: world %d / rank %d out of range (at most %d ranks)",
                          world, rank, kMaxPeers);
-    if (!mailboxes || !status_dev || epoch == 0)
-        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: null mailboxes/status or epoch 0");
+    if (!mailboxes || !status_dev || (epoch & 0xFFFFFFFFull) == 0)
+        return b2k::fail(B2K_ERR_INVALID_ARG,
+                         "b2k_reduce_peer: null mailboxes/status, or an epoch whose low 32 bits are zero");
+    if (!b2k::aligned_to<void>(status_dev, 8))
+        return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_peer: status must be 8-byte aligned");
+    if (flags & ~static_cast<unsigned>(B2K_REDUCE_INPUT_READY))
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: unknown flag bits 0x%x", flags);
     PeerLink link{};
     for (int p = 0; p < world; ++p) {
         if (!mailboxes[p] || !b2k::aligned_to<void>(mailboxes[p], 16))
@@ -409,8 +486,8 @@ int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void 
     link.rank = rank;
     link.epoch = epoch;
     link.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
-    link.status = status_dev;
-    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, &link);
+    link.status = static_cast<unsigned long long *>(status_dev);
+    return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, &link, flags);
 }
 
 }  // extern "C"

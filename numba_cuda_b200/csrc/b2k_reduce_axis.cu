@@ -110,9 +110,15 @@ template <typename T, typename Op, int V>
 __global__ void __launch_bounds__(kThreads)
 reduce_cols_kernel(const unsigned char *__restrict__ x, int64_t rows, int64_t packs, int64_t pitch, int lx_log2,
                    int64_t rows_per_chunk, T init, Pack<T, V> *__restrict__ out, Pack<T, V> *__restrict__ partials,
-                   unsigned int *__restrict__ tickets) {
+                   unsigned int *__restrict__ tickets, int64_t slab_bytes) {
     __shared__ Pack<T, V> lanes[kThreads];
     __shared__ bool is_last;
+    // blockIdx.z numbers the matrices of a batch: `slab_bytes` apart on the input side,
+    // one output row, one block of partial rows and one run of tickets each
+    x += static_cast<int64_t>(blockIdx.z) * slab_bytes;
+    out += static_cast<int64_t>(blockIdx.z) * packs;
+    partials += static_cast<int64_t>(blockIdx.z) * gridDim.y * packs;
+    tickets += static_cast<int64_t>(blockIdx.z) * gridDim.x;
     const int lx = 1 << lx_log2;
     const int tx = threadIdx.x & (lx - 1), ty = threadIdx.x >> lx_log2, ny = kThreads >> lx_log2;
     const int64_t pack = static_cast<int64_t>(blockIdx.x) * lx + tx;
@@ -304,7 +310,7 @@ int log2_ceil(int64_t v) {
     return l;
 }
 
-Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, int64_t alignment) {
+Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, int64_t alignment, int64_t batch = 1) {
     Plan p{};
     // widest pack that the layout's alignment and the row length allow
     p.pack_bytes = item;
@@ -320,16 +326,17 @@ Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, int64_t align
         p.lx_log2 = p.packs >= 32 ? 5 : log2_ceil(p.packs < 1 ? 1 : p.packs);
         const int64_t lx = int64_t(1) << p.lx_log2, ny = kThreads / lx;
         p.tiles = (p.packs + lx - 1) / lx;
-        int64_t chunks = (sms * 8 + p.tiles - 1) / p.tiles;
+        const int64_t columns_of_ctas = p.tiles * batch;
+        int64_t chunks = (sms * 8 + columns_of_ctas - 1) / columns_of_ctas;
         const int64_t most = rows / (ny * kUnroll);  // every chunk gets at least one unrolled pass
         if (chunks > most) chunks = most;
         if (chunks > kMaxChunks) chunks = kMaxChunks;
-        if (chunks < 1 || p.tiles > kMaxTickets) chunks = 1;
+        if (chunks < 1 || columns_of_ctas > kMaxTickets) chunks = 1;
         p.rows_per_chunk = (rows + chunks - 1) / chunks;
         p.chunks = (rows + p.rows_per_chunk - 1) / (p.rows_per_chunk < 1 ? 1 : p.rows_per_chunk);
         if (p.chunks < 1) p.chunks = 1;
         p.ticket_bytes = p.chunks > 1 ? kTicketRegion : 0;
-        p.scratch_bytes = p.ticket_bytes + (p.chunks > 1 ? p.chunks * p.packs * p.pack_bytes : 0);
+        p.scratch_bytes = p.ticket_bytes + (p.chunks > 1 ? batch * p.chunks * p.packs * p.pack_bytes : 0);
     } else {
         // lanes per row: about 64 bytes per lane, a whole CTA for long rows
         const int64_t want = (p.packs * p.pack_bytes + 63) / 64;
@@ -355,15 +362,15 @@ Plan make_plan(int64_t rows, int64_t cols, int64_t item, int axis, int64_t align
 
 template <typename T, typename Op, int V>
 int launch_planned(const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis, T init, void *out,
-                   void *scratch, cudaStream_t stream) {
+                   void *scratch, cudaStream_t stream, int64_t batch, int64_t slab_bytes) {
     const unsigned char *src = static_cast<const unsigned char *>(x);
     unsigned char *sc = static_cast<unsigned char *>(scratch);
     if (axis == 0) {
         if (p.tiles > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_reduce_axis: too many columns");
-        const dim3 grid(static_cast<unsigned>(p.tiles), static_cast<unsigned>(p.chunks));
+        const dim3 grid(static_cast<unsigned>(p.tiles), static_cast<unsigned>(p.chunks), static_cast<unsigned>(batch));
         reduce_cols_kernel<T, Op, V><<<grid, kThreads, 0, stream>>>(
             src, rows, p.packs, pitch, p.lx_log2, p.rows_per_chunk, init, static_cast<Pack<T, V> *>(out),
-            reinterpret_cast<Pack<T, V> *>(sc + p.ticket_bytes), reinterpret_cast<unsigned int *>(sc));
+            reinterpret_cast<Pack<T, V> *>(sc + p.ticket_bytes), reinterpret_cast<unsigned int *>(sc), slab_bytes);
     } else if (p.split) {
         const dim3 grid(static_cast<unsigned>(p.segments), static_cast<unsigned>(rows));
         reduce_rows_split_kernel<T, Op, V><<<grid, kThreads, 0, stream>>>(
@@ -383,51 +390,53 @@ int launch_planned(const Plan &p, const void *x, int64_t rows, int64_t pitch, in
 
 template <typename T, typename Op>
 int launch_typed(const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis, const void *init_host,
-                 void *out, void *scratch, cudaStream_t stream) {
+                 void *out, void *scratch, cudaStream_t stream, int64_t batch, int64_t slab_bytes) {
     T init;
     memcpy(&init, init_host, sizeof(T));
     constexpr int SIZE = sizeof(T);
     if constexpr (SIZE < 16) {
-        if (p.pack_bytes == 16) return launch_planned<T, Op, 16 / SIZE>(p, x, rows, pitch, axis, init, out, scratch, stream);
+        if (p.pack_bytes == 16) return launch_planned<T, Op, 16 / SIZE>(p, x, rows, pitch, axis, init, out, scratch, stream, batch, slab_bytes);
     }
     if constexpr (SIZE < 8) {
-        if (p.pack_bytes == 8) return launch_planned<T, Op, (8 / SIZE > 0 ? 8 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+        if (p.pack_bytes == 8) return launch_planned<T, Op, (8 / SIZE > 0 ? 8 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream, batch, slab_bytes);
     }
     if constexpr (SIZE < 4) {
-        if (p.pack_bytes == 4) return launch_planned<T, Op, (4 / SIZE > 0 ? 4 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream);
+        if (p.pack_bytes == 4) return launch_planned<T, Op, (4 / SIZE > 0 ? 4 / SIZE : 1)>(p, x, rows, pitch, axis, init, out, scratch, stream, batch, slab_bytes);
     }
-    return launch_planned<T, Op, 1>(p, x, rows, pitch, axis, init, out, scratch, stream);
+    return launch_planned<T, Op, 1>(p, x, rows, pitch, axis, init, out, scratch, stream, batch, slab_bytes);
 }
 
 // Integer +, *, &, |, ^ wrap identically for both signs, so signed types run those
 // ops in the unsigned type of their width; only max and min need the sign.
 template <typename S, typename U>
 int dispatch_integer(int op, bool is_signed, const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis,
-                     const void *init_host, void *out, void *scratch, cudaStream_t stream) {
+                     const void *init_host, void *out, void *scratch, cudaStream_t stream, int64_t batch,
+                     int64_t slab_bytes) {
     switch (op) {
-    case B2K_ADD: return launch_typed<U, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_MUL: return launch_typed<U, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_AND: return launch_typed<U, OpAnd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_OR: return launch_typed<U, OpOr>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_XOR: return launch_typed<U, OpXor>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_ADD: return launch_typed<U, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_MUL: return launch_typed<U, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_AND: return launch_typed<U, OpAnd>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_OR: return launch_typed<U, OpOr>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_XOR: return launch_typed<U, OpXor>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
     case B2K_MAX:
-        return is_signed ? launch_typed<S, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream)
-                         : launch_typed<U, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+        return is_signed ? launch_typed<S, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes)
+                         : launch_typed<U, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
     case B2K_MIN:
-        return is_signed ? launch_typed<S, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream)
-                         : launch_typed<U, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+        return is_signed ? launch_typed<S, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes)
+                         : launch_typed<U, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
     default: return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: unknown op %d", op);
     }
 }
 
 template <typename F>
 int dispatch_float(int op, const Plan &p, const void *x, int64_t rows, int64_t pitch, int axis,
-                   const void *init_host, void *out, void *scratch, cudaStream_t stream) {
+                   const void *init_host, void *out, void *scratch, cudaStream_t stream, int64_t batch,
+                     int64_t slab_bytes) {
     switch (op) {
-    case B2K_ADD: return launch_typed<F, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_MUL: return launch_typed<F, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_MAX: return launch_typed<F, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
-    case B2K_MIN: return launch_typed<F, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream);
+    case B2K_ADD: return launch_typed<F, OpAdd>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_MUL: return launch_typed<F, OpMul>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_MAX: return launch_typed<F, OpMax>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
+    case B2K_MIN: return launch_typed<F, OpMin>(p, x, rows, pitch, axis, init_host, out, scratch, stream, batch, slab_bytes);
     default: return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_axis: bitwise op on a floating-point type");
     }
 }
@@ -466,44 +475,75 @@ int64_t b2k_reduce_axis_scratch_bytes(int64_t rows, int64_t cols, int dtype, int
     return most;
 }
 
-int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols, int64_t pitch_bytes, int axis,
-                    const void *init_host, void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+static int reduce_axis_impl(const char *who, int op, int dtype, const void *x_dev, int64_t batch, int64_t rows,
+                            int64_t cols, int64_t pitch_bytes, int64_t slab_bytes, int axis, const void *init_host,
+                            void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
     const int64_t item = item_size(dtype);
-    if (item == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: unknown dtype %d", dtype);
-    if (axis != 0 && axis != 1) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: axis must be 0 or 1");
-    if (rows < 0 || cols < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: negative shape");
-    if (!init_host) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null init");
-    const int64_t outputs = axis == 0 ? cols : rows;
+    if (item == 0) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: unknown dtype %d", who, dtype);
+    if (axis != 0 && axis != 1) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: axis must be 0 or 1", who);
+    if (rows < 0 || cols < 0 || batch < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: negative shape", who);
+    if (batch > 65535) return b2k::fail(B2K_ERR_TOO_LARGE, "%s: at most 65535 matrices per call", who);
+    if (!init_host) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: null init", who);
+    const int64_t outputs = (axis == 0 ? cols : rows) * batch;
     if (outputs == 0) return B2K_OK;
-    if (!out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null output");
-    if (reinterpret_cast<uintptr_t>(out_dev) % item) return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_axis: output not aligned to its item size");
+    if (!out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: null output", who);
+    if (reinterpret_cast<uintptr_t>(out_dev) % item)
+        return b2k::fail(B2K_ERR_ALIGNMENT, "%s: output not aligned to its item size", who);
     const int64_t reduced = axis == 0 ? rows : cols;
     if (reduced > 0) {
-        if (!x_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: null input");
-        if (reinterpret_cast<uintptr_t>(x_dev) % item || pitch_bytes % item)
-            return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_axis: input or pitch not aligned to the item size");
-        if (pitch_bytes < cols * item) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_axis: pitch shorter than a row");
+        if (!x_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: null input", who);
+        if (reinterpret_cast<uintptr_t>(x_dev) % item || pitch_bytes % item || slab_bytes % item)
+            return b2k::fail(B2K_ERR_ALIGNMENT, "%s: input, pitch or matrix stride not aligned to the item size", who);
+        if (pitch_bytes < cols * item) return b2k::fail(B2K_ERR_INVALID_ARG, "%s: pitch shorter than a row", who);
     }
     // an empty reduced axis leaves `init` in every output: same kernels, zero rows / packs
-    const Plan p = make_plan(rows, cols, item, axis, layout_alignment(x_dev, pitch_bytes, out_dev));
+    const int64_t alignment = layout_alignment(x_dev, pitch_bytes | (batch > 1 ? slab_bytes : 0), out_dev);
+    const Plan p = make_plan(rows, cols, item, axis, alignment, batch);
     if (p.scratch_bytes > 0) {
         if (!scratch_dev || scratch_bytes < p.scratch_bytes || reinterpret_cast<uintptr_t>(scratch_dev) % 256)
-            return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_axis: scratch of %lld bytes (256-byte aligned, zeroed once) needed",
+            return b2k::fail(B2K_ERR_SCRATCH, "%s: scratch of %lld bytes (256-byte aligned, zeroed once) needed", who,
                              static_cast<long long>(p.scratch_bytes));
     }
     cudaStream_t s = b2k::as_stream(stream);
+    const int64_t pitch = pitch_bytes;
     switch (dtype) {
-    case B2K_I8: return dispatch_integer<int8_t, uint8_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_U8: return dispatch_integer<int8_t, uint8_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_I16: return dispatch_integer<int16_t, uint16_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_U16: return dispatch_integer<int16_t, uint16_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_I32: return dispatch_integer<int32_t, uint32_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_U32: return dispatch_integer<int32_t, uint32_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_I64: return dispatch_integer<int64_t, uint64_t>(op, true, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_U64: return dispatch_integer<int64_t, uint64_t>(op, false, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    case B2K_F32: return dispatch_float<float>(op, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
-    default: return dispatch_float<double>(op, p, x_dev, rows, pitch_bytes, axis, init_host, out_dev, scratch_dev, s);
+    case B2K_I8: return dispatch_integer<int8_t, uint8_t>(op, true, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_U8: return dispatch_integer<int8_t, uint8_t>(op, false, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_I16: return dispatch_integer<int16_t, uint16_t>(op, true, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_U16: return dispatch_integer<int16_t, uint16_t>(op, false, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_I32: return dispatch_integer<int32_t, uint32_t>(op, true, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_U32: return dispatch_integer<int32_t, uint32_t>(op, false, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_I64: return dispatch_integer<int64_t, uint64_t>(op, true, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_U64: return dispatch_integer<int64_t, uint64_t>(op, false, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    case B2K_F32: return dispatch_float<float>(op, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
+    default: return dispatch_float<double>(op, p, x_dev, rows, pitch, axis, init_host, out_dev, scratch_dev, s, batch, slab_bytes);
     }
+}
+
+int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols, int64_t pitch_bytes, int axis,
+                    const void *init_host, void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    return reduce_axis_impl("b2k_reduce_axis", op, dtype, x_dev, 1, rows, cols, pitch_bytes, 0, axis, init_host,
+                            out_dev, scratch_dev, scratch_bytes, stream);
+}
+
+int64_t b2k_reduce_cols_batched_scratch_bytes(int64_t batch, int64_t rows, int64_t cols, int dtype) {
+    const int64_t item = item_size(dtype);
+    if (batch <= 0 || rows <= 0 || cols <= 0 || item == 0) return 0;
+    int64_t most = 0;
+    for (int64_t alignment = 16; alignment >= 1; alignment /= 2) {
+        const Plan p = make_plan(rows, cols, item, 0, alignment, batch);
+        if (p.scratch_bytes > most) most = p.scratch_bytes;
+    }
+    return most;
+}
+
+int b2k_reduce_cols_batched(int op, int dtype, const void *x_dev, int64_t batch, int64_t rows, int64_t cols,
+                            int64_t pitch_bytes, int64_t matrix_stride_bytes, const void *init_host, void *out_dev,
+                            void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    if (batch > 1 && matrix_stride_bytes < 0)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_cols_batched: negative matrix stride");
+    return reduce_axis_impl("b2k_reduce_cols_batched", op, dtype, x_dev, batch, rows, cols, pitch_bytes,
+                            matrix_stride_bytes, 0, init_host, out_dev, scratch_dev, scratch_bytes, stream);
 }
 
 }  // extern "C"

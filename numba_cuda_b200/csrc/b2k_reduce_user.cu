@@ -69,6 +69,15 @@ __device__ __forceinline__ unsigned long long b2k_abs(unsigned long long a) { re
 __device__ __forceinline__ double b2k_abs(double a) { return fabs(a); }
 __device__ __forceinline__ float b2k_abs(float a) { return fabsf(a); }
 
+// an unsigned 64-bit value against a signed one, compared as the numbers they are
+typedef unsigned long long b2k_u64;
+__device__ __forceinline__ bool b2k_lt(b2k_u64 a, long long b) { return b > 0 && a < (b2k_u64)b; }
+__device__ __forceinline__ bool b2k_lt(long long a, b2k_u64 b) { return a < 0 || (b2k_u64)a < b; }
+__device__ __forceinline__ bool b2k_le(b2k_u64 a, long long b) { return b >= 0 && a <= (b2k_u64)b; }
+__device__ __forceinline__ bool b2k_le(long long a, b2k_u64 b) { return a < 0 || (b2k_u64)a <= b; }
+__device__ __forceinline__ bool b2k_eq(b2k_u64 a, long long b) { return b >= 0 && a == (b2k_u64)b; }
+__device__ __forceinline__ bool b2k_eq(long long a, b2k_u64 b) { return a >= 0 && (b2k_u64)a == b; }
+
 __device__ __forceinline__ T user_op(T a_, T b_) {
     const W a = (W)a_;
     const W b = (W)b_;
@@ -120,7 +129,8 @@ __device__ __forceinline__ Partial block_fold(Partial p, Partial *slots) {
 
 extern "C" __global__ void __launch_bounds__(THREADS)
 b2k_user_reduce(const T *__restrict__ x, long long n, T init, T *__restrict__ out, T *partials,
-                unsigned int *ticket, long long per /* vectors per block; no block is empty */) {
+                unsigned int *ticket, long long per /* vectors per block; no block is empty */,
+                int fold_init) {
     __shared__ Partial slots[THREADS / 32];
     __shared__ bool is_last;
 
@@ -168,7 +178,7 @@ b2k_user_reduce(const T *__restrict__ x, long long n, T init, T *__restrict__ ou
     for (unsigned int i = threadIdx.x * each; i < g && i < (threadIdx.x + 1) * each; ++i)
         fold(mine, __ldcg(partials + i));
     total = block_fold(mine, slots);
-    if (threadIdx.x == 0) out[0] = user_op(total.v, init);
+    if (threadIdx.x == 0) out[0] = fold_init ? user_op(total.v, init) : total.v;
 }
 )b2ksrc";
 
@@ -246,10 +256,10 @@ bool type_info(int dtype, TypeInfo *out) {
     case B2K_I16: *out = {"short", "long long", "((long long)(x))", 2}; return true;
     case B2K_I32: *out = {"int", "long long", "((long long)(x))", 4}; return true;
     case B2K_I64: *out = {"long long", "long long", "((long long)(x))", 8}; return true;
-    case B2K_U8: *out = {"unsigned char", "long long", "((long long)(x))", 1}; return true;
-    case B2K_U16: *out = {"unsigned short", "long long", "((long long)(x))", 2}; return true;
-    case B2K_U32: *out = {"unsigned int", "long long", "((long long)(x))", 4}; return true;
-    case B2K_U64: *out = {"unsigned long long", "unsigned long long", "((unsigned long long)(x))", 8}; return true;
+    case B2K_U8: *out = {"unsigned char", "unsigned long long", "((long long)(x))", 1}; return true;
+    case B2K_U16: *out = {"unsigned short", "unsigned long long", "((long long)(x))", 2}; return true;
+    case B2K_U32: *out = {"unsigned int", "unsigned long long", "((long long)(x))", 4}; return true;
+    case B2K_U64: *out = {"unsigned long long", "unsigned long long", "((long long)(x))", 8}; return true;
     case B2K_F32: *out = {"float", "float", "((double)(x))", 4}; return true;
     case B2K_F64: *out = {"double", "double", "((double)(x))", 8}; return true;
     default: return false;
@@ -306,7 +316,7 @@ extern "C" int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, i
     if (!type_info(dtype, &ti)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: unknown dtype %d", dtype);
     if (!expr || !*expr) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: empty expression");
     if (n < 1) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: needs at least one element");
-    if (!x_dev || !init_host || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: null pointer");
+    if (!x_dev || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: null pointer");
     if (!scratch_dev || scratch_bytes < b2k_reduce_scratch_bytes() || !b2k::aligned_to<void>(scratch_dev, 256))
         return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce_expr: scratch of %lld bytes (256-byte aligned) required",
                          (long long)b2k_reduce_scratch_bytes());
@@ -343,11 +353,12 @@ extern "C" int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, i
     if (grid < 1) grid = 1;
     (void)nvec;
     unsigned long long init_bits = 0;
-    memcpy(&init_bits, init_host, ti.size);
+    int fold_init = init_host != nullptr;
+    if (fold_init) memcpy(&init_bits, init_host, ti.size);
     long long n_arg = n;
     void *ticket = scratch_dev;
     void *partials = static_cast<char *>(scratch_dev) + 256;
-    void *args[] = {const_cast<void **>(&x_dev), &n_arg, &init_bits, &out_dev, &partials, &ticket, &per};
+    void *args[] = {const_cast<void **>(&x_dev), &n_arg, &init_bits, &out_dev, &partials, &ticket, &per, &fold_init};
     const CUresult rc = driver().launch(fn, static_cast<unsigned>(grid), 1, 1, 512, 1, 1, 0,
                                         reinterpret_cast<CUstream>(stream), args, nullptr);
     b2k::note_launch();

@@ -98,7 +98,7 @@ extern "C" int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, 
     if (!in_dev || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_transpose2d: null pointer");
     cudaStream_t s = b2k::as_stream(stream);
 
-    if (b2k::env_int("B2K_TRANSPOSE_NO_TMA", 0) == 0) {
+    if (B2K_ENV_INT("B2K_TRANSPOSE_NO_TMA", 0) == 0) {
         const int rc = b2k::transpose_tma(in_dev, out_dev, rows, cols, in_stride0, in_stride1,
                                           out_stride0, out_stride1, itemsize, s);
         if (rc != B2K_ERR_UNSUPPORTED) return rc;
@@ -107,7 +107,7 @@ extern "C" int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, 
     // Items of up to 4 bytes: the 64x64 tiles of the strided-assignment kernels measured
     // 15-25 % faster than the 32x32 tiles below (out[j, i] = in[i, j] is an assignment
     // whose source strides are swapped).
-    if ((itemsize == 1 || itemsize == 2 || itemsize == 4) && b2k::env_int("B2K_TRANSPOSE_VIA_ASSIGN", 1) != 0) {
+    if ((itemsize == 1 || itemsize == 2 || itemsize == 4) && B2K_ENV_INT("B2K_TRANSPOSE_VIA_ASSIGN", 1) != 0) {
         const int64_t shape[2] = {cols, rows};
         const int64_t dst_steps[2] = {out_stride0, out_stride1};
         const int64_t src_steps[2] = {in_stride1, in_stride0};

@@ -527,32 +527,33 @@ int launch(const void *in, void *out, int64_t rows, int64_t cols, int64_t in_pit
     // back-to-back tiles.
     const bool aligned = in_pitch % 128 == 0 && out_pitch % 128 == 0;
     const bool auto_split = ES >= 4 || !aligned;
-    const int forced = b2k::env_int("B2K_TRANSPOSE_SPLIT", -1);
+    const int forced = B2K_ENV_INT("B2K_TRANSPOSE_SPLIT", -1);
     const bool split = forced < 0 ? auto_split : forced != 0;
     auto kernel = split ? transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>
                         : transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>;
-    static std::once_flag once;
-    static cudaError_t attr_status = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_status = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (attr_status == cudaSuccess)
-            attr_status = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // the shared-memory limit is a per-device attribute of the function
+    static b2k::PerDeviceOnce once;
+    const cudaError_t attr_status = once.run([] {
+        cudaError_t e = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(transpose_tma_kernel<ES, R, NSTAGE, THREADS, NOUT, false>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        return e;
     });
     if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
     // two resident CTAs per SM measured best (more CTAs only add DRAM page conflicts)
-    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 2);
+    const int per_sm = B2K_ENV_INT("B2K_TRANSPOSE_CTAS_PER_SM", 2);
     int64_t grid = static_cast<int64_t>(b2k::sm_count()) * (per_sm < 1 ? 1 : per_sm);
     if (grid > tiles) grid = tiles;
-    int panel_w = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
+    int panel_w = B2K_ENV_INT("B2K_TRANSPOSE_PANEL", 4);
     if (panel_w < 1 || panel_w > tiles_x) panel_w = static_cast<int>(tiles_x);
     const TileOrder order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), panel_w};
     // the refill thread is a run-time argument on purpose: as a constant the compiler
     // would fuse the two blocks of the SPLIT shape back into one
     kernel<<<static_cast<unsigned>(grid), THREADS, SMEM, stream>>>(in_map, out_map, order,
                                                                    static_cast<long long>(tiles),
-                                                                   b2k::env_int("B2K_TRANSPOSE_REFILL_THREAD", 0));
+                                                                   B2K_ENV_INT("B2K_TRANSPOSE_REFILL_THREAD", 0));
     b2k::note_launch();
     B2K_RETURN_IF_LAUNCH_FAILED("b2k_transpose2d (tma) launch");
     return B2K_OK;
@@ -600,16 +601,15 @@ int launch_batched(const void *in, void *out, int64_t rows, int64_t cols, int64_
     const int64_t tiles = tiles2d * slices;
     constexpr int SMEM = (NSTAGE + NOUT) * R * 128 + NSTAGE * 8 + 1024;
     auto kernel = transpose_tma_batched_kernel<ES, R, NSTAGE, THREADS, NOUT>;
-    static std::once_flag once;
-    static cudaError_t attr_status = cudaSuccess;
-    std::call_once(once, [&] {
-        attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    static b2k::PerDeviceOnce once;
+    const cudaError_t attr_status = once.run([&] {
+        return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     });
     if (attr_status != cudaSuccess) return b2k::check_cuda(attr_status, "transpose smem attribute");
-    const int per_sm = b2k::env_int("B2K_TRANSPOSE_CTAS_PER_SM", 2);
+    const int per_sm = B2K_ENV_INT("B2K_TRANSPOSE_CTAS_PER_SM", 2);
     int64_t grid = static_cast<int64_t>(b2k::sm_count()) * (per_sm < 1 ? 1 : per_sm);
     if (grid > tiles) grid = tiles;
-    int panel_w = b2k::env_int("B2K_TRANSPOSE_PANEL", 4);
+    int panel_w = B2K_ENV_INT("B2K_TRANSPOSE_PANEL", 4);
     if (panel_w < 1 || panel_w > tiles_x) panel_w = static_cast<int>(tiles_x);
     const TileOrder order{static_cast<int>(tiles_x), static_cast<int>(tiles_y), panel_w};
     const int64_t adv_slices = grid / tiles2d;
@@ -646,7 +646,7 @@ int transpose_tma(const void *in, void *out, int64_t rows, int64_t cols, int64_t
         cols * (itemsize >= 4 ? itemsize / 4 : 1) >= (int64_t(1) << 31))
         return B2K_ERR_UNSUPPORTED;
     // small arrays: the general tile kernel has less fixed cost
-    if (rows * cols * itemsize < b2k::env_int("B2K_TRANSPOSE_TMA_MIN_BYTES", 1 << 16)) return B2K_ERR_UNSUPPORTED;
+    if (rows * cols * itemsize < B2K_ENV_INT("B2K_TRANSPOSE_TMA_MIN_BYTES", 1 << 16)) return B2K_ERR_UNSUPPORTED;
     // Single bytes on lines that are multiples of 64 bytes run 10-18 % faster through
     // the stacked kernel with an empty stack (its issuing thread reads the coordinates
     // of the tile to store from shared memory instead of recomputing them, which

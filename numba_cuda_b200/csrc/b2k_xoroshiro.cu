@@ -558,20 +558,19 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
     Poly4 p_low{{static_cast<uint32_t>(rc.p_low.lo), static_cast<uint32_t>(rc.p_low.lo >> 32),
                  static_cast<uint32_t>(rc.p_low.hi), static_cast<uint32_t>(rc.p_low.hi >> 32)}};
 
-    if (n >= (int64_t(1) << 18) && b2k::env_int("B2K_XORO_INIT_TABLES", 1) != 0) {
-        static std::once_flag once;
-        static cudaError_t attr = cudaSuccess;
-        std::call_once(once, [] {
-            attr = cudaFuncSetAttribute(xoro_init_table_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (n >= (int64_t(1) << 18) && B2K_ENV_INT("B2K_XORO_INIT_TABLES", 1) != 0) {
+        static b2k::PerDeviceOnce once;   // the limit belongs to the device, not to the process
+        const cudaError_t attr = once.run([] {
+            return cudaFuncSetAttribute(xoro_init_table_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kTableBytes);
         });
         if (attr != cudaSuccess) return b2k::check_cuda(attr, "b2k_xoroshiro128p_init: smem attribute");
         // one contiguous run per thread over a grid that fills the GPU once; runs of
         // at least 64 states keep the y^index products a small share of the work
         const int64_t resident =
-            static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_INIT_CTAS_PER_SM", 2) * 256;
+            static_cast<int64_t>(b2k::sm_count()) * B2K_ENV_INT("B2K_XORO_INIT_CTAS_PER_SM", 2) * 256;
         int64_t per_thread = (n + resident - 1) / resident;
-        const int64_t floor_run = b2k::env_int("B2K_XORO_INIT_PER_THREAD", 64);
+        const int64_t floor_run = B2K_ENV_INT("B2K_XORO_INIT_PER_THREAD", 64);
         if (per_thread < floor_run) per_thread = floor_run;
         per_thread += per_thread & 1;
         if (per_thread > 0x7FFFFFFE) per_thread = 0x7FFFFFFE;
@@ -585,7 +584,7 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
     } else {
         // short arrays: runs of 16 amortise the table products, tiny ones stay parallel
         int per_thread = n >= (int64_t(1) << 16) ? 16 : 1;
-        per_thread = b2k::env_int("B2K_XORO_INIT_SHORT_PER_THREAD", per_thread);
+        per_thread = B2K_ENV_INT("B2K_XORO_INIT_SHORT_PER_THREAD", per_thread);
         if (per_thread < 1) per_thread = 1;
         const int64_t threads = (n + per_thread - 1) / per_thread;
         const int64_t grid = (threads + 255) / 256;
@@ -618,7 +617,7 @@ int b2k_xoroshiro128p_fill(void *states_dev, int64_t n, int draw0, void *out0_de
     }
     const int64_t groups = (n + 31) / 32;
     int64_t grid = (groups + kFillWarps - 1) / kFillWarps;
-    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * b2k::env_int("B2K_XORO_FILL_CTAS_PER_SM", 8);
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * B2K_ENV_INT("B2K_XORO_FILL_CTAS_PER_SM", 8);
     if (grid > cap) grid = cap;
     Segment a{out0_dev, count0, draw0}, b{out1_dev, count1, draw1};
     xoro_fill_kernel<4, 4><<<static_cast<unsigned>(grid), kFillWarps * 32, 0, b2k::as_stream(stream)>>>(

@@ -12,8 +12,10 @@ loops over the operands, more than 64 paths) raises ``NotImplementedError``.
 
 Arithmetic follows numba's typing of the same function: integer operands are
 widened to 64 bits for the whole expression and truncated when the result is
-stored; float32 stays float32 unless it meets a Python float (a double);
-``//`` and ``%`` have Python's floor semantics.
+stored -- unsigned items to ``uint64``, signed items and integer constants to
+``int64``, and an operation that mixes the two is done in ``int64`` (numba's
+integer rule: 64 bits, signed if either side is); float32 stays float32 unless it
+meets a Python float (a double); ``//`` and ``%`` have Python's floor semantics.
 """
 from __future__ import annotations
 
@@ -24,14 +26,20 @@ import numpy as np
 _MAX_PATHS = 64
 
 
-class _NeedDecision(Exception):
-    pass
+#: comparisons between an unsigned and a signed 64-bit value (helpers of the kernel source)
+_MIXED_COMPARE = {
+    "({a} < {b})": "b2k_lt({a}, {b})", "({a} <= {b})": "b2k_le({a}, {b})",
+    "({a} > {b})": "b2k_lt({b}, {a})", "({a} >= {b})": "b2k_le({b}, {a})",
+    "({a} == {b})": "b2k_eq({a}, {b})", "({a} != {b})": "(!b2k_eq({a}, {b}))",
+}
 
 
 class _Tracer:
-    def __init__(self):
+    def __init__(self, operand_sign=None):
         self.forced = []       # outcomes imposed on the first comparisons
         self.taken = []        # (condition code, outcome) met during this run
+        self.operand_sign = operand_sign          # 'u', 's' or None (floating point)
+        self.integers = operand_sign is not None
 
     def decide(self, cond_code: str) -> bool:
         k = len(self.taken)
@@ -41,13 +49,14 @@ class _Tracer:
 
 
 class Sym:
-    """A traced value: ``code`` is a C++ expression, ``kind`` is 'v' (value) or 'b' (bool)."""
+    """A traced value: ``code`` is a C++ expression, ``kind`` is 'v' (value) or 'b'
+    (bool), ``sign`` is 'u' (uint64), 's' (int64) or None (floating point / unknown)."""
 
-    __slots__ = ("code", "kind", "tr")
+    __slots__ = ("code", "kind", "tr", "sign")
     __array_priority__ = 1000  # keep NumPy scalars from taking over mixed operations
 
-    def __init__(self, code, tr, kind="v"):
-        self.code, self.tr, self.kind = code, tr, kind
+    def __init__(self, code, tr, kind="v", sign=None):
+        self.code, self.tr, self.kind, self.sign = code, tr, kind, sign
 
     # -- helpers
     def _lit(self, other):
@@ -61,17 +70,43 @@ class Sym:
                 raise NotImplementedError("integer constant out of 64-bit range")
             # B2K_ILIT: the wide integer type for integer arrays, double for float arrays
             # (numba promotes float32 <op> integer to float64)
-            return f"B2K_ILIT({v}ULL)" if v >= 2 ** 63 else f"B2K_ILIT({v}LL)"
+            if v >= 2 ** 63:       # only uint64 holds it
+                return f"{v}ULL" if self.tr.integers else f"B2K_ILIT({v}ULL)"
+            return f"B2K_ILIT({v}LL)"
         if isinstance(other, (numbers.Real, np.floating)):
             return repr(float(other)) if np.isfinite(other) else \
                 ("B2K_NAN" if np.isnan(other) else ("B2K_INF" if other > 0 else "(-B2K_INF)"))
         raise NotImplementedError(f"cannot use a {type(other).__name__} in a reduce functor")
 
+    def _sign_of(self, other):
+        if isinstance(other, Sym):
+            return other.sign
+        if isinstance(other, (bool, np.bool_)):
+            return "s"
+        if isinstance(other, (numbers.Integral, np.integer)):
+            return "u" if int(other) >= 2 ** 63 else "s"
+        return None
+
+    def _meet(self, left, lsign, right, rsign, fmt, kind):
+        """One binary operation under the integer rule: unsigned only if both sides are."""
+        if self.tr.integers and kind == "v" and "b2k_truediv" in fmt:
+            sign = None
+        elif lsign is None or rsign is None or not self.tr.integers:
+            sign = None
+        elif lsign == rsign:
+            sign = lsign
+        elif kind == "b":
+            # an unsigned value against a signed one: compared as the numbers they are
+            fmt, sign = _MIXED_COMPARE[fmt], None
+        else:
+            left, right, sign = f"((long long){left})", f"((long long){right})", "s"
+        return Sym(fmt.format(a=left, b=right), self.tr, kind, sign if kind == "v" else None)
+
     def _bin(self, other, fmt, kind="v"):
-        return Sym(fmt.format(a=self.code, b=self._lit(other)), self.tr, kind)
+        return self._meet(self.code, self.sign, self._lit(other), self._sign_of(other), fmt, kind)
 
     def _rbin(self, other, fmt, kind="v"):
-        return Sym(fmt.format(a=self._lit(other), b=self.code), self.tr, kind)
+        return self._meet(self._lit(other), self._sign_of(other), self.code, self.sign, fmt, kind)
 
     # -- arithmetic
     def __add__(self, o): return self._bin(o, "({a} + {b})")
@@ -92,18 +127,23 @@ class Sym:
     def __ror__(self, o): return self._rbin(o, "({a} | {b})")
     def __xor__(self, o): return self._bin(o, "({a} ^ {b})")
     def __rxor__(self, o): return self._rbin(o, "({a} ^ {b})")
-    def __lshift__(self, o): return self._bin(o, "({a} << {b})")
-    def __rshift__(self, o): return self._bin(o, "({a} >> {b})")
-    def __neg__(self): return Sym(f"(-{self.code})", self.tr)
+    def __lshift__(self, o): return Sym("({a} << {b})".format(a=self.code, b=self._lit(o)), self.tr, "v", self.sign)
+    def __rshift__(self, o): return Sym("({a} >> {b})".format(a=self.code, b=self._lit(o)), self.tr, "v", self.sign)
+
+    def __neg__(self):
+        if self.sign == "u":      # the negative of an unsigned value is a signed one
+            return Sym(f"(-(long long){self.code})", self.tr, "v", "s")
+        return Sym(f"(-{self.code})", self.tr, "v", self.sign)
+
     def __pos__(self): return self
-    def __invert__(self): return Sym(f"(~{self.code})", self.tr)
-    def __abs__(self): return Sym(f"b2k_abs({self.code})", self.tr)
+    def __invert__(self): return Sym(f"(~{self.code})", self.tr, "v", self.sign)
+    def __abs__(self): return Sym(f"b2k_abs({self.code})", self.tr, "v", self.sign)
 
     def __pow__(self, o):
         if isinstance(o, (numbers.Integral, np.integer)) and 0 <= int(o) <= 8:
             if int(o) == 0:
-                return Sym("B2K_ILIT(1LL)", self.tr)
-            return Sym("(" + " * ".join([self.code] * int(o)) + ")", self.tr)
+                return Sym("B2K_ILIT(1LL)", self.tr, "v", "s" if self.tr.integers else None)
+            return Sym("(" + " * ".join([self.code] * int(o)) + ")", self.tr, "v", self.sign)
         raise NotImplementedError("only small constant integer powers are supported")
 
     # -- comparisons
@@ -128,10 +168,10 @@ class Sym:
     __int__ = __float__
 
 
-def _run(functor, forced):
-    tr = _Tracer()
+def _run(functor, forced, operand_sign):
+    tr = _Tracer(operand_sign)
     tr.forced = list(forced)
-    res = functor(Sym("a", tr), Sym("b", tr))
+    res = functor(Sym("a", tr, "v", operand_sign), Sym("b", tr, "v", operand_sign))
     if isinstance(res, Sym):
         code = res.code if res.kind == "v" else f"({res.code} ? 1 : 0)"
     else:
@@ -139,8 +179,11 @@ def _run(functor, forced):
     return code, tr.taken
 
 
-def trace_functor(functor) -> str:
-    """C++ expression over ``a`` and ``b`` equivalent to ``functor(a, b)``."""
+def trace_functor(functor, dtype=None) -> str:
+    """C++ expression over ``a`` and ``b`` equivalent to ``functor(a, b)`` for items of
+    ``dtype`` (its kind decides how integers widen; None = signed)."""
+    kind = np.dtype(dtype).kind if dtype is not None else "i"
+    operand_sign = {"u": "u", "f": None}.get(kind, "s")
     paths = [0]
 
     def explore(forced):
@@ -148,7 +191,7 @@ def trace_functor(functor) -> str:
         if paths[0] > _MAX_PATHS:
             raise NotImplementedError("reduce functor has too many data-dependent branches")
         try:
-            code, taken = _run(functor, forced)
+            code, taken = _run(functor, forced, operand_sign)
         except NotImplementedError:
             raise
         except Exception as exc:

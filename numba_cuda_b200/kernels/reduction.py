@@ -5,13 +5,13 @@ Same call surface as numba/cuda/kernels/reduction.py:169-265:
 ``Reduce(functor)(arr, size=None, res=None, init=0, stream=0)``.
 
 The reference JIT-compiles the Python functor into its kernel.  Here the
-functor is first *classified* into the table of ops the precompiled kernels
-carry (add, mul, max, min, and, or, xor): it is evaluated on a fixed set of
-sample pairs and must agree with exactly one table op on all of them.  Any other
-functor is traced into a C++ expression (``_trace.py``) and the reduce kernel is
-compiled around it at run time with NVRTC (``b2k_reduce_expr``).  A functor that
-cannot be traced raises ``NotImplementedError`` -- nothing is ever computed on
-the CPU instead.
+functor is traced into a C++ expression (``_trace.py``).  When that expression is
+one of the plain forms of the ops the precompiled kernels carry (add, mul, max,
+min, and, or, xor) and the functor also agrees with that op on a fixed set of
+sample pairs, the precompiled kernel runs.  Any other traceable functor has the
+reduce kernel compiled around its expression at run time with NVRTC
+(``b2k_reduce_expr``).  A functor that cannot be traced raises
+``NotImplementedError`` -- nothing is ever computed on the CPU instead.
 """
 from __future__ import annotations
 
@@ -95,12 +95,36 @@ def classify_functor(functor, dtype) -> int:
         "(a+b, a*b, max(a,b), min(a,b), a&b, a|b, a^b)")
 
 
+def _canonical_forms():
+    """The expressions the tracer produces for the table ops themselves."""
+    forms = {code: set() for _, code, _ in _OP_TABLE}
+    for sym, code in (("+", _lib.ADD), ("*", _lib.MUL), ("&", _lib.AND), ("|", _lib.OR), ("^", _lib.XOR)):
+        forms[code] |= {f"(a {sym} b)", f"(b {sym} a)"}
+    picks_a = ["(a > b)", "(a >= b)", "(b < a)", "(b <= a)"]      # true when a is the larger
+    picks_b = ["(b > a)", "(b >= a)", "(a < b)", "(a <= b)"]
+    for cond in picks_a:
+        forms[_lib.MAX].add(f"({cond} ? a : b)")
+        forms[_lib.MIN].add(f"({cond} ? b : a)")
+    for cond in picks_b:
+        forms[_lib.MAX].add(f"({cond} ? b : a)")
+        forms[_lib.MIN].add(f"({cond} ? a : b)")
+    return forms
+
+
+_CANONICAL = _canonical_forms()
+
+
 class _Scratch:
-    """Per-(device, stream) scratch: ticket + partials for the kernel, and one
-    result slot.  Zero-filled once; the kernel leaves it reusable."""
+    """Kernel scratch (ticket + partials) per (device, stream): zero-filled once, the
+    kernel leaves it reusable, and calls on one stream are ordered, so every host
+    thread may share it.  The result slot and its page-locked landing buffer are
+    per (device, stream, host thread): two threads reducing on one stream must not
+    read each other's result (the reference allocates fresh partials per call,
+    reduction.py:236-241)."""
 
     _lock = threading.Lock()
     _pool: dict = {}
+    _local = threading.local()
 
     @classmethod
     def get(cls, stream):
@@ -111,10 +135,16 @@ class _Scratch:
                 nbytes = int(_lib.lib().b2k_reduce_scratch_bytes())
                 with torch.cuda.stream(_torch_stream(stream)):
                     scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
-                    result = torch.zeros(16, dtype=torch.uint8, device="cuda")
-                entry = (scratch, result, nbytes, torch.zeros(16, dtype=torch.uint8, pin_memory=True))
+                entry = (scratch, nbytes)
                 cls._pool[key] = entry
-            return entry
+        mine = cls._local.__dict__.setdefault("slots", {})
+        own = mine.get(key)
+        if own is None:
+            with torch.cuda.stream(_torch_stream(stream)):
+                own = (torch.zeros(16, dtype=torch.uint8, device="cuda"),
+                       torch.zeros(16, dtype=torch.uint8, pin_memory=True))
+            mine[key] = own
+        return entry[0], own[0], entry[1], own[1]
 
 
 class Reduce:
@@ -135,26 +165,34 @@ class Reduce:
         op = self._cache.get(key)
         if op is None:
             from ._trace import trace_functor
+            if np.dtype(dtype) not in _DTYPE_CODES:
+                raise NotImplementedError(f"cuda.reduce: dtype {np.dtype(dtype)} has no kernel")
             try:
-                op = classify_functor(self._functor, dtype)
+                expr = trace_functor(self._functor, dtype)
             except NotImplementedError:
-                if np.dtype(dtype) not in _DTYPE_CODES:
-                    raise
-                op = trace_functor(self._functor)
+                expr = None
+            try:
+                table = classify_functor(self._functor, dtype)
+            except NotImplementedError:
+                table = None
+            if table is not None and expr in _CANONICAL[table]:
+                # the samples AND the function's own structure say it is this op
+                op = table
+            elif expr is not None:
+                # anything else that can be followed runs as what it is (a function that
+                # only looks like a table op on the samples -- a cap, a modulus, a
+                # threshold -- included)
+                op = expr
             else:
-                # The probe only sees moderate magnitudes.  A functor that carries any
-                # constant (a cap, a modulus, a threshold) is never a pure table op, so
-                # it takes the traced path even when it agreed on every sample.
-                try:
-                    expr = trace_functor(self._functor)
-                except NotImplementedError:
-                    expr = None
-                if expr is not None and any(ch.isdigit() for ch in expr):
-                    op = expr
+                # Not followable (math.*, float(), NumPy calls ...): agreeing with a table
+                # op on the samples proves nothing about the values not sampled.
+                raise NotImplementedError(
+                    "cuda.reduce: the binary function can be neither traced nor identified as one of "
+                    "a+b, a*b, max(a,b), min(a,b), a&b, a|b, a^b")
             self._cache[key] = op
         return op
 
-    def __call__(self, arr, size=None, res=None, init=0, stream=0):
+    def __call__(self, arr, size=None, res=None, init=0, stream=0, _fold_init=True):
         """Performs a full reduction.
 
         :param arr: A host or device array (1-D).
@@ -191,8 +229,10 @@ class Reduce:
 
         init_host = np.array([init], dtype=arr.dtype)
         if isinstance(op, str):
+            # a traced function has no identity; the sharded wrapper asks for the bare fold
             _lib.check(_lib.lib().b2k_reduce_expr(
-                op.encode(), _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
+                op.encode(), _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size,
+                init_host.ctypes.data if _fold_init else None,
                 out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
         else:
             _lib.check(_lib.lib().b2k_reduce(
@@ -298,12 +338,23 @@ class Reduce:
         elif outer == 1:
             self.along_axis(darr._sub((length, inner), (inner * item, item), 0), 0, res=flat, init=init, stream=stream)
         else:
-            if outer > 4096:
-                raise NotImplementedError("more than 4096 outer slabs: permute the reduced axis to the front first")
+            # every outer slab is a (length x inner) matrix reduced along its rows: one launch
+            # over the batch of slabs (65535 per launch)
+            op = self._compile(dtype)
+            if isinstance(op, str):
+                raise NotImplementedError("axis-wise reduction supports the precompiled table ops only")
+            L = _lib.lib()
+            code = _DTYPE_CODES[dtype]
             slab = length * inner * item
-            for o in range(outer):
-                self.along_axis(darr._sub((length, inner), (inner * item, item), o * slab), 0,
-                                res=flat._sub((inner,), (item,), o * inner * item), init=init, stream=stream)
+            init_host = np.array([init], dtype=dtype)
+            for first in range(0, outer, 65535):
+                count = min(65535, outer - first)
+                need = int(L.b2k_reduce_cols_batched_scratch_bytes(count, length, inner, code))
+                scratch = _AxisScratch.get(stream, need)
+                _lib.check(L.b2k_reduce_cols_batched(
+                    op, code, darr._ptr + first * slab, count, length, inner, inner * item, slab,
+                    init_host.ctypes.data, flat._ptr + first * inner * item,
+                    scratch.data_ptr() if need else None, need, stream_ptr(stream)))
         return dres
 
 

@@ -3,11 +3,13 @@
 The reference has no distributed layer; this module is the new part of the
 drop-in.  Reduce, RNG and casts partition by contiguous index range:
 
-* reduce: every rank folds its shard with the single-launch kernel, then ONE
-  collective on a one-element buffer combines the partials -- ``all_reduce``
-  (sum / product / max / min) where the backend carries the dtype, else an
-  ``all_gather`` of the G partials folded locally.  ``init`` is folded in once,
-  after the collective;
+* reduce: every rank folds its shard with the single-launch kernel; the partials
+  are combined either inside that kernel over NVLink peer memory
+  (``PeerMailboxes``) or by ONE collective on a one-element buffer --
+  ``all_reduce`` (sum / product / max / min) where the backend carries the dtype,
+  else an ``all_gather`` of the G partials folded locally; for a traced user
+  function the gathered partials are folded on the device by the same run-time
+  compiled kernel.  ``init`` is folded in once, after the combine;
 * RNG: rank k creates states ``[lo_k, hi_k)`` with
   ``subsequence_start + lo_k``, so the concatenation over ranks equals the
   single-GPU array, and fills only its rows -- no exchange;
@@ -36,6 +38,17 @@ def shard_bounds(n: int, world_size: int, rank: int, align: int = 1):
     lo = rank * base
     hi = n if rank == world_size - 1 else lo + base
     return lo, hi
+
+
+def _on_stream(tensor: torch.Tensor, stream):
+    """Context in which torch orders work on ``tensor`` behind ``stream``: the
+    collectives and copies of this module must follow the kernel that was launched
+    on the caller's stream, and torch orders them against ITS current stream."""
+    import contextlib
+    if not tensor.is_cuda:
+        return contextlib.nullcontext()
+    from .devicearray import _torch_stream
+    return torch.cuda.stream(_torch_stream(stream))
 
 
 def _world(group=None):
@@ -91,26 +104,25 @@ _NATIVE_ALLREDUCE_DTYPES = {np.dtype(np.int32): torch.int32, np.dtype(np.int64):
                             np.dtype(np.int8): torch.int8, np.dtype(np.uint8): torch.uint8}
 
 
-def combine_partials(partial: torch.Tensor, op: int, dtype, group=None) -> torch.Tensor:
+def combine_partials(partial: torch.Tensor, op: int, dtype, group=None, stream=0) -> torch.Tensor:
     """Combine one-element per-rank partials (raw ``uint8`` bytes of ``dtype``,
     on whatever device the process group works with) into the same buffer on
-    every rank.  One collective call."""
+    every rank.  One collective call, ordered behind ``stream``."""
     dist, world, _ = _world(group)
     dtype = np.dtype(dtype)
     if world == 1:
         return partial
-    if op in (_lib.ADD, _lib.MUL, _lib.MAX, _lib.MIN) and dtype in _NATIVE_ALLREDUCE_DTYPES:
-        typed = partial.view(_NATIVE_ALLREDUCE_DTYPES[dtype])
-        red = {_lib.ADD: dist.ReduceOp.SUM, _lib.MUL: dist.ReduceOp.PRODUCT,
-               _lib.MAX: dist.ReduceOp.MAX, _lib.MIN: dist.ReduceOp.MIN}[op]
-        dist.all_reduce(typed, op=red, group=group)
-        return partial
-    gathered = torch.empty(world * partial.numel(), dtype=torch.uint8, device=partial.device)
-    dist.all_gather_into_tensor(gathered, partial, group=group) if partial.is_cuda else \
-        dist.all_gather(list(gathered.view(world, -1).unbind(0)), partial, group=group)
-    host = gathered.cpu().numpy().view(dtype)
-    folded = host_fold(op, host, op_identity(op, dtype))
-    partial.copy_(torch.from_numpy(np.array([folded], dtype=dtype).view(np.uint8)))
+    with _on_stream(partial, stream):
+        if op in (_lib.ADD, _lib.MUL, _lib.MAX, _lib.MIN) and dtype in _NATIVE_ALLREDUCE_DTYPES:
+            typed = partial.view(_NATIVE_ALLREDUCE_DTYPES[dtype])
+            red = {_lib.ADD: dist.ReduceOp.SUM, _lib.MUL: dist.ReduceOp.PRODUCT,
+                   _lib.MAX: dist.ReduceOp.MAX, _lib.MIN: dist.ReduceOp.MIN}[op]
+            dist.all_reduce(typed, op=red, group=group)
+            return partial
+        gathered = gather_partial_rows(partial, group=group, stream=stream)
+        host = gathered.cpu().numpy().reshape(-1).view(dtype)
+        folded = host_fold(op, host, op_identity(op, dtype))
+        partial.copy_(torch.from_numpy(np.array([folded], dtype=dtype).view(np.uint8)))
     return partial
 
 
@@ -120,7 +132,13 @@ class PeerMailboxes:
     peer's, exchanged as IPC handles over the process group at construction.
     All ranks of the group must construct it together and must then call
     ``reduce`` in the same order (the call counter is the epoch the kernels
-    match on).  Single node, at most ``b2k_peer_max_world()`` ranks."""
+    match on).  Single node, at most ``b2k_peer_max_world()`` ranks.
+
+    A rank whose wait runs out (``timeout_s``; a peer delayed by a long copy, by
+    first-call module loading, or gone) writes only ``init`` and reports it through
+    ``check``, while ranks whose waits succeeded hold the real result: after a
+    timeout the ranks DISAGREE.  ``check(agree=True)`` makes the decision common
+    (one small all-reduce of the status over the process group)."""
 
     def __init__(self, group=None, world_size=None, rank=None, timeout_s: float = 2.0):
         import ctypes
@@ -153,23 +171,59 @@ class PeerMailboxes:
                 self._opened.append(peer.value)
             dist.barrier(group=group)
         self._ptrs = (ctypes.c_void_p * world)(*ptrs)
-        self._status = torch.zeros(1, dtype=torch.int32, device="cuda")
-        self._scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+        # [0] timed-out flag, [1] local fold done (ns), [2] all peers seen (ns)
+        self._status = torch.zeros(3, dtype=torch.int64, device="cuda")
+        self._scratch = {}           # per stream: overlapping reductions must not share a ticket
 
-    def reduce(self, op, dtype_code, x_ptr, n, init_host, out_ptr, stream=0):
-        """One collective call: launches the fused kernel on this rank."""
+    def _scratch_for(self, sptr: int) -> torch.Tensor:
+        buf = self._scratch.get(sptr)
+        if buf is None:
+            buf = torch.zeros(int(_lib.lib().b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+            torch.cuda.current_stream().synchronize()      # zero-filled before any stream uses it
+            self._scratch[sptr] = buf
+        return buf
+
+    @staticmethod
+    def _next_epoch(epoch: int) -> int:
+        epoch += 1
+        if epoch & 0xFFFFFFFF == 0:      # the kernels compare the low 32 bits, and 0 means "never written"
+            epoch += 1
+        return epoch
+
+    def reduce(self, op, dtype_code, x_ptr, n, init_host, out_ptr, stream=0, input_ready=False):
+        """One collective call: launches the fused kernel on this rank.  The epoch
+        advances only when the launch was accepted, so an argument error on one rank
+        does not put it out of step with the others."""
         from .devicearray import stream_ptr
-        self.epoch += 1
+        sptr = stream_ptr(stream)
+        scratch = self._scratch_for(sptr)
+        epoch = self._next_epoch(self.epoch)
         _lib.check(_lib.lib().b2k_reduce_peer(
-            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, self._scratch.data_ptr(),
-            self._scratch.numel(), self._ptrs, self.world, self.rank, self.epoch, self.timeout_ns,
-            self._status.data_ptr(), stream_ptr(stream)))
+            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, scratch.data_ptr(),
+            scratch.numel(), self._ptrs, self.world, self.rank, epoch, self.timeout_ns,
+            self._status.data_ptr(), _lib.REDUCE_INPUT_READY if input_ready else 0, sptr))
+        self.epoch = epoch
 
-    def check(self):
-        """Raise if any earlier call gave up waiting for a peer (synchronises)."""
-        if int(self._status.item()) != 0:
-            self._status.zero_()
-            raise RuntimeError("a peer's partial result did not arrive within the time limit")
+    def exchange_ns(self) -> int:
+        """What the exchange of the most recent call cost this rank, from the GPU's
+        nanosecond timer: local fold complete -> last peer value seen (launch skew
+        between the ranks included).  Synchronises."""
+        s = self._status.cpu()
+        return int(s[2] - s[1])
+
+    def check(self, agree: bool = False):
+        """Raise if any earlier call on this rank gave up waiting for a peer
+        (synchronises).  With ``agree=True`` the ranks first take the maximum of
+        their flags over the process group, so that either all raise or none."""
+        flag = self._status[:1].clone()
+        if agree and self.world > 1:
+            dist, _, _ = _world(self.group)
+            if dist is not None:
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+        if int(flag.item()) != 0:
+            self._status[:1].zero_()
+            raise RuntimeError("a peer's partial result did not arrive within the time limit; "
+                               "the ranks may hold different results for that call")
 
     def close(self):
         L = _lib.lib()
@@ -188,7 +242,10 @@ class ShardedReduce:
 
     With ``peer=PeerMailboxes(...)`` the combine happens inside the reduce kernel
     over NVLink peer memory (one launch per rank, no library collective);
-    without it, one NCCL collective on a one-element buffer follows the kernel."""
+    without it, one NCCL collective on a one-element buffer follows the kernel.
+    A user function outside the precompiled table (a traced expression) always
+    takes the collective route: one all-gather of the partials, which the same
+    run-time compiled kernel then folds on the device."""
 
     def __init__(self, functor, peer: "PeerMailboxes | None" = None):
         self._functor = functor
@@ -199,10 +256,10 @@ class ShardedReduce:
         from .api import auto_device, device_array
         from .kernels.reduction import _DTYPE_CODES
         dtype = np.dtype(local_arr.dtype)
+        op = self._local._compile(dtype)
+        if isinstance(op, str):
+            return self._traced(local_arr, dtype, init, stream, group)
         if self._peer is not None:
-            op = self._local._compile(dtype)
-            if isinstance(op, str):
-                raise NotImplementedError("the fused cross-GPU combine supports the precompiled table ops only")
             darr, _ = auto_device(local_arr, stream=stream)
             slot = device_array(1, dtype=dtype, stream=stream)
             init_host = np.array([init], dtype=dtype)
@@ -210,31 +267,70 @@ class ShardedReduce:
             result = slot.copy_to_host()[0]
             self._peer.check()
             return result
-        op = self._local._compile(dtype)
-        if isinstance(op, str):
-            raise NotImplementedError("sharded reduce supports the precompiled table ops only")
         ident = op_identity(op, dtype)
         slot = device_array(1, dtype=dtype, stream=stream)
         if local_arr.size:
             self._local(local_arr, res=slot, init=ident, stream=stream)
         else:
             slot.copy_to_device(np.array([ident], dtype=dtype), stream=stream)
-        combined = combine_partials(slot._bytes_view(), op, dtype, group=group)
-        host = combined.cpu().numpy().view(dtype)
+        combined = combine_partials(slot._bytes_view(), op, dtype, group=group, stream=stream)
+        with _on_stream(combined, stream):
+            host = combined.cpu().numpy().view(dtype)
         return host_fold(op, host, dtype.type(init))
 
+    def _traced(self, local_arr, dtype, init, stream, group):
+        """A user function with no identity element: every rank with a non-empty shard
+        contributes its partial (no ``init`` in it) plus a presence mark; after one
+        all-gather the partials that are there are folded, with ``init``, by the same
+        kernel that folded the shards."""
+        from .api import device_array
+        record = device_array(16, dtype=np.uint8, stream=stream)          # [value | present]
+        mark = np.zeros(16, dtype=np.uint8)
+        if local_arr.size:
+            mark[8] = 1
+            record.copy_to_device(mark, stream=stream)
+            self._local(local_arr, res=record.view(dtype)[:1], stream=stream, _fold_init=False)
+        else:
+            record.copy_to_device(mark, stream=stream)
+        rows = gather_partial_rows(record._bytes_view(), group=group, stream=stream)
+        return fold_gathered(rows, dtype, init, lambda values: self._local(values, init=init, stream=stream),
+                             stream=stream)
 
-def gather_partial_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
+
+def fold_gathered(rows: torch.Tensor, dtype, init, fold, stream=0):
+    """``rows`` is the ``[world, 16]`` stack of per-rank records ``[value | present]``.
+    The values that are present go, in rank order, to ``fold`` (a callable that
+    reduces a 1-D array of ``dtype`` with the user's function and ``init``); with
+    none present the result is ``init``."""
+    from .devicearray import DeviceNDArray
+    dtype = np.dtype(dtype)
+    with _on_stream(rows, stream):
+        present = rows[:, 8].cpu().numpy() != 0
+        if not present.any():
+            return dtype.type(init)
+        keep = torch.from_numpy(np.flatnonzero(present)).to(rows.device)
+        values = rows[:, :dtype.itemsize].index_select(0, keep).contiguous().reshape(-1)
+    if values.is_cuda:
+        count = int(present.sum())
+        values = DeviceNDArray((count,), (dtype.itemsize,), dtype, stream=stream, gpu_data=(values, 0))
+    else:
+        values = values.numpy().view(dtype)
+    return fold(values)
+
+
+def gather_partial_rows(partial: torch.Tensor, group=None, stream=0) -> torch.Tensor:
     """All ranks' partial result rows (raw ``uint8`` bytes, same length on every
-    rank) stacked into a ``[world, nbytes]`` tensor on every rank: ONE collective."""
+    rank) stacked into a ``[world, nbytes]`` tensor on every rank: ONE collective,
+    ordered behind ``stream``."""
     dist, world, _ = _world(group)
     if world == 1:
         return partial.reshape(1, -1)
-    stacked = torch.empty(world * partial.numel(), dtype=torch.uint8, device=partial.device)
-    if partial.is_cuda:
-        dist.all_gather_into_tensor(stacked, partial.contiguous(), group=group)
-    else:
-        dist.all_gather(list(stacked.view(world, -1).unbind(0)), partial.contiguous(), group=group)
+    with _on_stream(partial, stream):
+        stacked = torch.empty(world * partial.numel(), dtype=torch.uint8, device=partial.device)
+        if partial.is_cuda:
+            dist.all_gather_into_tensor(stacked, partial.contiguous(), group=group)
+        else:
+            dist.all_gather(list(stacked.view(world, -1).unbind(0)), partial.contiguous(), group=group)
     return stacked.view(world, -1)
 
 
@@ -260,7 +356,7 @@ class ShardedReduceAxis:
             return self._local.along_axis(local_rows, 1, init=init, stream=stream)
         darr, _ = auto_device(local_rows, stream=stream)
         partial = self._local.along_axis(darr, 0, init=op_identity(op, dtype), stream=stream)
-        stacked = gather_partial_rows(partial._bytes_view(), group=group)
+        stacked = gather_partial_rows(partial._bytes_view(), group=group, stream=stream)
         world, cols = stacked.shape[0], partial.shape[0]
         rows = DeviceNDArray((world, cols), _c_strides((world, cols), dtype.itemsize), dtype, stream=stream,
                              gpu_data=(stacked.view(-1), 0))
@@ -292,5 +388,5 @@ def sharded_cast(src_local, src_format, dst_format, out=None, saturate=1, stream
     return cast(src_local, src_format, dst_format, out=out, saturate=saturate, stream=stream)
 
 
-__all__ = ["PeerMailboxes", "ShardedReduceAxis", "gather_partial_rows", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
+__all__ = ["PeerMailboxes", "ShardedReduceAxis", "gather_partial_rows", "fold_gathered", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
            "create_sharded_xoroshiro128p_states", "sharded_cast", "op_name"]

@@ -1,0 +1,133 @@
+"""The benchmark configurations at their FULL sizes against the CPU oracle:
+
+* configuration 3: 32768 x 32768 float32 and 16384 x 65536 bfloat16 transposes of the
+  seeded NumPy inputs, every item compared with NumPy ``.T``;
+* configuration 4: 2^24 generators (seed 42), 64 uniform float32 + 16 normal float64
+  each -- states after creation, every uniform and the final states bit for bit against
+  the serial CPU restatement of the reference, normals within the libm/libdevice
+  tolerance (their bit parity is pinned by the GPU-generated fixture elsewhere);
+* configuration 5: all 2^30 values of the chunked ``default_rng(3)`` input -- e4m3, e5m2
+  and bf16 codes bit for bit against the reference's own header code, decodes checked
+  on the codes.
+
+Host work dominates (drawing 2^30 normals takes NumPy the better part of a minute), so
+each test keeps its host arrays bounded and compares slab by slab."""
+import numpy as np
+import pytest
+import torch
+
+import config_inputs
+import oracle
+import numba_cuda_b200 as cuda
+from numba_cuda_b200.casts import cast
+from numba_cuda_b200.kernels.transpose import transpose
+from numba_cuda_b200.random import create_xoroshiro128p_states, xoroshiro128p_fill
+
+pytestmark = pytest.mark.gpu
+
+
+def _need(gigabytes):
+    free, _ = torch.cuda.mem_get_info()
+    if free < gigabytes * (1 << 30):
+        pytest.skip(f"needs {gigabytes} GiB of free device memory")
+
+
+@pytest.fixture(scope="module")
+def normals_2p30():
+    """The first 2^30 float32 normals of default_rng(2): configuration 3a uses them as
+    a 32768 x 32768 matrix, 3b (rounded to bfloat16) as 16384 x 65536."""
+    return config_inputs.c3_normals(32768, 32768)
+
+
+def _compare_with_numpy_T(dev_out, host_in_bits, block):
+    """dev_out[j, i] == host_in[i, j] for every item, in slabs of `block` output rows."""
+    rows, cols = host_in_bits.shape
+    assert dev_out.shape == (cols, rows)
+    for j0 in range(0, cols, block):
+        got = dev_out[j0:j0 + block].copy_to_host().view(host_in_bits.dtype)
+        want = host_in_bits[:, j0:j0 + block].T          # NumPy .T is the authority
+        assert np.array_equal(got, want), f"output rows {j0}..{j0 + block}"
+
+
+def test_config3a_float32_32768_square_vs_numpy(normals_2p30):
+    _need(10)
+    a = normals_2p30
+    out = transpose(cuda.to_device(a))
+    assert out.shape == (32768, 32768) and out.dtype == np.float32
+    assert out.strides == (4 * 32768, 4)
+    _compare_with_numpy_T(out, a.view(np.uint32), 2048)
+
+
+def test_config3b_bfloat16_16384x65536_vs_numpy(normals_2p30):
+    _need(6)
+    f = normals_2p30.reshape(16384, 65536)
+    # bit patterns of the float32 values rounded to nearest even
+    bits = oracle.ref_cast(f, oracle.F32, oracle.BF16) if oracle.have_ref_headers() else \
+        oracle.cast(f, oracle.F32, oracle.BF16)
+    assert bits.shape == (16384, 65536) and bits.dtype == np.uint16
+    d = cuda.to_device(bits).view(cuda.bf16.bfloat16_dtype())
+    out = transpose(d)
+    assert out.shape == (65536, 16384) and out.dtype.itemsize == 2
+    _compare_with_numpy_T(out.view(np.uint16), bits, 8192)
+
+
+def test_config4_2p24_generators_vs_oracle():
+    _need(8)
+    n, seed = 1 << 24, 42
+    states = create_xoroshiro128p_states(n, seed=seed, subsequence_start=0)
+    host = oracle.init_states(n, seed, 0)                 # the serial chain of random.py:242-257
+    got = states.copy_to_host()
+    assert got.tobytes() == host.tobytes()
+    # the survey's known answers for seed 42
+    assert int(got[0]["s0"]) == int(got[0]["s1"]) == 0xBDD732262FEB6E95
+    assert (int(got[1]["s0"]), int(got[1]["s1"])) == (313611670190079035, 410834281257317300)
+    assert (int(got[(1 << 20) - 1]["s0"]), int(got[(1 << 20) - 1]["s1"])) == \
+        (3414912191147488299, 14710813771771363680)
+    del got
+
+    u, z = xoroshiro128p_fill(states, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+    slab = 1 << 21
+    worst = 0.0
+    for lo in range(0, n, slab):
+        st = host[lo:lo + slab]                            # advanced in place by the oracle
+        want_u = oracle.fill(st, "uniform", np.float32, 64, threads=0)
+        assert u[lo:lo + slab].copy_to_host().tobytes() == want_u.tobytes(), f"uniforms of generators {lo}.."
+        want_z = oracle.fill(st, "normal", np.float64, 16, threads=0)
+        got_z = z[lo:lo + slab].copy_to_host()
+        # log is taken in float32 on both sides (libdevice here, libm there)
+        np.testing.assert_allclose(got_z, want_z, rtol=2e-6, atol=2e-6)
+        worst = max(worst, float(np.abs(got_z - want_z).max()))
+    assert states.copy_to_host().tobytes() == host.tobytes()      # 96 steps on, every generator
+    assert worst < 1e-5
+
+
+def test_config5_2p30_values_vs_reference_headers():
+    _need(12)
+    if not oracle.have_ref_headers():
+        pytest.skip("the reference-header checker is not built")
+    n, chunk = config_inputs.C5_CHUNK * config_inputs.C5_CHUNKS, config_inputs.C5_CHUNK
+    x = cuda.device_array(n, dtype=np.float32)
+    want = {"e4m3": np.empty(n, np.uint8), "e5m2": np.empty(n, np.uint8), "bf16": np.empty(n, np.uint16)}
+    fmt = {"e4m3": oracle.E4M3, "e5m2": oracle.E5M2, "bf16": oracle.BF16}
+    specials = 0
+    for k, xc in config_inputs.c5_chunks():
+        x[k * chunk:(k + 1) * chunk].copy_to_device(xc)
+        for name, code in fmt.items():
+            want[name][k * chunk:(k + 1) * chunk] = oracle.ref_cast(xc, oracle.F32, code, 1, threads=0)
+        specials += int((~np.isfinite(xc)).sum()) + int((np.abs(xc) == 1e6).sum())
+    assert abs(specials / n - 0.01) < 1e-4                # about 1 % of the positions
+
+    for name, code in fmt.items():
+        codes = cast(x, "f32", name)                       # one launch over all 2^30 values
+        back = cast(codes, name, "f32")
+        for k in range(config_inputs.C5_CHUNKS):
+            sl = slice(k * chunk, (k + 1) * chunk)
+            got = codes[sl].copy_to_host().view(want[name].dtype)
+            assert got.tobytes() == want[name][sl].tobytes(), f"{name} codes of chunk {k}"
+            want_back = oracle.ref_cast(want[name][sl], code, oracle.F32, threads=0)
+            got_back = back[sl].copy_to_host()
+            nan = np.isnan(want_back)                      # NaN payloads: header host path vs cvt
+            assert np.array_equal(np.isnan(got_back), nan)
+            assert np.array_equal(got_back.view(np.uint32)[~nan], want_back.view(np.uint32)[~nan]), \
+                f"{name} decode of chunk {k}"
+        del codes, back

@@ -208,3 +208,49 @@ def test_basic_indexing_matches_numpy_views():
         _basic_index((3, 4), (16, 4), (0, 0, 0))
     with pytest.raises(IndexError):
         _basic_index((3, 4), (16, 4), (Ellipsis, Ellipsis))
+
+
+def test_table_ops_are_recognised_in_every_usual_spelling():
+    import operator
+    spellings = {
+        _lib.ADD: [lambda a, b: a + b, lambda a, b: b + a, operator.add],
+        _lib.MUL: [lambda a, b: a * b, operator.mul],
+        _lib.MAX: [lambda a, b: max(a, b), max, lambda a, b: a if a > b else b, lambda a, b: b if a < b else a,
+                   lambda a, b: a if a >= b else b],
+        _lib.MIN: [lambda a, b: min(a, b), min, lambda a, b: a if a < b else b, lambda a, b: b if b <= a else a],
+        _lib.AND: [lambda a, b: a & b, operator.and_],
+        _lib.OR: [lambda a, b: a | b],
+        _lib.XOR: [lambda a, b: a ^ b, operator.xor],
+    }
+    for code, fns in spellings.items():
+        for fn in fns:
+            for dt in (np.int8, np.uint16, np.int32, np.uint64) + (() if code >= _lib.AND else (np.float32, np.float64)):
+                assert Reduce(fn)._compile(np.dtype(dt)) == code, (code, dt)
+
+
+def test_a_look_alike_that_cannot_be_traced_is_refused():
+    LIMIT = 10 ** 9
+
+    def looks_like_add(a, b):
+        return float(min(a + b, LIMIT))       # equals a+b on every probe sample
+
+    assert classify_functor(lambda a, b: min(a + b, LIMIT), np.float64) == _lib.ADD
+    with pytest.raises(NotImplementedError):
+        Reduce(looks_like_add)._compile(np.dtype(np.float64))
+    # the traceable form of the same function runs as what it is
+    op = Reduce(lambda a, b: min(a + b, LIMIT))._compile(np.dtype(np.int64))
+    assert isinstance(op, str) and "1000000000" in op
+
+
+def test_unsigned_items_widen_to_uint64_and_mix_as_int64():
+    from numba_cuda_b200.kernels._trace import trace_functor
+    # uint - uint stays unsigned (wraps), and is compared with the signed literal as a number
+    assert trace_functor(lambda a, b: a if a - b > 0 else b, np.uint32) == \
+        "(b2k_lt(B2K_ILIT(0LL), (a - b)) ? a : b)"
+    # signed items: plain comparison
+    assert trace_functor(lambda a, b: a if a - b > 0 else b, np.int32) == "(((a - b) > B2K_ILIT(0LL)) ? a : b)"
+    # unsigned with a signed constant: the operation is done in int64
+    assert trace_functor(lambda a, b: (a + b) % 7, np.uint8) == "b2k_mod(((long long)(a + b)), ((long long)B2K_ILIT(7LL)))"
+    assert trace_functor(lambda a, b: -a + b, np.uint16) == "(((long long)(-(long long)a)) + ((long long)b))"
+    # floats are untouched by the integer rule
+    assert trace_functor(lambda a, b: a + b * 2, np.float32) == "(a + (b * B2K_ILIT(2LL)))"

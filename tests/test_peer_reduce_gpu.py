@@ -3,8 +3,9 @@
 On one GPU the exchange is exercised without ever making a kernel wait for
 another launch: a peer's mailbox is a second local buffer and the peer's value
 is written into this rank's mailbox *before* the kernel starts.  The give-up path
-is checked by letting a short wait run out on a flag that nothing sets (the
-kernel records a status and returns; the context stays usable).  With two or
+is checked by letting a short wait run out on a word that nothing writes (the
+kernel records a status and returns; the context stays usable).  A value travels
+as 64-bit words {low 32 bits of the epoch | 32 bits of payload}.  With two or
 more GPUs, real ranks in separate processes run the fused path end to end."""
 import ctypes
 import os
@@ -40,11 +41,36 @@ class Mailbox:
         _lib.lib().b2k_peer_mailbox_destroy(self.ptr)
 
 
-def call_peer(op, code, x, init, boxes, world, rank, epoch, timeout_ns, status, scratch, out):
+def new_status():
+    return torch.zeros(3, dtype=torch.int64, device="cuda")
+
+
+def deliver(box, epoch, writer, bits):
+    """What rank `writer`'s kernel stores into `box` for call `epoch`."""
+    s = box.slot(epoch, writer)
+    tag = (epoch & 0xFFFFFFFF) << 32
+    for k, part in enumerate((bits & 0xFFFFFFFF, (bits >> 32) & 0xFFFFFFFF)):
+        word = tag | part
+        box.words[s + k] = word - (1 << 64) if word >= (1 << 63) else word
+
+
+def delivered(box, epoch, writer, itemsize):
+    s = box.slot(epoch, writer)
+    w0 = int(box.words[s].item()) & (2 ** 64 - 1)
+    assert w0 >> 32 == epoch & 0xFFFFFFFF
+    bits = w0 & 0xFFFFFFFF
+    if itemsize > 4:
+        w1 = int(box.words[s + 1].item()) & (2 ** 64 - 1)
+        assert w1 >> 32 == epoch & 0xFFFFFFFF
+        bits |= (w1 & 0xFFFFFFFF) << 32
+    return bits
+
+
+def call_peer(op, code, x, init, boxes, world, rank, epoch, timeout_ns, status, scratch, out, flags=0):
     L = _lib.lib()
     ptrs = (ctypes.c_void_p * world)(*[b.ptr for b in boxes])
     rc = L.b2k_reduce_peer(op, code, x.data_ptr(), x.numel(), init.ctypes.data, out.data_ptr(), scratch.data_ptr(),
-                           scratch.numel(), ptrs, world, rank, epoch, timeout_ns, status.data_ptr(),
+                           scratch.numel(), ptrs, world, rank, epoch, timeout_ns, status.data_ptr(), flags,
                            torch.cuda.current_stream().cuda_stream)
     assert rc == 0, L.b2k_last_error()
 
@@ -53,13 +79,15 @@ def test_world_of_one_equals_plain_reduce():
     L = _lib.lib()
     box = Mailbox()
     scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = new_status()
     x = torch.randint(-2 ** 31, 2 ** 31 - 1, (1 << 20,), dtype=torch.int32, device="cuda")
     out = torch.zeros(1, dtype=torch.int32, device="cuda")
     init = np.array([-5], dtype=np.int32)
-    for epoch in (1, 2, 3):
-        call_peer(_lib.MAX, _lib.I32, x, init, [box], 1, 0, epoch, 0, status, scratch, out)
-        assert out.item() == max(int(x.max().item()), -5) and status.item() == 0
+    for epoch in (1, 2, 3, (1 << 32) + 1):
+        for flags in (0, _lib.REDUCE_INPUT_READY):
+            call_peer(_lib.MAX, _lib.I32, x, init, [box], 1, 0, epoch, 0, status, scratch, out, flags)
+            assert out.item() == max(int(x.max().item()), -5) and status[0].item() == 0
+            assert 0 <= (status[2] - status[1]).item() < 1_000_000     # both stamps written, microseconds apart
     box.close()
 
 
@@ -71,7 +99,7 @@ def test_fold_with_a_value_that_already_arrived(op, code, tdt, name):
     L = _lib.lib()
     mine, theirs = Mailbox(), Mailbox()         # rank 0's mailbox, and a stand-in for rank 1's memory
     scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = new_status()
     ndt = np.dtype(str(tdt).replace("torch.", ""))
     if tdt.is_floating_point:
         x = torch.rand(100003, dtype=tdt, device="cuda")
@@ -82,11 +110,9 @@ def test_fold_with_a_value_that_already_arrived(op, code, tdt, name):
     init = np.array([3], dtype=ndt)
     peer_value = np.array([7], dtype=ndt)
     for epoch in (1, 2, 3, 4):                  # both parities, reuse without any reset
-        bits = np.zeros(1, dtype=np.int64)
+        bits = np.zeros(1, dtype=np.uint64)
         bits.view(np.uint8)[: ndt.itemsize] = peer_value.view(np.uint8)
-        s = mine.slot(epoch, 1)
-        mine.words[s] = int(bits[0])
-        mine.words[s + 1] = epoch
+        deliver(mine, epoch, 1, int(bits[0]))
         torch.cuda.synchronize()
         call_peer(op, code, x, init, [mine, theirs], 2, 0, epoch, 0, status, scratch, out)
         local = oracle.fold(x.cpu().numpy(), name, sharded.op_identity(op, ndt))
@@ -96,11 +122,10 @@ def test_fold_with_a_value_that_already_arrived(op, code, tdt, name):
             assert abs(got - want) <= (1e-12 if ndt == np.float64 else 1e-5) * abs(want)
         else:
             assert got == want
-        assert status.item() == 0
-        # this rank published its own value and flag into the peer's mailbox
-        t = theirs.slot(epoch, 0)
-        assert int(theirs.words[t + 1].item()) == epoch
-        pub = np.array([int(theirs.words[t].item())], dtype=np.int64).view(np.uint8)[: ndt.itemsize].view(ndt)[0]
+        assert status[0].item() == 0
+        # this rank published its own value, under the epoch, into the peer's mailbox
+        raw = np.array([delivered(theirs, epoch, 0, ndt.itemsize)], dtype=np.uint64)
+        pub = raw.view(np.uint8)[: ndt.itemsize].view(ndt)[0]
         assert pub == local or (ndt.kind == "f" and abs(pub - local) <= 1e-5 * abs(local))
     mine.close(); theirs.close()
 
@@ -109,14 +134,22 @@ def test_wait_that_runs_out_sets_status_and_returns():
     L = _lib.lib()
     mine, theirs = Mailbox(), Mailbox()
     scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
-    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = new_status()
     x = torch.ones(1000, dtype=torch.int32, device="cuda")
     out = torch.zeros(1, dtype=torch.int32, device="cuda")
     init = np.array([0], dtype=np.int32)
-    # nothing ever sets rank 1's flag: the wait gives up after 2 ms
+    # nothing ever writes rank 1's word: the wait gives up after 2 ms
     call_peer(_lib.ADD, _lib.I32, x, init, [mine, theirs], 2, 0, 1, 2_000_000, status, scratch, out)
     torch.cuda.synchronize()
-    assert status.item() == 1
+    assert status[0].item() == 1
+    assert (status[2] - status[1]).item() >= 2_000_000
+    # a word of the wrong epoch (a call two steps back) does not count either
+    deliver(mine, 3, 1, 99)
+    torch.cuda.synchronize()
+    status.zero_()
+    call_peer(_lib.ADD, _lib.I32, x, init, [mine, theirs], 2, 0, 5, 2_000_000, status, scratch, out)
+    torch.cuda.synchronize()
+    assert status[0].item() == 1
     # the context is intact and the scratch reusable
     status.zero_()
     plain = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -140,11 +173,17 @@ def test_argument_checks():
     init = np.zeros(1, dtype=np.int32)
     ptrs = (ctypes.c_void_p * 1)(4096)
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 0, 0, 1, 0,
-                             4096, None) == _lib.ERR_INVALID_ARG
+                             4096, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 0, 0,
-                             4096, None) == _lib.ERR_INVALID_ARG
+                             4096, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 1 << 32, 0,
+                             4096, 0, None) == _lib.ERR_INVALID_ARG          # low 32 bits of the epoch are zero
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 17, 0, 1, 0,
-                             4096, None) == _lib.ERR_INVALID_ARG
+                             4096, 0, None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 1, 0,
+                             4096, 2, None) == _lib.ERR_INVALID_ARG          # unknown flag
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 1, 0,
+                             4100, 0, None) == _lib.ERR_ALIGNMENT            # status not 8-byte aligned
 
 
 # ---- real ranks on separate GPUs ---------------------------------------------------
@@ -183,6 +222,51 @@ def _rank_main(rank, world, port, errors):
                     assert abs(nccl - want) <= 1e-12 * np.abs(whole).sum()
                 else:
                     assert fused == want == nccl, (name, dt, fused, nccl, want)
+        # a user function outside the op table: partials gathered once, folded on the device
+        fn = lambda a, b: (a + b) % 1000003       # noqa: E731
+        whole = np.random.default_rng(77).integers(0, 1000003, size=300001, dtype=np.int64)
+        lo, hi = sharded.shard_bounds(whole.size, world, rank)
+        import functools
+        want = functools.reduce(lambda a, b: (a + b) % 1000003, [int(v) for v in whole[::1]], 5)
+        for peer in (None, boxes):
+            assert sharded.ShardedReduce(fn, peer=peer)(whole[lo:hi], init=5) == want
+        empty_here = whole[:0] if rank == world - 1 else whole[lo:hi]      # one rank has nothing
+        want = functools.reduce(lambda a, b: (a + b) % 1000003, [int(v) for v in whole[:sharded.shard_bounds(
+            whole.size, world, world - 1)[0]]], 5)
+        assert sharded.ShardedReduce(fn)(empty_here, init=5) == want
+        # a non-default stream: collectives and copies must follow the kernel on it
+        side = cuda.stream()
+        x = np.random.default_rng(5).integers(-2 ** 31, 2 ** 31, size=1 << 22, dtype=np.int32)
+        lo, hi = sharded.shard_bounds(x.size, world, rank)
+        for peer in (None, boxes):
+            for _ in range(5):
+                assert sharded.ShardedReduce(lambda a, b: max(a, b), peer=peer)(x[lo:hi], init=0, stream=side) == \
+                    max(int(x.max()), 0)
+        with np.errstate(over="ignore"):
+            m = x[: (x.size // 512) * 512].reshape(-1, 512)
+            lo, hi = sharded.shard_bounds(m.shape[0], world, rank)
+            got = sharded.ShardedReduceAxis(lambda a, b: a + b)(m[lo:hi], 0, stream=side).copy_to_host(stream=side)
+            side.synchronize()
+            assert got.tobytes() == np.add.reduce(m, axis=0, dtype=np.int32).tobytes()
+        # a pipeline of fused reductions whose inputs are all complete beforehand:
+        # each reads its shard while the one before finishes its exchange
+        from numba_cuda_b200.kernels.reduction import _DTYPE_CODES
+        shards = [cuda.to_device(np.random.default_rng(200 + k).integers(-2 ** 31, 2 ** 31, size=1 << 22,
+                                                                          dtype=np.int32)[
+            slice(*sharded.shard_bounds(1 << 22, world, rank))]) for k in range(8)]
+        outs = cuda.device_array(8, dtype=np.int32)
+        ident = np.array([-2 ** 31], dtype=np.int32)
+        torch.cuda.synchronize()
+        dist.barrier()
+        for k, sh in enumerate(shards):
+            boxes.reduce(_lib.MAX, _DTYPE_CODES[np.dtype(np.int32)], sh._ptr, sh.size, ident, outs[k:k + 1]._ptr,
+                         0, input_ready=True)
+        got = outs.copy_to_host()
+        boxes.check(agree=True)
+        want = [int(np.random.default_rng(200 + k).integers(-2 ** 31, 2 ** 31, size=1 << 22, dtype=np.int32).max())
+                for k in range(8)]
+        assert got.tolist() == want
+        assert 0 <= boxes.exchange_ns() < 50_000_000
         # a row-sharded matrix reduced along both axes
         full = np.random.default_rng(9).integers(-2 ** 31, 2 ** 31, size=(4099, 260), dtype=np.int32)
         lo, hi = sharded.shard_bounds(full.shape[0], world, rank)

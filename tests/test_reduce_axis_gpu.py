@@ -168,3 +168,27 @@ def test_argument_errors():
         cuda.Reduce(lambda a, b: (a + b) % 7).along_axis(np.zeros((4, 4), dtype=np.int32), 0)
     with pytest.raises((NotImplementedError, TypeError, cuda._lib.B2KError)):
         REDUCERS["and"].along_axis(np.zeros((4, 4), dtype=np.float32), 0)
+
+
+@pytest.mark.parametrize("shape,dtype", [((6, 5000, 130), np.int32), ((300, 700, 48), np.uint8),
+                                         ((5000, 37, 24), np.float64), ((3, 20011, 1000), np.int16),
+                                         ((70000, 3, 8), np.int32)])
+def test_middle_axis_of_a_batch_is_one_launch(shape, dtype):
+    """outer x length x inner with outer, inner > 1: every slab is reduced along its rows
+    by ONE launch over the batch of slabs (many tiles, rows cut into chunks, packed small
+    items, more slabs than one launch's 65535)."""
+    from numba_cuda_b200 import _lib
+    host = _data(shape, dtype, 13)
+    dev = cuda.to_device(host)
+    before = _lib.launch_count()
+    got = REDUCERS["add"].along_axis(dev, 1, init=2)
+    launches = _lib.launch_count() - before
+    assert launches == -(-shape[0] // 65535)
+    with np.errstate(over="ignore"):
+        want = np.add.reduce(host, axis=1, dtype=dtype) + np.dtype(dtype).type(2)
+    if np.dtype(dtype).kind == "f":
+        np.testing.assert_allclose(got.copy_to_host(), want, rtol=1e-12)
+    else:
+        assert got.copy_to_host().tobytes() == want.tobytes()
+    got = REDUCERS["max"].along_axis(dev, 1, init=host.min()).copy_to_host()
+    assert got.tobytes() == host.max(axis=1).tobytes()

@@ -195,3 +195,57 @@ def test_untraceable_functor_raises():
         cuda.reduce(lambda a, b: math.sqrt(a) + b)(np.arange(10.0))
     with pytest.raises(NotImplementedError):
         cuda.reduce(lambda a, b: a + b)(np.arange(10.0).astype(np.complex128))
+
+
+def test_two_host_threads_reducing_on_one_stream_get_their_own_results():
+    """Modelled on tests/cudapy/test_multithreads.py:40-68 of the reference: host threads
+    share the device and the default stream; every call must return ITS result."""
+    import threading
+    reducers = {"add": cuda.reduce(lambda a, b: a + b), "max": cuda.reduce(lambda a, b: max(a, b))}
+    arrays = [cuda.to_device(np.random.default_rng(50 + t).integers(-1000, 1000, size=20000 + 7 * t, dtype=np.int64))
+              for t in range(4)]
+    hosts = [a.copy_to_host() for a in arrays]
+    errors = []
+
+    def work(t):
+        try:
+            torch.cuda.set_device(0)
+            for k in range(300):
+                name = "add" if (k + t) % 2 else "max"
+                got = reducers[name](arrays[t], init=t)
+                want = hosts[t].sum() + t if name == "add" else max(hosts[t].max(), t)
+                if got != want:
+                    errors.append((t, k, name, int(got), int(want)))
+                    return
+        except Exception as exc:     # noqa: BLE001
+            errors.append((t, repr(exc)))
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors[:3]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_second_device_in_the_same_process():
+    """Function attributes (the dynamic shared-memory limit of the TMA transposes and of
+    state creation) belong to a device: everything must also run on device 1 after
+    device 0 has been used."""
+    from numba_cuda_b200.kernels.transpose import permute, transpose
+    from numba_cuda_b200.random import create_xoroshiro128p_states
+    a = np.random.default_rng(3).standard_normal((1024, 2048)).astype(np.float32)
+    cube = np.arange(32 * 64 * 128, dtype=np.float32).reshape(32, 64, 128)
+    want_states = oracle.init_states(1 << 18, 9, 0)
+    try:
+        for dev in (0, 1):
+            torch.cuda.set_device(dev)
+            assert transpose(cuda.to_device(a)).copy_to_host().tobytes() == np.ascontiguousarray(a.T).tobytes()
+            assert permute(cuda.to_device(cube), (0, 2, 1)).copy_to_host().tobytes() == \
+                np.ascontiguousarray(cube.transpose(0, 2, 1)).tobytes()
+            st = create_xoroshiro128p_states(1 << 18, seed=9)
+            assert st.copy_to_host().tobytes() == want_states.tobytes()
+            assert cuda.reduce(lambda x, y: x + y)(np.arange(100000, dtype=np.int64)) == 100000 * 99999 // 2
+    finally:
+        torch.cuda.set_device(0)

@@ -143,6 +143,41 @@ def _body_axis_rows(rank, world):
         assert rows[rank].tobytes() == partial.tobytes()
 
 
+def _body_traced_combine(rank, world):
+    """A user function outside the op table: per-rank records [value | present] are
+    gathered once and the values that are there are folded in rank order with init
+    (functools.reduce stands in for the run-time compiled kernel).  Rank 1's shard is
+    empty in the second case, every shard in the third."""
+    import functools
+    from numba_cuda_b200 import sharded
+    fn = lambda a, b: (a * 31 + b) % 1000003 if a > b else (b * 31 + a) % 1000003     # noqa: E731  (commutative)
+    whole = np.random.default_rng(8).integers(0, 1 << 20, size=1000, dtype=np.int64)
+    for case, bounds in (("all", sharded.shard_bounds(1000, world, rank)),
+                         ("one empty", (0, 1000) if rank == 0 else (1000, 1000)),
+                         ("all empty", (0, 0))):
+        lo, hi = bounds
+        record = np.zeros(16, dtype=np.uint8)
+        if hi > lo:
+            record[:8] = np.array([functools.reduce(fn, whole[lo:hi].tolist())], dtype=np.int64).view(np.uint8)
+            record[8] = 1
+        rows = sharded.gather_partial_rows(torch.from_numpy(record))
+        assert tuple(rows.shape) == (world, 16)
+        seen = []
+
+        def fold(values):
+            seen.append(np.array(values))
+            return np.int64(functools.reduce(fn, values.tolist(), 7))
+        got = sharded.fold_gathered(rows, np.int64, 7, fold)
+        if case == "all empty":
+            assert got == 7 and not seen
+        else:
+            parts = [functools.reduce(fn, whole[a:b].tolist())
+                     for a, b in ([sharded.shard_bounds(1000, world, r) for r in range(world)]
+                                  if case == "all" else [(0, 1000)])]
+            assert seen[0].tolist() == parts                      # rank order, absent ranks dropped
+            assert got == functools.reduce(fn, parts, 7)
+
+
 def _body_world_mismatch(rank, world):
     from numba_cuda_b200 import sharded
     with pytest.raises(ValueError):
@@ -194,6 +229,10 @@ def test_cast_shards_are_aligned_and_complete():
 
 def test_row_sharded_axis_reduce_combines_with_one_gather():
     _run("_body_axis_rows")
+
+
+def test_traced_function_partials_are_gathered_and_folded_in_rank_order():
+    _run("_body_traced_combine")
 
 
 def test_bad_rank_is_rejected():
