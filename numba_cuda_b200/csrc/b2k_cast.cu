@@ -380,52 +380,52 @@ struct F16ToF32 {
     __device__ static OutS one(InS h) { return f16bits_to_f32(h); }
 };
 
-// f64 -> fp8: __nv_cvt_double_to_fp8 (cuda_fp8.hpp:119-229), which is integer code on
-// the device too (there is no cvt from f64 to fp8), so NaN signs and payload bits come
-// out as that code makes them.  All its thresholds and the rounding decision depend on
-// the low 32 bits of the double only through "is any of them set", so the same steps
-// run here on the high word with that one sticky bit folded into its last place.
+// f64 -> fp8: __nv_cvt_double_to_fp8 (cuda_fp8.hpp:119-229) rounds the double to the
+// fp8 grid once, to nearest even, with integer code (on the device too: there is no
+// cvt from f64 to fp8).  The same result comes out of two hardware steps: the double
+// is first rounded to float32 "to odd" (truncate, then set the last bit if anything
+// was cut off), which keeps a sticky trace of every discarded bit, and the float is
+// then rounded to nearest even by the float encoder -- with 24 significant bits
+// against at most 4 in the target the second rounding sees exactly what a single
+// one would.  Doubles beyond the float range truncate to the largest finite float
+// and overflow the fp8 range like the double does; doubles below it leave a
+// non-zero denormal that rounds to a signed zero like the double does.  NaNs are
+// the one case where the integer code's result depends on the double's own bits
+// (sign, and for E5M2 the top two mantissa bits), so they are patched in from there.
+__device__ __forceinline__ float f64_to_f32_round_to_odd(double x) {
+    float f;
+    double back;
+    asm("cvt.rz.f32.f64 %0, %1;" : "=f"(f) : "d"(x));
+    asm("cvt.f64.f32 %0, %1;" : "=d"(back) : "f"(f));
+    const uint32_t u = __float_as_uint(f);
+    return __uint_as_float(back != x ? (u | 1u) : u);   // a NaN compares unequal and stays a NaN
+}
 template <bool E5M2, bool SAT>
 struct F64ToFp8 {
     using InS = double; using OutS = uint8_t;
-    __device__ static OutS one(InS x) {
-        constexpr uint32_t kMant = E5M2 ? 2u : 3u;               // stored mantissa bits
-        constexpr int kBias = E5M2 ? 15 : 7;
-        constexpr uint32_t kHalfMinDenorm = E5M2 ? 0x3EE00000u : 0x3F500000u;  // 2^-17 / 2^-10
-        constexpr uint32_t kMinNorm = E5M2 ? 0x3F100000u : 0x3F900000u;        // 2^-14 / 2^-6
-        // magnitudes above this no longer round to the largest finite value
-        constexpr uint32_t kOverflowAbove = E5M2 ? 0x40EDFFFFu : 0x407D0000u;
-        constexpr uint32_t kHalf = 1u << (19u - kMant);          // half an fp8 ulp in the high word
-
-        const uint32_t lo = static_cast<uint32_t>(__double2loint(x));
+    __device__ static uint32_t nan_code(double x) {
         const uint32_t hi = static_cast<uint32_t>(__double2hiint(x));
-        const uint32_t bits = hi | (lo != 0u ? 1u : 0u);
-        const uint32_t mag = bits & 0x7FFFFFFFu;
-        const uint32_t sign = (hi >> 24) & 0x80u;
-        uint32_t mant = (hi >> (20u - kMant)) & ((1u << kMant) - 1u);
-        uint32_t code;
-        if (mag <= kHalfMinDenorm) {
-            code = 0u;
-        } else if (mag > 0x7FF00000u) {                          // NaN
-            code = E5M2 ? (0x7Eu | mant) : 0x7Fu;
-        } else if (mag > kOverflowAbove) {                       // too large, infinities included
-            code = SAT ? (E5M2 ? 0x7Bu : 0x7Eu) : (E5M2 ? 0x7Cu : 0x7Fu);
+        return ((hi >> 24) & 0x80u) | (E5M2 ? (0x7Eu | ((hi >> 18) & 3u)) : 0x7Fu);
+    }
+    __device__ static OutS one(InS x) {
+        const uint32_t code = F32ToFp8<E5M2, SAT>::one(f64_to_f32_round_to_odd(x));
+        return static_cast<OutS>(x != x ? nan_code(x) : code);
+    }
+    // two codes at once, `a` in the low byte: one packed cvt in the saturating mode
+    __device__ static uint32_t pair(InS a, InS b) {
+        const float fa = f64_to_f32_round_to_odd(a), fb = f64_to_f32_round_to_odd(b);
+        uint32_t lo, hi;
+        if constexpr (SAT) {
+            const uint32_t both = E5M2 ? pack2_e5m2_sat(fb, fa) : pack2_e4m3_sat(fb, fa);
+            lo = both & 0xFFu;
+            hi = both >> 8;
         } else {
-            const int e8 = static_cast<int>((hi >> 20) & 0x7FFu) - 1023 + kBias;
-            if (mag >= kMinNorm) {
-                code = (static_cast<uint32_t>(e8) << kMant) | mant;
-                const uint32_t dropped = bits & ((kHalf << 1) - 1u);
-                if (dropped > kHalf || (dropped == kHalf && (mant & 1u))) ++code;
-            } else {
-                const uint32_t shift = static_cast<uint32_t>(1 - e8);
-                mant |= 1u << kMant;
-                code = mant >> shift;
-                const uint32_t dropped = (bits | (1u << 20)) & ((kHalf << (shift + 1u)) - 1u);
-                const uint32_t mid = kHalf << shift;
-                if (dropped > mid || (dropped == mid && (code & 1u))) ++code;
-            }
+            lo = f32_to_fp8_nosat<E5M2>(fa);
+            hi = f32_to_fp8_nosat<E5M2>(fb);
         }
-        return static_cast<OutS>(code | sign);
+        if (a != a) lo = nan_code(a);
+        if (b != b) hi = nan_code(b);
+        return lo | (hi << 8);
     }
 };
 // bf16 -> fp8: __nv_cvt_bfloat16raw_to_fp8 (cuda_fp8.hpp:442-450) = the bits moved into
@@ -467,6 +467,9 @@ template <> struct Mover<uint32_t> {
     __device__ static void store(uint32_t *p, const uint32_t &v) { __stcs(p, v); }
 };
 
+template <typename C, typename = void> struct HasPair : std::false_type {};
+template <typename C> struct HasPair<C, std::void_t<decltype(&C::pair)>> : std::true_type {};
+
 template <typename C>
 struct WideOf {
     static constexpr int ELEMS = (sizeof(typename C::InS) == 8 || sizeof(typename C::OutS) == 8) ? 4 : 8;
@@ -474,10 +477,15 @@ struct WideOf {
     using Out = typename VecOf<ELEMS * sizeof(typename C::OutS)>::type;
     __device__ static Out convert(const In &v) {
         union { In raw; typename C::InS e[ELEMS]; } src;
-        union { Out raw; typename C::OutS e[ELEMS]; } dst;
+        union { Out raw; typename C::OutS e[ELEMS]; uint16_t two[ELEMS / 2]; } dst;
         src.raw = v;
+        if constexpr (HasPair<C>::value) {   // converters of byte codes that do two at a time
 #pragma unroll
-        for (int k = 0; k < ELEMS; ++k) dst.e[k] = C::one(src.e[k]);
+            for (int k = 0; k < ELEMS; k += 2) dst.two[k / 2] = static_cast<uint16_t>(C::pair(src.e[k], src.e[k + 1]));
+        } else {
+#pragma unroll
+            for (int k = 0; k < ELEMS; ++k) dst.e[k] = C::one(src.e[k]);
+        }
         return dst.raw;
     }
 };

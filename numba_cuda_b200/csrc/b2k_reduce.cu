@@ -181,8 +181,7 @@ __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) 
 template <typename T, typename Op, int THREADS, int UNROLL, bool PEER>
 __global__ void __launch_bounds__(THREADS)
 reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
-              T *partials, unsigned int *ticket, const int chunked, const int input_ready,
-              const PeerLink link) {
+              T *partials, unsigned int *ticket, const int input_ready, const PeerLink link) {
     constexpr int VEC = 32 / sizeof(T);
     __shared__ T slots[THREADS / 32];
     __shared__ bool is_last;
@@ -206,10 +205,7 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     const int64_t nvec = (n - head) / VEC;
     const int64_t tail_begin = head + nvec * VEC;
     constexpr int64_t CHUNK = static_cast<int64_t>(THREADS) * UNROLL;
-    // short inputs skip the chunk loop: the grid-stride loop below spreads their
-    // vectors evenly over twice as many CTAs as there are whole chunks
-    const int64_t nchunks = chunked ? nvec / CHUNK : 0;
-    const int64_t gstride = static_cast<int64_t>(gridDim.x) * THREADS;
+    const int64_t nchunks = nvec / CHUNK;
 
     T acc[UNROLL];
 #pragma unroll
@@ -229,15 +225,9 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) packed[u] = fold_words<T, Op>(packed[u], raw[u]);
         }
-        int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
-        for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
-            Bits256 raw[UNROLL];
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(xv + v + u * gstride);
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) packed[u] = fold_words<T, Op>(packed[u], raw[u]);
-        }
-        for (; v < nvec; v += gstride) packed[0] = fold_words<T, Op>(packed[0], load_stream32(xv + v));
+        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
+             v += static_cast<int64_t>(gridDim.x) * THREADS)
+            packed[0] = fold_words<T, Op>(packed[0], load_stream32(xv + v));
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) acc[u] = fold_word<T, Op>(acc[u], packed[u]);
     } else {
@@ -253,18 +243,8 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
             }
         }
         // vectors past the last whole chunk, spread over the grid
-        int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
-        for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
-            Bits256 raw[UNROLL];
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) raw[u] = load_stream32(xv + v + u * gstride);
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                acc[u] = fold_vector<T, Op>(acc[u], raw[u].lo);
-                acc[u] = fold_vector<T, Op>(acc[u], raw[u].hi);
-            }
-        }
-        for (; v < nvec; v += gstride) {
+        for (int64_t v = nchunks * CHUNK + static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; v < nvec;
+             v += static_cast<int64_t>(gridDim.x) * THREADS) {
             const Bits256 raw = load_stream32(xv + v);
             acc[0] = fold_vector<T, Op>(acc[0], raw.lo);
             acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
@@ -302,17 +282,14 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
            cudaStream_t stream, const PeerLink *link, unsigned flags) {
     T init;
     memcpy(&init, init_host, sizeof(T));
-    // two persistent CTAs per SM measured best on B200.  Inputs of fewer than eight
-    // chunks per CTA are not cut into chunks (a CTA would own one or two of them and
-    // the grid would be lopsided, or smaller than the GPU): their 32-byte vectors go
-    // round the grid, one CTA per THREADS vectors up to the same two CTAs per SM.
+    // two persistent CTAs per SM measured best on B200; short inputs get one CTA per chunk
+    // (spreading an 8 MiB input over twice as many, smaller CTAs measured the same: that
+    // case is bound by the fixed latencies of launch, ticket and last-block fold)
     const int per_sm = B2K_ENV_INT("B2K_REDUCE_CTAS_PER_SM", 2);
     int64_t max_grid = static_cast<int64_t>(b2k::sm_count()) * per_sm;
     if (max_grid > kMaxGrid) max_grid = kMaxGrid;
     const int64_t chunk_bytes = static_cast<int64_t>(kThreads) * kUnroll * 32;
-    const int64_t nbytes = n * static_cast<int64_t>(sizeof(T));
-    const int chunked = nbytes >= chunk_bytes * max_grid * B2K_ENV_INT("B2K_REDUCE_MIN_CHUNKS_PER_CTA", 8);
-    int64_t grid = chunked ? max_grid : (nbytes + kThreads * 32 - 1) / (kThreads * 32);
+    int64_t grid = (n * static_cast<int64_t>(sizeof(T)) + chunk_bytes - 1) / chunk_bytes;
     if (grid < 1) grid = 1;
     if (grid > max_grid) grid = max_grid;
     auto *ticket = static_cast<unsigned int *>(scratch);
@@ -331,10 +308,10 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
     cudaError_t err;
     if (link) {
         err = cudaLaunchKernelEx(&cfg, reduce_kernel<T, Op, kThreads, kUnroll, true>, static_cast<const T *>(x), n,
-                                 init, static_cast<T *>(out), partials, ticket, chunked, input_ready, *link);
+                                 init, static_cast<T *>(out), partials, ticket, input_ready, *link);
     } else {
         err = cudaLaunchKernelEx(&cfg, reduce_kernel<T, Op, kThreads, kUnroll, false>, static_cast<const T *>(x), n,
-                                 init, static_cast<T *>(out), partials, ticket, chunked, input_ready, PeerLink{});
+                                 init, static_cast<T *>(out), partials, ticket, input_ready, PeerLink{});
     }
     if (err != cudaSuccess) return b2k::check_cuda(err, "b2k_reduce launch");
     b2k::note_launch();

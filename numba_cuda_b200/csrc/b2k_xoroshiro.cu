@@ -620,6 +620,9 @@ int b2k_xoroshiro128p_fill(void *states_dev, int64_t n, int draw0, void *out0_de
     const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * B2K_ENV_INT("B2K_XORO_FILL_CTAS_PER_SM", 8);
     if (grid > cap) grid = cap;
     Segment a{out0_dev, count0, draw0}, b{out1_dev, count1, draw1};
+    // four resident CTAs per SM at 64 registers; five or six (48 / 40 registers) measured
+    // 2-5 % slower: the kernel is bound by the integer pipe and by issue slots, not by
+    // latency that more warps could hide
     xoro_fill_kernel<4, 4><<<static_cast<unsigned>(grid), kFillWarps * 32, 0, b2k::as_stream(stream)>>>(
         static_cast<ulonglong2 *>(states_dev), n, a, b);
     b2k::note_launch();

@@ -187,7 +187,8 @@ def test_middle_axis_of_a_batch_is_one_launch(shape, dtype):
     with np.errstate(over="ignore"):
         want = np.add.reduce(host, axis=1, dtype=dtype) + np.dtype(dtype).type(2)
     if np.dtype(dtype).kind == "f":
-        np.testing.assert_allclose(got.copy_to_host(), want, rtol=1e-12)
+        scale = np.abs(host).sum(axis=1)                      # sums of mixed signs cancel
+        assert (np.abs(got.copy_to_host() - want) <= 1e-12 * scale).all()
     else:
         assert got.copy_to_host().tobytes() == want.tobytes()
     got = REDUCERS["max"].along_axis(dev, 1, init=host.min()).copy_to_host()
