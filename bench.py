@@ -691,38 +691,55 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
         out = torch.zeros(1, dtype=torch.float64, device="cuda")
         zero = np.zeros(1, dtype=np.float64)
 
+        # the arguments are worked out once: the loop below measures the C-ABI call, not
+        # Python attribute look-ups (ndarray.ctypes alone costs more than a microsecond)
+        xp, zp, op_, sp_, sn = x._ptr, zero.ctypes.data, out.data_ptr(), scratch.data_ptr(), scratch.numel()
+        reduce_fn, reduce_ex = L.b2k_reduce, L.b2k_reduce_ex
+
         def call():
-            check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
-                               scratch.data_ptr(), scratch.numel(), sptr))
+            if reduce_fn(_lib.ADD, _lib.F64, xp, n, zp, op_, sp_, sn, sptr):
+                raise RuntimeError(L.b2k_last_error())
+
+        def call_ready():
+            if reduce_ex(_lib.ADD, _lib.F64, xp, n, zp, op_, sp_, sn, _lib.REDUCE_INPUT_READY, sptr):
+                raise RuntimeError(L.b2k_last_error())
         ms, _ = timed(call, 200, 10)
         entry = dict(_roof(n * 8, ms, peak), us_per_call=ms * 1e3,
                      note="8 MiB: launch-latency bound, L2 resident; us_per_call = back-to-back calls through "
                           "ctypes (CUDA events), kernel_us = the same launches replayed from a CUDA graph, "
-                          "host_us_per_call = wall clock of the issuing loop alone")
+                          "host_us_per_call = wall clock of the issuing loop alone; *_input_ready = the same with "
+                          "B2K_REDUCE_INPUT_READY (the input is not produced by the previous kernel), which lets "
+                          "a reduction read its input while the one before finishes")
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(2000):
             call()
         entry["host_us_per_call"] = (time.perf_counter() - t0) / 2000 * 1e6
         torch.cuda.synchronize()
+        ms_r, _ = timed(call_ready, 200, 10)
+        entry["us_per_call_input_ready"] = ms_r * 1e3
+        assert abs(float(out.item()) - float(np.random.default_rng(0).random(n).sum())) < 1e-6
         # the same call captured in a CUDA graph (20 launches per replay): what is left
         # of the 8 MiB case once the launch path is off the critical line
-        try:
-            side = torch.cuda.Stream()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
-                                   scratch.data_ptr(), scratch.numel(), side.cuda_stream))
-            side.synchronize()
-            with torch.cuda.graph(graph, stream=side):
-                for _ in range(20):
-                    check(L.b2k_reduce(_lib.ADD, _lib.F64, x._ptr, n, zero.ctypes.data, out.data_ptr(),
-                                       scratch.data_ptr(), scratch.numel(), torch.cuda.current_stream().cuda_stream))
-            ms_g, _ = timed(graph.replay, 20, 5)
-            entry["kernel_us"] = entry["us_per_call_in_cuda_graph"] = ms_g * 1e3 / 20
-            del graph
-        except Exception as exc:  # graphs are an extra, never a reason to fail the bench
-            entry["cuda_graph_error"] = repr(exc)
+        for key, fn_ in (("kernel_us", reduce_fn), ("kernel_us_input_ready", reduce_ex)):
+            try:
+                side = torch.cuda.Stream()
+                graph = torch.cuda.CUDAGraph()
+                extra = () if fn_ is reduce_fn else (_lib.REDUCE_INPUT_READY,)
+                with torch.cuda.stream(side):
+                    check(fn_(_lib.ADD, _lib.F64, xp, n, zp, op_, sp_, sn, *extra, side.cuda_stream))
+                side.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        check(fn_(_lib.ADD, _lib.F64, xp, n, zp, op_, sp_, sn, *extra,
+                                  torch.cuda.current_stream().cuda_stream))
+                ms_g, _ = timed(graph.replay, 20, 5)
+                entry[key] = ms_g * 1e3 / 20
+                del graph
+            except Exception as exc:  # graphs are an extra, never a reason to fail the bench
+                entry[key + "_error"] = repr(exc)
+        if "kernel_us" in entry:
+            entry["us_per_call_in_cuda_graph"] = entry["kernel_us"]
         res["c1_reduce_sum_f64_2p20"] = entry
         n2 = 1 << (28 - scale)
         y = torch.rand(n2, dtype=torch.float64, device="cuda")

@@ -85,7 +85,8 @@ B2K_API int64_t b2k_launch_count(void);
  *   out_dev   : one element of `dtype`
  *   scratch   : b2k_reduce_scratch_bytes() bytes, zero-filled once by the caller
  *               before first use; the kernel leaves it reusable.  Two reductions
- *               that may overlap on the GPU need separate scratch.
+ *               that may overlap on the GPU need separate scratch.  (b2k_reduce,
+ *               b2k_reduce_ex and b2k_reduce_expr touch only the first half of it.)
  * n == 0 writes *init_host to out_dev. */
 B2K_API int64_t b2k_reduce_scratch_bytes(void);
 B2K_API int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
@@ -158,8 +159,8 @@ B2K_API int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int6
 /* Reduce + cross-GPU combine in ONE kernel per GPU (no counterpart in the
  * reference, which has no distributed layer).  For an array sharded over up to
  * b2k_peer_max_world() GPUs of one NVLink domain: every rank calls
- * b2k_reduce_peer on its shard with the same `epoch` (1, 2, 3, ... per call of a
- * communicator; its low 32 bits must not be zero); the block that finishes the
+ * b2k_reduce_peer on its shard with the same `epoch` (1, 2, 3, ... without gaps, per
+ * communicator and scratch buffer); the block that finishes the
  * local fold stores the rank's value into a mailbox in every peer's memory, waits
  * (at most timeout_ns, 0 = 2 s) for the peers' values of this epoch in its own
  * mailbox, folds them in rank order, folds *init_host in and writes out_dev[0] --
@@ -168,14 +169,22 @@ B2K_API int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int6
  *               as visible from this process (own: from b2k_peer_mailbox_create;
  *               others: b2k_peer_mailbox_open of the handle that rank exported).
  *   status_dev: three 64-bit words in device memory, 8-byte aligned.  [0] is set to
- *               1 when a peer's value did not arrive in time (the kernel then writes
+ *               1 when a peer's value did not arrive in time, 2 when a scratch set
+ *               was not released in time (in the first case the kernel writes
  *               the fold of nothing but *init_host and returns: no hang; the other
  *               ranks may have completed normally, so after a timeout the ranks hold
  *               DIFFERENT results and have to agree on the host what to do).  [1] and
  *               [2] receive the GPU's nanosecond timer when the local fold was done
  *               and when the last peer value had been seen: their difference is what
  *               the exchange cost this rank, launch skew between the ranks included.
- *   flags     : as for b2k_reduce_ex.
+ *   scratch   : b2k_reduce_scratch_bytes() bytes, zero-filled once; it belongs to the
+ *               communicator (all its calls, whatever the stream).  It holds two
+ *               ticket/partial sets that alternate with the epoch, so two calls may
+ *               overlap on the GPU; a third waits (bounded) for the first to let go.
+ *   flags     : as for b2k_reduce_ex.  With B2K_REDUCE_INPUT_READY only the block
+ *               that runs the exchange waits for the preceding kernel; the others
+ *               free their SMs as soon as their loads are done, so a peer that is
+ *               late does not stall this GPU's reads of the following calls.
  * The mailbox helpers allocate/map b2k_peer_mailbox_bytes() bytes once per
  * communicator; handles are b2k_peer_handle_bytes() bytes and travel between
  * processes by any host channel. */

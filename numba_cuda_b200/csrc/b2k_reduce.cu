@@ -28,7 +28,14 @@ using namespace b2k_reduce_ops;
 constexpr int kThreads = 512;
 constexpr int kUnroll = 4;
 constexpr int kMaxGrid = 4096;
-constexpr int kTicketBytes = 256;  // ticket word padded so partials stay 256-B aligned
+constexpr int kTicketBytes = 256;  // control words, padded so partials stay 256-B aligned
+// Scratch layout.  Bytes 0..255: ticket of set 0 at byte 0 and of set 1 at byte 4; at
+// bytes 64 and 72 the 64-bit "read" markers of the two sets (cross-GPU calls only).
+// Then kMaxGrid 8-byte partial slots of set 0, then those of set 1.  Plain reductions
+// use set 0 alone and need only the first half of the buffer.
+constexpr int kSetBytes = 8 * kMaxGrid;
+constexpr int kScratchPlain = kTicketBytes + kSetBytes;
+constexpr int kScratchFull = kTicketBytes + 2 * kSetBytes;
 
 // Block-wide fold; the result is valid in thread 0.  `slots` holds one T per warp.
 template <typename T, typename Op, int THREADS>
@@ -69,9 +76,10 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
 // peer's value for this call has arrived in its own mailbox, and folds the values in
 // rank order.  No second launch and no library collective.
 //
-// A value travels as 64-bit words that each carry 32 bits of payload under the low
-// 32 bits of the call's epoch: {epoch32, value bits 31..0} and, for 8-byte items,
-// {epoch32, value bits 63..32}.  A 64-bit store is single-copy atomic, so a word that
+// A value travels as 64-bit words that each carry 32 bits of payload under a 32-bit tag
+// of the call's epoch (epoch mod (2^32 - 1), plus one: never zero, and different for
+// epochs two apart): {tag, value bits 31..0} and, for 8-byte items, {tag, value bits
+// 63..32}.  A 64-bit store is single-copy atomic, so a word that
 // shows this call's epoch also shows its payload: no separate flag, and no release
 // fence between a value and its flag (a fence at system scope has to wait for the
 // remote write to be acknowledged -- a full NVLink round trip before the flag could
@@ -80,6 +88,17 @@ __device__ __forceinline__ Bits256 load_stream32(const Bits256 *p) {
 // be at most one call ahead (it cannot finish call k+1 before this rank has published
 // k+1).  The wait is bounded: when it runs out the block records an error status,
 // writes the identity-folded result and returns.
+//
+// Pipelining across calls.  Ticket and partial slots exist twice and a cross-GPU call
+// uses the set of its epoch's parity.  The block that folds a set's partials then
+// publishes "set read by call e" in that set's marker, and a CTA of call e+2 checks the
+// marker (a bounded wait that is normally satisfied at once) before it writes its
+// partial.  With B2K_REDUCE_INPUT_READY this is the only thing an ordinary CTA waits
+// for: it does not wait for the preceding kernel at all, so its SM slot is free again as
+// soon as its own loads are done, and only the ONE block that runs the exchange waits
+// for the preceding call to complete (mailboxes and result stay in stream order).  A
+// rank that is late therefore stalls one block per call in flight on its peers, not
+// their loads: every GPU streams at its own pace and the ranks meet in the tails.
 constexpr int kMaxPeers = 16;
 constexpr int kMailboxWords = 2 * kMaxPeers * 2;  // [parity][writer]{low word, high word}
 
@@ -97,7 +116,9 @@ struct PeerLink {
     unsigned long long *mailbox[kMaxPeers];  // mailbox of every rank (own one included)
     int world;
     int rank;
-    unsigned long long epoch;               // same on every rank for one call; low 32 bits never 0
+    unsigned long long epoch;               // same on every rank for one call: 1, 2, 3, ...
+    unsigned long long tag;                 // ((epoch mod (2^32 - 1)) + 1) << 32
+    unsigned long long *marker;             // "read by call e" word of this call's scratch set
     unsigned long long timeout_ns;
     // [0] = 1 when a wait ran out; [1], [2] = %globaltimer (ns) when this GPU's local fold
     // was complete and when every peer's value had been seen
@@ -110,6 +131,14 @@ __device__ __forceinline__ void store_relaxed_sys(unsigned long long *p, unsigne
 __device__ __forceinline__ unsigned long long load_relaxed_sys(const unsigned long long *p) {
     unsigned long long v;
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void store_release_gpu(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_acquire_gpu(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -135,7 +164,7 @@ __device__ __forceinline__ T exchange_with_peers(T local, const PeerLink &link) 
     }
     __syncthreads();
     const int slot_base = static_cast<int>(link.epoch & 1ull) * kMaxPeers;
-    const unsigned long long tag = (link.epoch & 0xFFFFFFFFull) << 32;
+    const unsigned long long tag = link.tag;
     if (threadIdx.x < link.world) {
         const int p = threadIdx.x;
         // publish to rank p (this rank's own mailbox included: one code path)
@@ -192,9 +221,11 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     // kernel may still write.  When the caller has promised that the input was
     // complete before the preceding kernel began (input_ready), that wait moves
     // behind the load loop: the reads of reduction k+1 then overlap the last block
-    // and the cross-GPU exchange of reduction k, and only the scratch, the mailboxes
-    // and the result are touched in stream order.  Both instructions do nothing in a
-    // launch without the programmatic attribute.
+    // (and the cross-GPU exchange) of reduction k, and only the scratch, the mailboxes
+    // and the result are touched in stream order.  In a cross-GPU call the scratch is
+    // double-buffered and guarded by its own marker, so there only the block that runs
+    // the exchange waits for the predecessor (see the notes on pipelining above).  Both
+    // instructions do nothing in a launch without the programmatic attribute.
     asm volatile("griddepcontrol.launch_dependents;");
     if (!input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -250,7 +281,7 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
             acc[0] = fold_vector<T, Op>(acc[0], raw.hi);
         }
     }
-    if (input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (input_ready && !PEER) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (blockIdx.x == 0) {  // fewer than 32 scalars on each side
         if (threadIdx.x < head) acc[0] = Op::template apply<T>(acc[0], x[threadIdx.x]);
         const int64_t t = tail_begin + threadIdx.x;
@@ -261,6 +292,19 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
 
     T total = block_fold<T, Op, THREADS>(acc[0], slots);
     if (threadIdx.x == 0) {
+        if constexpr (PEER) {
+            // this set's partials were last used by the call two epochs back: they may be
+            // overwritten once that call's folding block has read them
+            const unsigned long long want = link.epoch > 2 ? link.epoch - 2 : 0;
+            unsigned long long t0 = 0;
+            for (unsigned int spin = 0; load_acquire_gpu(link.marker) < want; ++spin) {
+                if (spin == 64) t0 = global_timer_ns();
+                if (spin > 64) {
+                    if (global_timer_ns() - t0 > link.timeout_ns) { link.status[0] = 2; break; }
+                    __nanosleep(100);
+                }
+            }
+        }
         partials[blockIdx.x] = total;
         __threadfence();
         const unsigned int t = atomicInc(ticket, gridDim.x - 1);
@@ -273,7 +317,12 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
         mine = Op::template apply<T>(mine, __ldcg(partials + i));
     total = block_fold<T, Op, THREADS>(mine, slots);
-    if constexpr (PEER) total = exchange_with_peers<T, Op, THREADS>(total, link);
+    if constexpr (PEER) {
+        if (threadIdx.x == 0) store_release_gpu(link.marker, link.epoch);   // the set is free for call epoch + 2
+        // from here on everything is in stream order: mailboxes, status, result
+        if (input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+        total = exchange_with_peers<T, Op, THREADS>(total, link);
+    }
     if (threadIdx.x == 0) out[0] = Op::template apply<T>(total, init);
 }
 
@@ -292,8 +341,15 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
     int64_t grid = (n * static_cast<int64_t>(sizeof(T)) + chunk_bytes - 1) / chunk_bytes;
     if (grid < 1) grid = 1;
     if (grid > max_grid) grid = max_grid;
-    auto *ticket = static_cast<unsigned int *>(scratch);
-    auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes);
+    const int set = link ? static_cast<int>(link->epoch & 1ull) : 0;
+    auto *ticket = static_cast<unsigned int *>(scratch) + set;
+    auto *partials = reinterpret_cast<T *>(static_cast<char *>(scratch) + kTicketBytes + set * kSetBytes);
+    PeerLink with_marker{};
+    if (link) {
+        with_marker = *link;
+        with_marker.marker = reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + 64) + set;
+        link = &with_marker;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(kThreads);
@@ -354,7 +410,7 @@ size_t dtype_size(int dtype) {
 
 extern "C" {
 
-int64_t b2k_reduce_scratch_bytes(void) { return kTicketBytes + 8 * static_cast<int64_t>(kMaxGrid); }
+int64_t b2k_reduce_scratch_bytes(void) { return kScratchFull; }
 
 static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
                        void *scratch_dev, int64_t scratch_bytes, void *stream, const PeerLink *link,
@@ -365,9 +421,10 @@ static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const vo
     if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: negative length %lld", (long long)n);
     if (!init_host || !out_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: null init or out");
     if (n > 0 && !x_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce: null input with n > 0");
-    if (!scratch_dev || scratch_bytes < b2k_reduce_scratch_bytes())
-        return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce: scratch of %lld bytes required",
-                         (long long)b2k_reduce_scratch_bytes());
+    // cross-GPU calls use both halves of the buffer, plain ones the first half only
+    const int64_t scratch_needed = link ? kScratchFull : kScratchPlain;
+    if (!scratch_dev || scratch_bytes < scratch_needed)
+        return b2k::fail(B2K_ERR_SCRATCH, "b2k_reduce: scratch of %lld bytes required", (long long)scratch_needed);
     if (!b2k::aligned_to<void>(x_dev, size) || !b2k::aligned_to<void>(out_dev, size))
         return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce: pointers must be aligned to the element size");
     if (!b2k::aligned_to<void>(scratch_dev, 256))
@@ -446,9 +503,8 @@ int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void 
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: world %d / rank %d out of range (at most %d ranks)",
                          world, rank, kMaxPeers);
-    if (!mailboxes || !status_dev || (epoch & 0xFFFFFFFFull) == 0)
-        return b2k::fail(B2K_ERR_INVALID_ARG,
-                         "b2k_reduce_peer: null mailboxes/status, or an epoch whose low 32 bits are zero");
+    if (!mailboxes || !status_dev || epoch == 0)
+        return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: null mailboxes/status or epoch 0");
     if (!b2k::aligned_to<void>(status_dev, 8))
         return b2k::fail(B2K_ERR_ALIGNMENT, "b2k_reduce_peer: status must be 8-byte aligned");
     if (flags & ~static_cast<unsigned>(B2K_REDUCE_INPUT_READY))
@@ -462,6 +518,7 @@ int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void 
     link.world = world;
     link.rank = rank;
     link.epoch = epoch;
+    link.tag = ((epoch % 0xFFFFFFFFull) + 1ull) << 32;
     link.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
     link.status = static_cast<unsigned long long *>(status_dev);
     return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, &link, flags);
@@ -482,7 +539,7 @@ int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void 
 // In host code the array's name stands for the symbol, not for an address the
 // GPU understands; the address a kernel can use comes from
 // cudaGetSymbolAddress, asked once per device with that device current.
-static __device__ __align__(256) unsigned char g_reduce_static_scratch[kTicketBytes + 8 * kMaxGrid];
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[kScratchPlain];
 
 namespace {
 
@@ -531,7 +588,7 @@ int b2k_reduce_noalloc(int op, int dtype, const void *x_dev, int64_t n, const vo
     // they are read.
     const cudaError_t e = cudaMemsetAsync(scratch, 0, kTicketBytes, b2k::as_stream(stream));
     if (e != cudaSuccess) return b2k::check_cuda(e, "b2k_reduce_noalloc: clearing the ticket");
-    return b2k_reduce(op, dtype, x_dev, n, init_host, out_dev, scratch, b2k_reduce_scratch_bytes(), stream);
+    return b2k_reduce(op, dtype, x_dev, n, init_host, out_dev, scratch, kScratchPlain, stream);
 }
 
 }  // extern "C"

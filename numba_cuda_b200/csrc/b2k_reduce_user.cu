@@ -30,22 +30,46 @@ typedef B2K_W W;
 #define B2K_INF (__longlong_as_double(0x7ff0000000000000LL))
 #define B2K_NAN (__longlong_as_double(0x7ff8000000000000LL))
 
+// Integer operands are 64 bits wide in the expression, as numba types them, but the
+// values of 8-, 16- and 32-bit items rarely leave the 32-bit range: division and
+// remainder test for that at run time and then take the 32-bit instruction
+// sequence, which is several times shorter than the 64-bit one.
 __device__ __forceinline__ long long fdiv_(long long a, long long b) {
     if (b == 0) return 0;
+    if (a == (long long)(int)a && b == (long long)(int)b && b != -1) {
+        const int x = (int)a, y = (int)b;
+        int q = x / y;
+        if ((x % y != 0) && ((x < 0) != (y < 0))) --q;
+        return q;
+    }
     long long q = a / b;
     if ((a % b != 0) && ((a < 0) != (b < 0))) --q;
     return q;
 }
-__device__ __forceinline__ unsigned long long fdiv_(unsigned long long a, unsigned long long b) { return b == 0 ? 0 : a / b; }
+__device__ __forceinline__ unsigned long long fdiv_(unsigned long long a, unsigned long long b) {
+    if (b == 0) return 0;
+    if (((a | b) >> 32) == 0) return (unsigned int)a / (unsigned int)b;
+    return a / b;
+}
 __device__ __forceinline__ double fdiv_(double a, double b) { return floor(a / b); }
 __device__ __forceinline__ float fdiv_(float a, float b) { return floorf(a / b); }
 __device__ __forceinline__ long long mod_(long long a, long long b) {
     if (b == 0) return 0;
+    if (a == (long long)(int)a && b == (long long)(int)b && b != -1) {
+        const int y = (int)b;
+        int r = (int)a % y;
+        if (r != 0 && ((r < 0) != (y < 0))) r += y;
+        return r;
+    }
     long long r = a % b;
     if (r != 0 && ((r < 0) != (b < 0))) r += b;
     return r;
 }
-__device__ __forceinline__ unsigned long long mod_(unsigned long long a, unsigned long long b) { return b == 0 ? 0 : a % b; }
+__device__ __forceinline__ unsigned long long mod_(unsigned long long a, unsigned long long b) {
+    if (b == 0) return 0;
+    if (((a | b) >> 32) == 0) return (unsigned int)a % (unsigned int)b;
+    return a % b;
+}
 __device__ __forceinline__ double mod_(double a, double b) {
     double r = fmod(a, b);
     if (r != 0.0 && ((r < 0.0) != (b < 0.0))) r += b;

@@ -173,22 +173,10 @@ class PeerMailboxes:
         self._ptrs = (ctypes.c_void_p * world)(*ptrs)
         # [0] timed-out flag, [1] local fold done (ns), [2] all peers seen (ns)
         self._status = torch.zeros(3, dtype=torch.int64, device="cuda")
-        self._scratch = {}           # per stream: overlapping reductions must not share a ticket
-
-    def _scratch_for(self, sptr: int) -> torch.Tensor:
-        buf = self._scratch.get(sptr)
-        if buf is None:
-            buf = torch.zeros(int(_lib.lib().b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
-            torch.cuda.current_stream().synchronize()      # zero-filled before any stream uses it
-            self._scratch[sptr] = buf
-        return buf
-
-    @staticmethod
-    def _next_epoch(epoch: int) -> int:
-        epoch += 1
-        if epoch & 0xFFFFFFFF == 0:      # the kernels compare the low 32 bits, and 0 means "never written"
-            epoch += 1
-        return epoch
+        # ONE scratch buffer per communicator: its two ticket/partial sets alternate with the
+        # call counter, so up to two calls may be in flight (on one stream or on several)
+        self._scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+        torch.cuda.current_stream().synchronize()          # zero-filled before any stream uses it
 
     def reduce(self, op, dtype_code, x_ptr, n, init_host, out_ptr, stream=0, input_ready=False):
         """One collective call: launches the fused kernel on this rank.  The epoch
@@ -196,11 +184,10 @@ class PeerMailboxes:
         does not put it out of step with the others."""
         from .devicearray import stream_ptr
         sptr = stream_ptr(stream)
-        scratch = self._scratch_for(sptr)
-        epoch = self._next_epoch(self.epoch)
+        epoch = self.epoch + 1
         _lib.check(_lib.lib().b2k_reduce_peer(
-            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, scratch.data_ptr(),
-            scratch.numel(), self._ptrs, self.world, self.rank, epoch, self.timeout_ns,
+            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, self._scratch.data_ptr(),
+            self._scratch.numel(), self._ptrs, self.world, self.rank, epoch, self.timeout_ns,
             self._status.data_ptr(), _lib.REDUCE_INPUT_READY if input_ready else 0, sptr))
         self.epoch = epoch
 

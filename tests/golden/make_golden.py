@@ -160,7 +160,7 @@ def f32_probe_inputs() -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="root of a numba-cuda source tree")
     args = ap.parse_args()
     if not os.path.isdir(args.reference):
         sys.exit("reference tree not found: fixtures can only be regenerated where it is mounted")

@@ -48,7 +48,7 @@ def new_status():
 def deliver(box, epoch, writer, bits):
     """What rank `writer`'s kernel stores into `box` for call `epoch`."""
     s = box.slot(epoch, writer)
-    tag = (epoch & 0xFFFFFFFF) << 32
+    tag = ((epoch % 0xFFFFFFFF) + 1) << 32
     for k, part in enumerate((bits & 0xFFFFFFFF, (bits >> 32) & 0xFFFFFFFF)):
         word = tag | part
         box.words[s + k] = word - (1 << 64) if word >= (1 << 63) else word
@@ -57,11 +57,11 @@ def deliver(box, epoch, writer, bits):
 def delivered(box, epoch, writer, itemsize):
     s = box.slot(epoch, writer)
     w0 = int(box.words[s].item()) & (2 ** 64 - 1)
-    assert w0 >> 32 == epoch & 0xFFFFFFFF
+    assert w0 >> 32 == (epoch % 0xFFFFFFFF) + 1
     bits = w0 & 0xFFFFFFFF
     if itemsize > 4:
         w1 = int(box.words[s + 1].item()) & (2 ** 64 - 1)
-        assert w1 >> 32 == epoch & 0xFFFFFFFF
+        assert w1 >> 32 == (epoch % 0xFFFFFFFF) + 1
         bits |= (w1 & 0xFFFFFFFF) << 32
     return bits
 
@@ -83,7 +83,7 @@ def test_world_of_one_equals_plain_reduce():
     x = torch.randint(-2 ** 31, 2 ** 31 - 1, (1 << 20,), dtype=torch.int32, device="cuda")
     out = torch.zeros(1, dtype=torch.int32, device="cuda")
     init = np.array([-5], dtype=np.int32)
-    for epoch in (1, 2, 3, (1 << 32) + 1):
+    for epoch in (1, 2, 3, 4, 5):
         for flags in (0, _lib.REDUCE_INPUT_READY):
             call_peer(_lib.MAX, _lib.I32, x, init, [box], 1, 0, epoch, 0, status, scratch, out, flags)
             assert out.item() == max(int(x.max().item()), -5) and status[0].item() == 0
@@ -143,19 +143,52 @@ def test_wait_that_runs_out_sets_status_and_returns():
     torch.cuda.synchronize()
     assert status[0].item() == 1
     assert (status[2] - status[1]).item() >= 2_000_000
-    # a word of the wrong epoch (a call two steps back) does not count either
-    deliver(mine, 3, 1, 99)
+    # a word of another epoch (a call two steps on, same slot) does not count either
+    deliver(mine, 4, 1, 99)
+    torch.cuda.synchronize()
+    status.zero_()
+    call_peer(_lib.ADD, _lib.I32, x, init, [mine, theirs], 2, 0, 2, 2_000_000, status, scratch, out)
+    torch.cuda.synchronize()
+    assert status[0].item() == 1
+    # a call whose scratch set was never released by the call two epochs back (epoch 5 after
+    # 1 and 2: nothing ran as 3) gives up on that too, and says which wait it was
+    deliver(mine, 5, 1, 7)
     torch.cuda.synchronize()
     status.zero_()
     call_peer(_lib.ADD, _lib.I32, x, init, [mine, theirs], 2, 0, 5, 2_000_000, status, scratch, out)
     torch.cuda.synchronize()
-    assert status[0].item() == 1
+    assert status[0].item() == 2 and out.item() == 1007      # the fold itself still completed
     # the context is intact and the scratch reusable
     status.zero_()
     plain = torch.zeros(1, dtype=torch.int32, device="cuda")
     assert L.b2k_reduce(_lib.ADD, _lib.I32, x.data_ptr(), x.numel(), init.ctypes.data, plain.data_ptr(),
                         scratch.data_ptr(), scratch.numel(), torch.cuda.current_stream().cuda_stream) == 0
     assert plain.item() == 1000
+    mine.close(); theirs.close()
+
+
+def test_epochs_across_the_tag_wrap():
+    """The 32-bit tag of an epoch is (epoch mod (2^32 - 1)) + 1; a communicator that has made
+    four billion calls runs through the wrap.  The scratch is prepared as those calls would
+    have left it (the markers of the two sets name the two preceding epochs)."""
+    L = _lib.lib()
+    mine, theirs = Mailbox(), Mailbox()
+    scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    markers = scratch[64:80].view(torch.int64)
+    first = (1 << 32) - 4
+    markers[(first - 2) & 1] = first - 2
+    markers[(first - 1) & 1] = first - 1
+    status = new_status()
+    x = torch.arange(1, 5001, dtype=torch.int64, device="cuda")
+    out = torch.zeros(1, dtype=torch.int64, device="cuda")
+    init = np.array([0], dtype=np.int64)
+    for epoch in range(first, first + 8):
+        deliver(mine, epoch, 1, 1_000_000_000_000 + epoch)          # an 8-byte value: two words
+        torch.cuda.synchronize()
+        call_peer(_lib.ADD, _lib.I64, x, init, [mine, theirs], 2, 0, epoch, 0, status, scratch, out,
+                  _lib.REDUCE_INPUT_READY)
+        assert out.item() == 5000 * 5001 // 2 + 1_000_000_000_000 + epoch and status[0].item() == 0
+        assert delivered(theirs, epoch, 0, 8) == 5000 * 5001 // 2
     mine.close(); theirs.close()
 
 
@@ -176,8 +209,8 @@ def test_argument_checks():
                              4096, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 0, 0,
                              4096, 0, None) == _lib.ERR_INVALID_ARG
-    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 1 << 32, 0,
-                             4096, 0, None) == _lib.ERR_INVALID_ARG          # low 32 bits of the epoch are zero
+    assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 40000, ptrs, 1, 0, 1, 0,
+                             4096, 0, None) == _lib.ERR_SCRATCH              # needs both halves of the scratch
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 17, 0, 1, 0,
                              4096, 0, None) == _lib.ERR_INVALID_ARG
     assert L.b2k_reduce_peer(_lib.ADD, _lib.I32, 4096, 4, init.ctypes.data, 8192, 256, 1 << 20, ptrs, 1, 0, 1, 0,

@@ -94,3 +94,33 @@ def test_large_input_and_cache():
 def test_trace_output_is_plain_cpp():
     assert trace_functor(mod_add) == "b2k_mod((a + b), B2K_ILIT(1000003LL))"
     assert trace_functor(lambda a, b: a if a < b else b) == "((a < b) ? a : b)"
+
+
+def test_floor_remainder_on_the_32_bit_and_the_64_bit_instruction_paths():
+    rng = np.random.default_rng(10)
+    # operands within 32 bits, negative modulus: Python's sign rule, short path
+    x = rng.integers(-10 ** 6, 10 ** 6, size=40001).astype(np.int32)
+    neg_mod = lambda a, b: (a + b) % -1009                 # noqa: E731
+    assert cuda.reduce(neg_mod)(x) == int(x.astype(np.int64).sum()) % -1009
+    # the same remainder spelled with floor division
+    via_div = lambda a, b: (a + b) - ((a + b) // 1009) * 1009   # noqa: E731
+    assert cuda.reduce(via_div)(x) == int(x.astype(np.int64).sum()) % 1009
+    # operands far outside 32 bits: the 64-bit path
+    big = rng.integers(-2 ** 45, 2 ** 45, size=30011, dtype=np.int64)
+    big_mod = lambda a, b: (a + b) % 1000000007            # noqa: E731
+    assert cuda.reduce(big_mod)(big, init=3) == (sum(int(v) for v in big) + 3) % 1000000007
+    # a divisor of -1 (the one case the 32-bit instructions cannot take)
+    minus_one = lambda a, b: (a + b) % -1                  # noqa: E731
+    assert cuda.reduce(minus_one)(x[:1000]) == 0
+    u = rng.integers(0, 2 ** 32, size=20001, dtype=np.uint64).astype(np.uint32)
+    assert cuda.reduce(lambda a, b: (a + b) % 65521)(u) == int(u.astype(np.uint64).sum()) % 65521
+
+
+def test_unsigned_items_follow_the_integer_rule():
+    """uint32 - uint32 is a uint64 that wraps, and comparing it with the signed 0 is done
+    by value (numba's typing of the same function): a - b > 0 holds whenever a != b."""
+    u = np.random.default_rng(11).integers(0, 2 ** 32, size=100003, dtype=np.uint64).astype(np.uint32)
+    fn = lambda a, b: max(a, b) if a - b > 0 else min(a, b)      # noqa: E731
+    assert cuda.reduce(fn)(u) == u.max()
+    s = u.astype(np.int64).astype(np.int32)                      # signed items: a - b > 0 only when a > b
+    assert cuda.reduce(lambda a, b: a if a - b > 0 else b)(s) == s.max()
