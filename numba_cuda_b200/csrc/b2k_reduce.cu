@@ -228,6 +228,13 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
     // instructions do nothing in a launch without the programmatic attribute.
     asm volatile("griddepcontrol.launch_dependents;");
     if (!input_ready) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // cross-GPU calls: the marker that frees this call's scratch set is normally in place
+    // long before the kernel starts; looking at it now keeps that round trip to L2 off the
+    // end of the CTA's life
+    unsigned long long marker_seen = 0;
+    if constexpr (PEER) {
+        if (threadIdx.x == 0) marker_seen = load_acquire_gpu(link.marker);
+    }
 
     const uintptr_t addr = reinterpret_cast<uintptr_t>(x);
     int64_t head = static_cast<int64_t>(((32u - (addr & 31u)) & 31u) / sizeof(T));
@@ -297,7 +304,9 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
             // overwritten once that call's folding block has read them
             const unsigned long long want = link.epoch > 2 ? link.epoch - 2 : 0;
             unsigned long long t0 = 0;
-            for (unsigned int spin = 0; load_acquire_gpu(link.marker) < want; ++spin) {
+            for (unsigned int spin = 0; marker_seen < want; ++spin) {
+                marker_seen = load_acquire_gpu(link.marker);
+                if (marker_seen >= want) break;
                 if (spin == 64) t0 = global_timer_ns();
                 if (spin > 64) {
                     if (global_timer_ns() - t0 > link.timeout_ns) { link.status[0] = 2; break; }
@@ -306,13 +315,15 @@ reduce_kernel(const T *__restrict__ x, int64_t n, T init, T *__restrict__ out,
             }
         }
         partials[blockIdx.x] = total;
-        __threadfence();
-        const unsigned int t = atomicInc(ticket, gridDim.x - 1);
+        // the ticket: an increment that wraps to zero with the last CTA.  It releases the
+        // partial just written and acquires the partials of the CTAs that came before.
+        unsigned int t;
+        asm volatile("atom.acq_rel.gpu.global.inc.u32 %0, [%1], %2;"
+                     : "=r"(t) : "l"(ticket), "r"(gridDim.x - 1) : "memory");
         is_last = (t == gridDim.x - 1);
     }
-    __syncthreads();
+    __syncthreads();   // carries thread 0's acquire to the whole block
     if (!is_last) return;
-    __threadfence();
     T mine = Op::template identity<T>();
     for (unsigned int i = threadIdx.x; i < gridDim.x; i += THREADS)
         mine = Op::template apply<T>(mine, __ldcg(partials + i));
