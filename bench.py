@@ -54,7 +54,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the reduce kernel over
 # 2^28 int32, from an ncu capture of this kernel (traffic grows with the bytes read, so
 # a shard's launch is charged its share)
-REDUCE_TRAFFIC_BYTES_2P28 = 1081083744
+REDUCE_TRAFFIC_BYTES_2P28 = 1077902920
 # executed thread-instructions per sample of the RNG fill kernels, from ncu
 # (smsp__thread_inst_executed.sum / samples) on 2^21 generators
 RNG_INSTR_PER_SAMPLE = {"c4_rng_generate_64u32_16n64": 48.0, "rng_uniform_f32_only_64": 22.0}
