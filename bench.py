@@ -748,6 +748,21 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
                       iters, warm)
         res["reduce_sum_f64_2p28"] = _roof(n2 * 8, ms, peak)
         del x, y
+        # a user function outside the op table: traced, compiled at run time around the same reduce skeleton
+        n3 = 1 << (28 - scale)
+        w = torch.randint(0, 1000003, (n3,), dtype=torch.int32, device="cuda")
+        out32 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        zero32 = np.zeros(1, dtype=np.int32)
+        expr = cuda.Reduce(lambda a, b: (a + b) % 1000003)._compile(np.dtype(np.int32))
+        assert isinstance(expr, str)
+        ms, _ = timed(lambda: check(L.b2k_reduce_expr(expr.encode(), _lib.I32, w.data_ptr(), n3, zero32.ctypes.data,
+                                                      out32.data_ptr(), scratch.data_ptr(), scratch.numel(), sptr)),
+                      iters, warm)
+        res["user_reduce_mod_add_int32_2p28"] = dict(
+            _roof(n3 * 4, ms, peak), expression=expr,
+            spot_check=bool(int(out32.item()) == int(w.sum(dtype=torch.int64).item()) % 1000003),
+            note="numba's typing: the sum and the remainder are 64-bit operations")
+        del w
 
     for name, rows, cols, tdt, item in (("c3a_transpose_f32_32768x32768", 32768, 32768, torch.float32, 4),
                                         ("c3b_transpose_bf16_16384x65536", 16384, 65536, torch.bfloat16, 2)):

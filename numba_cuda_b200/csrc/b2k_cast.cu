@@ -436,6 +436,13 @@ struct Bf16ToFp8 {
     __device__ static OutS one(InS h) {
         return F32ToFp8<E5M2, SAT>::one(__uint_as_float(static_cast<uint32_t>(h) << 16));
     }
+    // two codes at once, `a` in the low byte: one packed cvt in the saturating mode
+    __device__ static uint32_t pair(InS a, InS b) {
+        const float fa = __uint_as_float(static_cast<uint32_t>(a) << 16);
+        const float fb = __uint_as_float(static_cast<uint32_t>(b) << 16);
+        if constexpr (SAT) return E5M2 ? pack2_e5m2_sat(fb, fa) : pack2_e4m3_sat(fb, fa);
+        else return f32_to_fp8_nosat<E5M2>(fa) | (f32_to_fp8_nosat<E5M2>(fb) << 8);
+    }
 };
 // f64 -> e8m0: __nv_cvt_double_to_e8m0 (cuda_fp8.hpp:772-806).  The double is rounded
 // to float "to odd" (a sticky bit for everything discarded lands in the last place),
@@ -472,7 +479,11 @@ template <typename C> struct HasPair<C, std::void_t<decltype(&C::pair)>> : std::
 
 template <typename C>
 struct WideOf {
-    static constexpr int ELEMS = (sizeof(typename C::InS) == 8 || sizeof(typename C::OutS) == 8) ? 4 : 8;
+    // elements per thread: the wider side moves as one 256-bit access (128-bit when an
+    // 8-byte type is involved, to keep the narrow side at 32 bits or more)
+    static constexpr int WIDER = sizeof(typename C::InS) > sizeof(typename C::OutS) ? sizeof(typename C::InS)
+                                                                                     : sizeof(typename C::OutS);
+    static constexpr int ELEMS = WIDER == 8 ? 4 : 32 / WIDER;
     using In = typename VecOf<ELEMS * sizeof(typename C::InS)>::type;
     using Out = typename VecOf<ELEMS * sizeof(typename C::OutS)>::type;
     __device__ static Out convert(const In &v) {
