@@ -50,3 +50,17 @@ def c5_chunks(chunks: int = C5_CHUNKS, chunk: int = C5_CHUNK):
 def c3_normals(rows: int, cols: int) -> np.ndarray:
     """Configuration 3: ``default_rng(2).standard_normal((rows, cols), float32)``."""
     return np.random.default_rng(2).standard_normal((rows, cols), dtype=np.float32)
+
+
+def block_checksums(a: np.ndarray, rows_per_block: int = 4096) -> np.ndarray:
+    """Three 64-bit checksums of the BIT PATTERNS of every block of ``rows_per_block`` rows of
+    a 2-D float array: xor, wrap-around sum, and wrap-around sum weighted by position (odd
+    weights, so that two values changing places show).  Shape ``(blocks, 3)``, uint64."""
+    rows = a.shape[0]
+    assert rows % rows_per_block == 0
+    bits = np.ascontiguousarray(a).view(np.uint32 if a.dtype.itemsize == 4 else np.uint64)
+    bits = bits.reshape(rows // rows_per_block, -1).astype(np.uint64)
+    weights = (np.arange(bits.shape[1], dtype=np.uint64) << np.uint64(1)) | np.uint64(1)
+    with np.errstate(over="ignore"):
+        return np.stack([np.bitwise_xor.reduce(bits, axis=1), np.add.reduce(bits, axis=1, dtype=np.uint64),
+                         np.add.reduce(bits * weights, axis=1, dtype=np.uint64)], axis=1)

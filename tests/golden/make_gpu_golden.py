@@ -11,9 +11,13 @@ GPU; it writes next to itself or to ``$1``::
 
     python tests/golden/make_gpu_golden.py [output.npz]
 
+Writes ``output.npz`` (256 generators, every value) and ``output_checksums.npz`` (2^20
+generators, block checksums of the bit patterns).
+
 Also prints timings of the stock kernels (cuda.reduce, transpose, RNG) for context.
 """
 import json
+import os
 import sys
 import time
 
@@ -75,6 +79,33 @@ def main():
     normal64_kernel[(n + 127) // 128, 128](st, o, 32)
     res["normal_f64"] = o.copy_to_host().reshape(n, 32)
     np.savez_compressed(out_path, **res)
+
+    # The same three kernels over 2^20 generators, kept as block checksums of the bit
+    # patterns (tests/config_inputs.py:block_checksums): a bit-level pin of 2^26 uniforms
+    # and 2^24 + 2 * 2^25 normals in a few kilobytes.
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+    from config_inputs import block_checksums
+    big = 1 << 20
+    sums = {"generators": np.int64(big), "rows_per_block": np.int64(4096)}
+    st = create_xoroshiro128p_states(big, seed=42)
+    u = cuda.device_array(big * 64, dtype=np.float32)
+    z = cuda.device_array(big * 16, dtype=np.float64)
+    c4_kernel[(big + 127) // 128, 128](st, u, z, 64, 16)
+    sums["c4_u"] = block_checksums(u.copy_to_host().reshape(big, 64))
+    sums["c4_z"] = block_checksums(z.copy_to_host().reshape(big, 16))
+    e = st.copy_to_host()
+    sums["c4_end"] = block_checksums(np.stack([e["s0"], e["s1"]], axis=1).view(np.float64))
+    del u, z
+    st = create_xoroshiro128p_states(big, seed=42)
+    o = cuda.device_array(big * 32, dtype=np.float32)
+    normal32_kernel[(big + 127) // 128, 128](st, o, 32)
+    sums["normal_f32"] = block_checksums(o.copy_to_host().reshape(big, 32))
+    st = create_xoroshiro128p_states(big, seed=42)
+    o = cuda.device_array(big * 32, dtype=np.float64)
+    normal64_kernel[(big + 127) // 128, 128](st, o, 32)
+    sums["normal_f64"] = block_checksums(o.copy_to_host().reshape(big, 32))
+    del o
+    np.savez_compressed(out_path.replace(".npz", "_checksums.npz"), **sums)
 
     # context timings of the stock kernels on this GPU (not fixtures)
     def timeit(fn, reps=5):

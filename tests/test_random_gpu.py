@@ -189,6 +189,29 @@ def test_normals_bit_exact_vs_gpu_reference(golden_dir):
     assert xoroshiro128p_fill(st, "normal", count=32, dtype=np.float64).copy_to_host().tobytes() == g["normal_f64"].tobytes()
 
 
+def test_normals_bit_exact_over_2p20_generators_by_checksum(golden_dir):
+    """The same GPU reference over 2^20 generators, kept as checksums of the bit patterns
+    of every block of 4096 generators (tests/golden/make_gpu_golden.py): 2^26 uniforms,
+    2^24 fused normals and 2 x 2^25 normals of the single-kind kernels, every bit."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from config_inputs import block_checksums
+    path = os.path.join(golden_dir, "gpu_normals_reference_checksums.npz")
+    if not os.path.exists(path):
+        pytest.skip("checksum fixture not generated")
+    g = np.load(path)
+    n, rows = int(g["generators"]), int(g["rows_per_block"])
+    st = create_xoroshiro128p_states(n, 42, 0)
+    u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
+    assert np.array_equal(block_checksums(u.copy_to_host(), rows), g["c4_u"])
+    assert np.array_equal(block_checksums(z.copy_to_host(), rows), g["c4_z"])
+    assert np.array_equal(block_checksums(pairs(st.copy_to_host()).view(np.float64), rows), g["c4_end"])
+    for dtype, key in ((np.float32, "normal_f32"), (np.float64, "normal_f64")):
+        st = create_xoroshiro128p_states(n, 42, 0)
+        got = xoroshiro128p_fill(st, "normal", count=32, dtype=dtype).copy_to_host()
+        assert np.array_equal(block_checksums(got, rows), g[key]), key
+
+
 def test_fused_config4_sequence_small(gold):
     st = create_xoroshiro128p_states(8, 42, 0)
     u, z = xoroshiro128p_fill(st, "uniform", count=64, dtype=np.float32, then=("normal", 16, np.float64))
