@@ -78,7 +78,7 @@ def test_config4_2p24_generators_vs_oracle():
     host = oracle.init_states(n, seed, 0)                 # the serial chain of random.py:242-257
     got = states.copy_to_host()
     assert got.tobytes() == host.tobytes()
-    # the survey's known answers for seed 42
+    # known answers for seed 42 (obtained by executing the reference's CPU-jitted functions)
     assert int(got[0]["s0"]) == int(got[0]["s1"]) == 0xBDD732262FEB6E95
     assert (int(got[1]["s0"]), int(got[1]["s1"])) == (313611670190079035, 410834281257317300)
     assert (int(got[(1 << 20) - 1]["s0"]), int(got[(1 << 20) - 1]["s1"])) == \
