@@ -271,11 +271,13 @@ def main():
     scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
     out = torch.zeros(1, dtype=torch.int32, device="cuda")
     ident = np.array([-2 ** 31], dtype=np.int32)
+    ident_ptr, out_ptr = ident.ctypes.data, out.data_ptr()
+    copy_ptrs = [c._ptr for c in copies]
     turn = [0]
 
     def next_copy():
-        turn[0] = (turn[0] + 1) % len(copies)
-        return copies[turn[0]]._ptr
+        turn[0] = (turn[0] + 1) % len(copy_ptrs)
+        return copy_ptrs[turn[0]]
 
     def check(rc):
         if rc:
@@ -296,7 +298,7 @@ def main():
 
     def step_pipelined():
         if boxes is not None:
-            boxes.reduce(_lib.MAX, _lib.I32, next_copy(), n_shard, ident, out.data_ptr(), sptr, input_ready=True)
+            boxes.reduce(_lib.MAX, _lib.I32, next_copy(), n_shard, ident_ptr, out_ptr, sptr, input_ready=True)
         elif distributed:
             step_nccl()
         else:
@@ -305,7 +307,7 @@ def main():
 
     def step_unpipelined():
         if boxes is not None:
-            boxes.reduce(_lib.MAX, _lib.I32, next_copy(), n_shard, ident, out.data_ptr(), sptr)
+            boxes.reduce(_lib.MAX, _lib.I32, next_copy(), n_shard, ident_ptr, out_ptr, sptr)
         else:
             kernel_only()
 

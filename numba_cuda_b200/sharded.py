@@ -177,18 +177,26 @@ class PeerMailboxes:
         # call counter, so up to two calls may be in flight (on one stream or on several)
         self._scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
         torch.cuda.current_stream().synchronize()          # zero-filled before any stream uses it
+        self._launch = L.b2k_reduce_peer
+        self._scratch_ptr, self._scratch_bytes = self._scratch.data_ptr(), self._scratch.numel()
+        self._status_ptr = self._status.data_ptr()
 
     def reduce(self, op, dtype_code, x_ptr, n, init_host, out_ptr, stream=0, input_ready=False):
         """One collective call: launches the fused kernel on this rank.  The epoch
         advances only when the launch was accepted, so an argument error on one rank
-        does not put it out of step with the others."""
-        from .devicearray import stream_ptr
-        sptr = stream_ptr(stream)
+        does not put it out of step with the others.  ``init_host`` is a one-element
+        NumPy array or the address of one; ``stream`` a stream object or its handle
+        (plain integers keep the per-call cost of a tight loop of launches down)."""
+        if not isinstance(stream, int):
+            from .devicearray import stream_ptr
+            stream = stream_ptr(stream)
+        init_ptr = init_host if isinstance(init_host, int) else init_host.ctypes.data
         epoch = self.epoch + 1
-        _lib.check(_lib.lib().b2k_reduce_peer(
-            op, dtype_code, x_ptr, n, init_host.ctypes.data, out_ptr, self._scratch.data_ptr(),
-            self._scratch.numel(), self._ptrs, self.world, self.rank, epoch, self.timeout_ns,
-            self._status.data_ptr(), _lib.REDUCE_INPUT_READY if input_ready else 0, sptr))
+        rc = self._launch(op, dtype_code, x_ptr, n, init_ptr, out_ptr, self._scratch_ptr, self._scratch_bytes,
+                          self._ptrs, self.world, self.rank, epoch, self.timeout_ns, self._status_ptr,
+                          _lib.REDUCE_INPUT_READY if input_ready else 0, stream)
+        if rc:
+            _lib.check(rc)
         self.epoch = epoch
 
     def exchange_ns(self) -> int:
