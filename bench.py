@@ -232,7 +232,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(fn, steps, warmup):
+    by_rank = {}
+
+    def timed(fn, steps, warmup, label=None):
         """CUDA-event time per step on the launching stream, max over ranks (ms)."""
         for _ in range(max(warmup, 3)):
             fn()
@@ -245,7 +247,12 @@ def main():
         e1.record(stream)
         barrier()
         launches = L.b2k_launch_count() - before
-        return max_over_ranks(e0.elapsed_time(e1) / steps), launches
+        mine = e0.elapsed_time(e1) / steps
+        if label and distributed:
+            every = torch.empty(world, dtype=torch.float64, device="cuda")
+            dist.all_gather_into_tensor(every, torch.tensor([mine], dtype=torch.float64, device="cuda"))
+            by_rank[label] = [round(v * 1e3, 2) for v in every.cpu().tolist()]
+        return max_over_ranks(mine), launches
 
     peak, peak_kind = measured_peak()
 
@@ -325,7 +332,7 @@ def main():
     # alone lasts only a few milliseconds, less than one nvidia-smi sample)
     clocks = ClockSampler(local_rank)
     clocks.__enter__()
-    ms_step, launches = timed(step_pipelined, args.steps, args.warmup)
+    ms_step, launches = timed(step_pipelined, args.steps, args.warmup, "step_us")
     verify("pipelined step")
 
     variants = {}
@@ -333,7 +340,7 @@ def main():
     if distributed:
         verify("unpipelined step")
     # the kernel alone (roofline): the same launches on this rank's shard, no combine
-    ms_kernel, _ = timed(kernel_only, args.steps, 3)
+    ms_kernel, _ = timed(kernel_only, args.steps, 3, "kernel_us")
     shard_bytes = n_shard * 4
     total_bytes = N_C2 * 4
 
@@ -345,6 +352,16 @@ def main():
         "note": "the same step with every kernel waiting for the one before (no programmatic overlap)"}
     exchange = None
     if distributed:
+        # every rank alone: the same pipelined launches without any exchange (what a kernel
+        # boundary costs by itself on a shard of this size)
+        def step_alone():
+            check(L.b2k_reduce_ex(_lib.MAX, _lib.I32, next_copy(), n_shard, ident_ptr, out_ptr,
+                                  scratch.data_ptr(), scratch.numel(), _lib.REDUCE_INPUT_READY, sptr))
+        ms_alone, _ = timed(step_alone, args.steps, 3, "alone_us")
+        variants["c2_pipelined_no_exchange"] = {
+            "GBps": gbs(ms_alone), "ms": ms_alone,
+            "note": "every rank reduces its shard with the same pipelined launches and no combine (not a valid "
+                    "result for the job: shows what the exchange adds)"}
         ms_nccl, _ = timed(step_nccl, args.steps, 3)
         verify("nccl step")
         variants["c2_nccl"] = {"GBps": gbs(ms_nccl), "ms": ms_nccl,
@@ -398,6 +415,8 @@ def main():
     }
     if exchange is not None:
         line["exchange_us"] = exchange
+    if by_rank:
+        line["us_by_rank"] = by_rank
 
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline(host)
