@@ -10,7 +10,8 @@ import functools
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libb2k.so")
+#: B2K_LIBRARY names another build of the library (comparing two builds side by side)
+LIB_PATH = os.environ.get("B2K_LIBRARY") or os.path.join(_HERE, "csrc", "libb2k.so")
 
 # enums of include/b2k.h
 I8, I16, I32, I64, U8, U16, U32, U64, F32, F64 = range(10)

@@ -201,6 +201,128 @@ reduce_cols_kernel(const unsigned char *__restrict__ x, int64_t rows, int64_t pa
     }
 }
 
+// A second form of the same kernel, kept beside the first because neither wins everywhere
+// (GB/s read, first form / this form with runs / this form with dealt blocks): float32
+// 16384^2 6422 / 6104 / 6474, float64 8192x16384 6938 / 5058 / 6428, uint8 32768^2 6714 /
+// 6122 / 4776 -- but one column tile (2^22 x 64 float32) 5379 / 6627 / 5549, few rows
+// (64 x 2^22) 6751 / 7126 / 6770, rows of 8-byte packs (2^20 x 250 float32) 4496 / 5344 /
+// 6627.  The launcher picks by shape.  With INTERLEAVE the rows go to the chunks in blocks
+// of ny * kUnroll rows dealt round robin, so the CTAs that run at the same time sweep one
+// window of consecutive rows; without it a chunk is one run of rows, as in the first form
+// (same loop; the two differ in what the compiler makes of it).
+template <typename T, typename Op, int V, bool INTERLEAVE>
+__global__ void __launch_bounds__(kThreads)
+reduce_cols_dealt_kernel(const unsigned char *__restrict__ x, int64_t rows, int64_t packs, int64_t pitch, int lx_log2,
+                   int64_t rows_per_chunk, T init, Pack<T, V> *__restrict__ out, Pack<T, V> *__restrict__ partials,
+                   unsigned int *__restrict__ tickets, int64_t slab_bytes) {
+    __shared__ Pack<T, V> lanes[kThreads];
+    __shared__ bool is_last;
+    // blockIdx.z numbers the matrices of a batch: `slab_bytes` apart on the input side,
+    // one output row, one block of partial rows and one run of tickets each
+    x += static_cast<int64_t>(blockIdx.z) * slab_bytes;
+    out += static_cast<int64_t>(blockIdx.z) * packs;
+    partials += static_cast<int64_t>(blockIdx.z) * gridDim.y * packs;
+    tickets += static_cast<int64_t>(blockIdx.z) * gridDim.x;
+    const int lx = 1 << lx_log2;
+    const int tx = threadIdx.x & (lx - 1), ty = threadIdx.x >> lx_log2, ny = kThreads >> lx_log2;
+    const int64_t pack = static_cast<int64_t>(blockIdx.x) * lx + tx;
+    Pack<T, V> acc[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) acc[u] = identity_pack<T, Op, V>();
+    if (pack < packs) {
+        const unsigned char *col = x + pack * static_cast<int64_t>(V * sizeof(T));
+        if constexpr (INTERLEAVE) {
+            const int64_t block_rows = static_cast<int64_t>(ny) * kUnroll;
+            for (int64_t base = static_cast<int64_t>(blockIdx.y) * block_rows; base < rows;
+                 base += static_cast<int64_t>(gridDim.y) * block_rows) {
+                const int64_t r = base + ty;
+                if (base + block_rows <= rows) {
+                    Pack<T, V> v[kUnroll];
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) v[u] = load_pack<T, V>(col + (r + u * ny) * pitch);
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u) fold_into<T, Op, V>(acc[u], v[u]);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < kUnroll; ++u)
+                        if (r + u * ny < rows) fold_into<T, Op, V>(acc[u], load_pack<T, V>(col + (r + u * ny) * pitch));
+                }
+            }
+        } else {
+            const int64_t r0 = static_cast<int64_t>(blockIdx.y) * rows_per_chunk;
+            const int64_t r1 = (r0 + rows_per_chunk < rows) ? r0 + rows_per_chunk : rows;
+            int64_t r = r0 + ty;
+            for (; r + (kUnroll - 1) * ny < r1; r += kUnroll * ny) {
+                Pack<T, V> v[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) v[u] = load_pack<T, V>(col + (r + u * ny) * pitch);
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) fold_into<T, Op, V>(acc[u], v[u]);
+            }
+            for (; r < r1; r += ny) fold_into<T, Op, V>(acc[0], load_pack<T, V>(col + r * pitch));
+        }
+    }
+#pragma unroll
+    for (int u = 1; u < kUnroll; ++u) fold_into<T, Op, V>(acc[0], acc[u]);
+
+    lanes[threadIdx.x] = acc[0];
+    __syncthreads();
+    for (int s = ny >> 1; s >= 1; s >>= 1) {
+        if (ty < s) {
+            Pack<T, V> mine = lanes[threadIdx.x];
+            fold_into<T, Op, V>(mine, lanes[threadIdx.x + s * lx]);
+            lanes[threadIdx.x] = mine;
+        }
+        __syncthreads();
+    }
+    const bool owner = ty == 0 && pack < packs;
+    const unsigned int chunks = gridDim.y;
+    if (chunks == 1) {
+        if (owner) {
+            Pack<T, V> total = lanes[threadIdx.x];
+#pragma unroll
+            for (int k = 0; k < V; ++k) total.e[k] = Op::template apply<T>(total.e[k], init);
+            out[pack] = total;
+        }
+        return;
+    }
+    if (owner) partials[static_cast<int64_t>(blockIdx.y) * packs + pack] = lanes[threadIdx.x];
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicInc(&tickets[blockIdx.x], chunks - 1) == chunks - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // the last CTA folds the partial rows: row lanes take chunks ty, ty + ny, ..., then
+    // the same shared-memory tree as above
+    Pack<T, V> total = identity_pack<T, Op, V>();
+    if (pack < packs) {
+        for (unsigned int c = ty; c < chunks; c += ny) {
+            const Pack<T, V> *src = partials + static_cast<int64_t>(c) * packs + pack;
+            Pack<T, V> v;
+#pragma unroll
+            for (int k = 0; k < V; ++k) v.e[k] = __ldcg(&src->e[k]);
+            fold_into<T, Op, V>(total, v);
+        }
+    }
+    lanes[threadIdx.x] = total;
+    __syncthreads();
+    for (int s = ny >> 1; s >= 1; s >>= 1) {
+        if (ty < s) {
+            Pack<T, V> mine = lanes[threadIdx.x];
+            fold_into<T, Op, V>(mine, lanes[threadIdx.x + s * lx]);
+            lanes[threadIdx.x] = mine;
+        }
+        __syncthreads();
+    }
+    if (owner) {
+        total = lanes[threadIdx.x];
+#pragma unroll
+        for (int k = 0; k < V; ++k) total.e[k] = Op::template apply<T>(total.e[k], init);
+        out[pack] = total;
+    }
+}
+
 // ---- axis 1 ----------------------------------------------------------------------
 // Fold of packs [first, last) of one row by `width` cooperating lanes.
 template <typename T, typename Op, int V>
@@ -373,7 +495,13 @@ int launch_planned(const Plan &p, const void *x, int64_t rows, int64_t pitch, in
     if (axis == 0) {
         if (p.tiles > 0x7FFFFFFFll) return b2k::fail(B2K_ERR_TOO_LARGE, "b2k_reduce_axis: too many columns");
         const dim3 grid(static_cast<unsigned>(p.tiles), static_cast<unsigned>(p.chunks), static_cast<unsigned>(batch));
-        reduce_cols_kernel<T, Op, V><<<grid, kThreads, 0, stream>>>(
+        // which form: see the note above reduce_cols_dealt_kernel
+        const int form = B2K_ENV_INT("B2K_AXIS0_FORM", -1);
+        const int pick = form >= 0 ? form : (p.pack_bytes < 16 && p.pack_bytes > static_cast<int64_t>(sizeof(T))) ? 2
+                                            : (p.tiles == 1 || rows <= 256) ? 1 : 0;
+        auto kernel = pick == 2 ? reduce_cols_dealt_kernel<T, Op, V, true>
+                      : pick == 1 ? reduce_cols_dealt_kernel<T, Op, V, false> : reduce_cols_kernel<T, Op, V>;
+        kernel<<<grid, kThreads, 0, stream>>>(
             src, rows, p.packs, pitch, p.lx_log2, p.rows_per_chunk, init, static_cast<Pack<T, V> *>(out),
             reinterpret_cast<Pack<T, V> *>(sc + p.ticket_bytes), reinterpret_cast<unsigned int *>(sc), slab_bytes);
     } else if (p.split) {
