@@ -82,6 +82,26 @@ def test_argument_errors_are_reported_on_host():
     assert L.b2k_reduce_axis_scratch_bytes(1 << 20, 8, _lib.F32, 0) > 16384
     assert L.b2k_reduce_axis_scratch_bytes(64, 64, _lib.F32, 1) == 0
     assert L.b2k_reduce_axis_scratch_bytes(64, 64, 99, 1) == 0
+    # a batch of matrices reduced along their rows, the flags of b2k_reduce_ex, the new cast pairs
+    assert L.b2k_reduce_cols_batched(_lib.ADD, _lib.F32, 1024, 70000, 4, 4, 16, 64, init.ctypes.data, 2048, None, 0,
+                                     None) == _lib.ERR_TOO_LARGE
+    assert L.b2k_reduce_cols_batched(_lib.ADD, _lib.F32, 1024, 3, 4, 4, 16, -64, init.ctypes.data, 2048, None, 0,
+                                     None) == _lib.ERR_INVALID_ARG
+    assert L.b2k_reduce_cols_batched(_lib.ADD, _lib.F32, 1024, 3, 4, 4, 16, 66, init.ctypes.data, 2048, None, 0,
+                                     None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_reduce_cols_batched(_lib.ADD, _lib.F32, 1024, 4, 1 << 20, 8, 32, 1 << 25, init.ctypes.data, 2048,
+                                     None, 0, None) == _lib.ERR_SCRATCH
+    assert L.b2k_reduce_cols_batched(_lib.ADD, _lib.F32, None, 0, 4, 4, 16, 64, init.ctypes.data, None, None, 0,
+                                     None) == 0                                                   # no matrices
+    assert L.b2k_reduce_cols_batched_scratch_bytes(4, 1 << 20, 8, _lib.F32) > \
+        L.b2k_reduce_axis_scratch_bytes(1 << 20, 8, _lib.F32, 0)
+    assert L.b2k_reduce_ex(_lib.ADD, _lib.F64, 1024, 4, init.ctypes.data, 8, 256, 1 << 20, 2, None) == _lib.ERR_INVALID_ARG
+    assert b"flag" in L.b2k_last_error()
+    assert L.b2k_reduce(_lib.ADD, _lib.F64, 1024, 4, init.ctypes.data, 8, 256, 1000, None) == _lib.ERR_SCRATCH
+    assert L.b2k_cast_ex(_lib.FMT_F64, _lib.FMT_E4M3, 1, _lib.ROUND_ZERO, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_F64, _lib.FMT_E4M3, 1, _lib.ROUND_NEAREST, 1028, 2048, 16, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_cast_ex(_lib.FMT_F64, _lib.FMT_E8M0, 1, _lib.ROUND_NEAREST, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_BF16, _lib.FMT_E5M2, 0, _lib.ROUND_NEAREST, None, None, 0, None) == 0
     # empty work is a no-op that needs no device
     assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, None, None, 0, None) == 0
     assert L.b2k_transpose2d(None, None, 0, 4, 16, 4, 0, 4, 4, None) == 0
