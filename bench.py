@@ -943,7 +943,22 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
         ms, _ = timed(lambda: check(L.b2k_cast_ex(_lib.FMT_BF16, _lib.FMT_E4M3, 1, 0, hb.data_ptr(), e.data_ptr(), n,
                                                   sptr)), iters, warm)
         res["n1_cast_bf16_to_e4m3"] = _roof(n * 3, ms, peak)
-        del x, e, hb
+        del hb
+        # integer sides: int32(fp8_e4m3) over the codes just written, fp8_e4m3(int32) and
+        # int32_to_bfloat16_rn over the same integers
+        ni = n // 2
+        iv = torch.empty(ni, dtype=torch.int32, device="cuda")
+        ms, _ = timed(lambda: check(L.b2k_cast_ex(_lib.FMT_E4M3, _lib.FMT_I32, 1, _lib.ROUND_ZERO, e.data_ptr(),
+                                                  iv.data_ptr(), ni, sptr)), iters, warm)
+        res["n1_cast_e4m3_to_int32"] = dict(_roof(ni * 5, ms, peak), elements=ni)
+        ms, _ = timed(lambda: check(L.b2k_cast_ex(_lib.FMT_I32, _lib.FMT_E4M3, 1, 0, iv.data_ptr(), e.data_ptr(), ni,
+                                                  sptr)), iters, warm)
+        res["n1_cast_int32_to_e4m3"] = dict(_roof(ni * 5, ms, peak), elements=ni)
+        hb = torch.empty(ni, dtype=torch.bfloat16, device="cuda")
+        ms, _ = timed(lambda: check(L.b2k_cast_ex(_lib.FMT_I32, _lib.FMT_BF16, 1, 0, iv.data_ptr(), hb.data_ptr(), ni,
+                                                  sptr)), iters, warm)
+        res["n1_cast_int32_to_bf16"] = dict(_roof(ni * 6, ms, peak), elements=ni)
+        del x, e, hb, iv
     torch.cuda.empty_cache()
     return res
 

@@ -57,7 +57,11 @@ enum b2k_op {
 /* storage formats (cast) */
 enum b2k_format {
     B2K_FMT_F32 = 0, B2K_FMT_BF16 = 1, B2K_FMT_E4M3 = 2, B2K_FMT_E5M2 = 3,
-    B2K_FMT_F64 = 4, B2K_FMT_F16 = 5, B2K_FMT_E8M0 = 6   /* b2k_cast_ex only */
+    B2K_FMT_F64 = 4, B2K_FMT_F16 = 5, B2K_FMT_E8M0 = 6,  /* b2k_cast_ex only */
+    /* integer sides of b2k_cast_ex; BOOL is one byte holding 0 or 1 */
+    B2K_FMT_I8 = 7, B2K_FMT_I16 = 8, B2K_FMT_I32 = 9, B2K_FMT_I64 = 10,
+    B2K_FMT_U8 = 11, B2K_FMT_U16 = 12, B2K_FMT_U32 = 13, B2K_FMT_U64 = 14,
+    B2K_FMT_BOOL = 15
 };
 
 /* rounding modes (b2k_cast_ex), numbered like cudaRoundMode */
@@ -307,7 +311,30 @@ B2K_API int b2k_cast(int src_format, int dst_format, int saturate, const void *i
  *                       include/12/cuda_fp8.hpp:546-589, :689-740)
  *   e8m0 -> bf16, e8m0 -> f32 : cvt_e8m0_to_bf16raw, float(fp8_e8m0)
  *                      (cuda_fp8.hpp:817-851)
- *   f32 <-> f16      : round to nearest even */
+ *   f32 <-> f16      : round to nearest even
+ *   f64 -> e4m3/e5m2, bf16 -> e4m3/e5m2 : cvt_double_to_fp8 (one rounding from the
+ *                      double), cvt_bfloat16raw_to_fp8 (cuda_fp8.py:3269-3338,
+ *                      :3413-3446; cuda_fp8.hpp:119-229, :442-450)
+ *   f64 -> e8m0      : cvt_double_to_e8m0 (cuda_fp8.py:3557-3590; cuda_fp8.hpp:772-806)
+ * and the conversions with an integer side (formats B2K_FMT_I8 .. B2K_FMT_U64,
+ * B2K_FMT_BOOL):
+ *   int16/32/64, uint16/32/64 <-> bf16 in all four rounding modes, bf16 -> int8 /
+ *   uint8 toward zero : int16_to_bfloat16_rn ... bfloat16_to_uint64_ru,
+ *                      bfloat16_to_int8_rz (numba/cuda/bf16.py:213-263;
+ *                      cuda_bf16.hpp:641-1500).  To an integer: saturating, NaN
+ *                      gives 0 (0x8000000000000000 in 64 bits)
+ *   any integer -> e4m3/e5m2 (saturate = 1, nearest) and -> e8m0 (saturate = 1,
+ *   B2K_ROUND_POS_INF) : the constructors fp8_e4m3(int) ... fp8_e8m0(uint64)
+ *                      (cuda_fp8.py:568-613, :1562-1607, :2580-2601;
+ *                       cuda_fp8.hpp:955-1023, :1568-1636, :2160-2215)
+ *   e4m3/e5m2/e8m0 -> any integer (B2K_ROUND_ZERO) and -> bool : the conversion
+ *                      operators int32(fp8_e4m3) ... (cuda_fp8.py:616-926,
+ *                      :1610-1944, :2604-2962; cuda_fp8.hpp:1065-1263, :1678-1876,
+ *                      :2305-2494)
+ *   e4m3/e5m2 -> f16/bf16/f64, e8m0 -> f16/f64, f16 -> e4m3/e5m2 (either
+ *   saturation), f16 -> e8m0 : the value types' floating-point neighbours
+ *                      (cuda_fp8.hpp:363-388, :473-523, :1031-1063, :2260-2300)
+ * A pair or a mode outside this list returns B2K_ERR_UNSUPPORTED. */
 B2K_API int b2k_cast_ex(int src_format, int dst_format, int saturate, int rounding, const void *in_dev,
                         void *out_dev, int64_t n, void *stream);
 

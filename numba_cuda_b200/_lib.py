@@ -17,6 +17,7 @@ LIB_PATH = os.environ.get("B2K_LIBRARY") or os.path.join(_HERE, "csrc", "libb2k.
 I8, I16, I32, I64, U8, U16, U32, U64, F32, F64 = range(10)
 ADD, MUL, MAX, MIN, AND, OR, XOR = range(7)
 FMT_F32, FMT_BF16, FMT_E4M3, FMT_E5M2, FMT_F64, FMT_F16, FMT_E8M0 = range(7)
+FMT_I8, FMT_I16, FMT_I32, FMT_I64, FMT_U8, FMT_U16, FMT_U32, FMT_U64, FMT_BOOL = range(7, 16)
 ROUND_NEAREST, ROUND_ZERO, ROUND_POS_INF, ROUND_MIN_INF = range(4)
 UNIFORM_F32, UNIFORM_F64, NORMAL_F32, NORMAL_F64 = range(4)
 

@@ -464,6 +464,174 @@ struct F64ToE8m0 {
     }
 };
 
+// ---- integer formats -------------------------------------------------------------
+// The fp8 value types are constructed from and converted to every integer type
+// (cuda_fp8.hpp:955-1023, :1065-1263 for E5M2; :1568-1636, :1678-1876 for E4M3;
+// :2160-2215, :2305-2494 for E8M0), and bf16 converts from and to the 16-, 32-
+// and 64-bit integers in all four rounding modes (numba/cuda/bf16.py:213-263 =
+// cuda_bf16.hpp:641-1500).  Each is one or two cvt instructions; float-to-integer
+// cvt saturates at the ends of the integer range and turns a NaN into 0 (into
+// 0x8000000000000000 for a 64-bit result), which is what the headers' host paths
+// spell out with comparisons.
+template <typename I> struct IntPtx;
+#define B2K_INT_PTX(I, REG, SUFFIX, CONS)                                                          \
+    template <> struct IntPtx<I> {                                                                 \
+        template <int MODE> __device__ static uint16_t to_bf16(I v) {                              \
+            uint16_t r;                                                                            \
+            const REG x = static_cast<REG>(v);                                                     \
+            if constexpr (MODE == 1) asm("cvt.rz.bf16." SUFFIX " %0, %1;" : "=h"(r) : CONS(x));    \
+            else if constexpr (MODE == 2) asm("cvt.rp.bf16." SUFFIX " %0, %1;" : "=h"(r) : CONS(x)); \
+            else if constexpr (MODE == 3) asm("cvt.rm.bf16." SUFFIX " %0, %1;" : "=h"(r) : CONS(x)); \
+            else asm("cvt.rn.bf16." SUFFIX " %0, %1;" : "=h"(r) : CONS(x));                        \
+            return r;                                                                              \
+        }                                                                                          \
+        template <int MODE> __device__ static I from_bf16(uint16_t h) {                            \
+            REG r;                                                                                 \
+            if constexpr (MODE == 1) asm("cvt.rzi." SUFFIX ".bf16 %0, %1;" : "=" CONS(r) : "h"(h)); \
+            else if constexpr (MODE == 2) asm("cvt.rpi." SUFFIX ".bf16 %0, %1;" : "=" CONS(r) : "h"(h)); \
+            else if constexpr (MODE == 3) asm("cvt.rmi." SUFFIX ".bf16 %0, %1;" : "=" CONS(r) : "h"(h)); \
+            else asm("cvt.rni." SUFFIX ".bf16 %0, %1;" : "=" CONS(r) : "h"(h));                    \
+            return static_cast<I>(r);                                                              \
+        }                                                                                          \
+        __device__ static I from_f16_rz(uint16_t h) {                                              \
+            REG r;                                                                                 \
+            asm("cvt.rzi." SUFFIX ".f16 %0, %1;" : "=" CONS(r) : "h"(h));                          \
+            return static_cast<I>(r);                                                              \
+        }                                                                                          \
+    };
+B2K_INT_PTX(int16_t, short, "s16", "h")
+B2K_INT_PTX(uint16_t, unsigned short, "u16", "h")
+B2K_INT_PTX(int32_t, int, "s32", "r")
+B2K_INT_PTX(uint32_t, unsigned int, "u32", "r")
+B2K_INT_PTX(int64_t, long long, "s64", "l")
+B2K_INT_PTX(uint64_t, unsigned long long, "u64", "l")
+#undef B2K_INT_PTX
+// the 8-bit results: convert to 32 bits, then clamp (a NaN has become 0 by then)
+template <> struct IntPtx<int8_t> {
+    template <int MODE> __device__ static int8_t from_bf16(uint16_t h) {
+        const int v = IntPtx<int32_t>::from_bf16<MODE>(h);
+        return static_cast<int8_t>(v < -128 ? -128 : v > 127 ? 127 : v);
+    }
+    __device__ static int8_t from_f16_rz(uint16_t h) {
+        const int v = IntPtx<int32_t>::from_f16_rz(h);
+        return static_cast<int8_t>(v < -128 ? -128 : v > 127 ? 127 : v);
+    }
+};
+template <> struct IntPtx<uint8_t> {
+    template <int MODE> __device__ static uint8_t from_bf16(uint16_t h) {
+        const unsigned int v = IntPtx<uint32_t>::from_bf16<MODE>(h);
+        return static_cast<uint8_t>(v > 255u ? 255u : v);
+    }
+    __device__ static uint8_t from_f16_rz(uint16_t h) {
+        const unsigned int v = IntPtx<uint32_t>::from_f16_rz(h);
+        return static_cast<uint8_t>(v > 255u ? 255u : v);
+    }
+};
+
+template <typename I, int MODE>
+struct IntToBf16 {
+    using InS = I; using OutS = uint16_t;
+    __device__ static OutS one(InS v) { return IntPtx<I>::template to_bf16<MODE>(v); }
+};
+template <typename I, int MODE>
+struct Bf16ToInt {
+    using InS = uint16_t; using OutS = I;
+    __device__ static OutS one(InS h) { return IntPtx<I>::template from_bf16<MODE>(h); }
+};
+// fp8_e4m3(int) / fp8_e5m2(int): the integer rounded to float32, then the saturating
+// float conversion
+template <typename I, bool E5M2>
+struct IntToFp8 {
+    using InS = I; using OutS = uint8_t;
+    __device__ static OutS one(InS v) { return F32ToFp8<E5M2, true>::one(static_cast<float>(v)); }
+};
+// fp8_e8m0(int): the smallest power of two that is not below |v| (the constructors
+// go through float, double or a bf16 bumped up by one place, all to that effect):
+// |v| rounded up to float32, then the float conversion rounding up, saturating
+template <typename I>
+struct IntToE8m0 {
+    using InS = I; using OutS = uint8_t;
+    __device__ static OutS one(InS v) {
+        unsigned long long mag;
+        if constexpr (std::is_signed<I>::value) {
+            const long long w = static_cast<long long>(v);
+            mag = w < 0 ? 0ull - static_cast<unsigned long long>(w) : static_cast<unsigned long long>(w);
+        } else {
+            mag = static_cast<unsigned long long>(v);
+        }
+        return F32ToE8m0<true, true>::one(__ull2float_ru(mag));
+    }
+};
+// int(fp8_e4m3) etc.: the code widened to half (exact), then cvt toward zero
+template <typename I, bool E5M2>
+struct Fp8ToInt {
+    using InS = uint8_t; using OutS = I;
+    __device__ static OutS one(InS c) {
+        const uint32_t h = E5M2 ? fp8x2_to_f16x2_e5m2(c) : fp8x2_to_f16x2_e4m3(c);
+        return IntPtx<I>::from_f16_rz(static_cast<uint16_t>(h));
+    }
+};
+template <typename I>
+struct E8m0ToInt {
+    using InS = uint8_t; using OutS = I;
+    __device__ static OutS one(InS e) { return IntPtx<I>::template from_bf16<1>(E8m0ToBf16::one(e)); }
+};
+// bool(fp8): anything but a zero of either sign; an E8M0 code is never zero
+template <int FORMAT>
+struct Fp8ToBool {
+    using InS = uint8_t; using OutS = uint8_t;
+    __device__ static OutS one(InS c) { return FORMAT == B2K_FMT_E8M0 ? 1u : ((c & 0x7Fu) != 0u ? 1u : 0u); }
+};
+// the remaining floating-point neighbours of the value types
+template <bool E5M2>
+struct Fp8ToF16 {  // __nv_cvt_fp8_to_halfraw (cuda_fp8.hpp:473-523)
+    using InS = uint8_t; using OutS = uint16_t;
+    __device__ static OutS one(InS c) {
+        return static_cast<OutS>(E5M2 ? fp8x2_to_f16x2_e5m2(c) : fp8x2_to_f16x2_e4m3(c));
+    }
+};
+template <bool E5M2>
+struct Fp8ToBf16 {  // __float2bfloat16_rz(float(fp8)): every fp8 value is a bf16 value
+    using InS = uint8_t; using OutS = uint16_t;
+    __device__ static OutS one(InS c) { return F32ToBf16Mode<1>::one(Fp8ToF32<E5M2>::one(c)); }
+};
+template <bool E5M2>
+struct Fp8ToF64 {
+    using InS = uint8_t; using OutS = double;
+    __device__ static OutS one(InS c) { return static_cast<double>(Fp8ToF32<E5M2>::one(c)); }
+};
+struct E8m0ToF64 {
+    using InS = uint8_t; using OutS = double;
+    __device__ static OutS one(InS e) {
+        double d;   // written as a cvt so that no flush-to-zero mode can touch 2^-127
+        asm("cvt.f64.f32 %0, %1;" : "=d"(d) : "f"(E8m0ToF32::one(e)));
+        return d;
+    }
+};
+struct E8m0ToF16 {  // __float2half_rn(float(fp8_e8m0)): beyond 2^15 it is infinity, below 2^-25 zero
+    using InS = uint8_t; using OutS = uint16_t;
+    __device__ static OutS one(InS e) { return F32ToF16::one(E8m0ToF32::one(e)); }
+};
+template <bool E5M2, bool SAT>
+struct F16ToFp8 {  // __nv_cvt_halfraw_to_fp8 (cuda_fp8.hpp:363-388)
+    using InS = uint16_t; using OutS = uint8_t;
+    __device__ static OutS one(InS h) {
+        if constexpr (SAT) {
+            uint16_t r;
+            if constexpr (E5M2) asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(r) : "r"(static_cast<uint32_t>(h)));
+            else asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(static_cast<uint32_t>(h)));
+            return static_cast<OutS>(r);
+        } else {
+            return static_cast<OutS>(f32_to_fp8_nosat<E5M2>(f16bits_to_f32(h)));
+        }
+    }
+};
+template <bool UP, bool SAT>
+struct F16ToE8m0 {  // fp8_e8m0(half): through float
+    using InS = uint16_t; using OutS = uint8_t;
+    __device__ static OutS one(InS h) { return F32ToE8m0<UP, SAT>::one(f16bits_to_f32(h)); }
+};
+
 template <int BYTES> struct VecOf;
 template <> struct VecOf<4> { using type = uint32_t; };
 template <> struct VecOf<8> { using type = uint2; };
@@ -543,6 +711,128 @@ int launch_generic(const void *in, void *out, int64_t n, cudaStream_t stream) {
     return B2K_OK;
 }
 
+// ---- dispatch of the integer formats ----------------------------------------------
+inline bool is_int_format(int f) { return f >= B2K_FMT_I8 && f <= B2K_FMT_U64; }
+
+// `CALL` is an expression that names the integer type as `I`
+#define B2K_FOR_WIDE_INT(FMT, CALL)                                         \
+    switch (FMT) {                                                          \
+        case B2K_FMT_I16: { using I = int16_t; return CALL; }               \
+        case B2K_FMT_I32: { using I = int32_t; return CALL; }               \
+        case B2K_FMT_I64: { using I = int64_t; return CALL; }               \
+        case B2K_FMT_U16: { using I = uint16_t; return CALL; }              \
+        case B2K_FMT_U32: { using I = uint32_t; return CALL; }              \
+        case B2K_FMT_U64: { using I = uint64_t; return CALL; }              \
+        default: break;                                                     \
+    }
+#define B2K_FOR_ANY_INT(FMT, CALL)                                          \
+    switch (FMT) {                                                          \
+        case B2K_FMT_I8: { using I = int8_t; return CALL; }                 \
+        case B2K_FMT_U8: { using I = uint8_t; return CALL; }                \
+        default: break;                                                     \
+    }                                                                       \
+    B2K_FOR_WIDE_INT(FMT, CALL)
+
+template <int MODE>
+int int_to_bf16(int src, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_WIDE_INT(src, (launch_generic<IntToBf16<I, MODE>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+template <int MODE>
+int bf16_to_int(int dst, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_WIDE_INT(dst, (launch_generic<Bf16ToInt<I, MODE>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+template <bool E5M2>
+int int_to_fp8(int src, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_ANY_INT(src, (launch_generic<IntToFp8<I, E5M2>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+int int_to_e8m0(int src, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_ANY_INT(src, (launch_generic<IntToE8m0<I>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+template <bool E5M2>
+int fp8_to_int(int dst, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_ANY_INT(dst, (launch_generic<Fp8ToInt<I, E5M2>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+int e8m0_to_int(int dst, const void *in, void *out, int64_t n, cudaStream_t s) {
+    B2K_FOR_ANY_INT(dst, (launch_generic<E8m0ToInt<I>>(in, out, n, s)))
+    return B2K_ERR_UNSUPPORTED;
+}
+
+// Conversions with an integer or bool side, and the half / bfloat16 / double
+// neighbours of the fp8 value types.  Returns B2K_ERR_UNSUPPORTED (without a
+// message) for a pair or a mode that is not one of them.
+int cast_value_types(int src, int dst, bool sat, int rounding, const void *in, void *out, int64_t n,
+                     cudaStream_t s) {
+    const bool nearest = rounding == B2K_ROUND_NEAREST;
+    const bool e8_mode = rounding == B2K_ROUND_ZERO || rounding == B2K_ROUND_POS_INF;
+    if (is_int_format(src) && dst == B2K_FMT_BF16) {
+        switch (rounding) {
+            case B2K_ROUND_ZERO: return int_to_bf16<1>(src, in, out, n, s);
+            case B2K_ROUND_POS_INF: return int_to_bf16<2>(src, in, out, n, s);
+            case B2K_ROUND_MIN_INF: return int_to_bf16<3>(src, in, out, n, s);
+            default: return int_to_bf16<0>(src, in, out, n, s);
+        }
+    }
+    if (src == B2K_FMT_BF16 && is_int_format(dst)) {
+        if (dst == B2K_FMT_I8 && rounding == B2K_ROUND_ZERO) return launch_generic<Bf16ToInt<int8_t, 1>>(in, out, n, s);
+        if (dst == B2K_FMT_U8 && rounding == B2K_ROUND_ZERO) return launch_generic<Bf16ToInt<uint8_t, 1>>(in, out, n, s);
+        switch (rounding) {
+            case B2K_ROUND_ZERO: return bf16_to_int<1>(dst, in, out, n, s);
+            case B2K_ROUND_POS_INF: return bf16_to_int<2>(dst, in, out, n, s);
+            case B2K_ROUND_MIN_INF: return bf16_to_int<3>(dst, in, out, n, s);
+            default: return bf16_to_int<0>(dst, in, out, n, s);
+        }
+    }
+    // constructors of the value types from integers: saturating, to nearest
+    // (E4M3 / E5M2) or up to the next power of two (E8M0)
+    if (is_int_format(src) && sat) {
+        if (dst == B2K_FMT_E4M3 && nearest) return int_to_fp8<false>(src, in, out, n, s);
+        if (dst == B2K_FMT_E5M2 && nearest) return int_to_fp8<true>(src, in, out, n, s);
+        if (dst == B2K_FMT_E8M0 && rounding == B2K_ROUND_POS_INF) return int_to_e8m0(src, in, out, n, s);
+    }
+    // conversion operators of the value types to integers: toward zero
+    if (is_int_format(dst) && rounding == B2K_ROUND_ZERO) {
+        if (src == B2K_FMT_E4M3) return fp8_to_int<false>(dst, in, out, n, s);
+        if (src == B2K_FMT_E5M2) return fp8_to_int<true>(dst, in, out, n, s);
+        if (src == B2K_FMT_E8M0) return e8m0_to_int(dst, in, out, n, s);
+    }
+    if (dst == B2K_FMT_BOOL) {
+        if (src == B2K_FMT_E4M3) return launch_generic<Fp8ToBool<B2K_FMT_E4M3>>(in, out, n, s);
+        if (src == B2K_FMT_E5M2) return launch_generic<Fp8ToBool<B2K_FMT_E5M2>>(in, out, n, s);
+        if (src == B2K_FMT_E8M0) return launch_generic<Fp8ToBool<B2K_FMT_E8M0>>(in, out, n, s);
+    }
+    if (nearest) {
+        if (src == B2K_FMT_E4M3 && dst == B2K_FMT_F16) return launch_generic<Fp8ToF16<false>>(in, out, n, s);
+        if (src == B2K_FMT_E5M2 && dst == B2K_FMT_F16) return launch_generic<Fp8ToF16<true>>(in, out, n, s);
+        if (src == B2K_FMT_E4M3 && dst == B2K_FMT_BF16) return launch_generic<Fp8ToBf16<false>>(in, out, n, s);
+        if (src == B2K_FMT_E5M2 && dst == B2K_FMT_BF16) return launch_generic<Fp8ToBf16<true>>(in, out, n, s);
+        if (src == B2K_FMT_E4M3 && dst == B2K_FMT_F64) return launch_generic<Fp8ToF64<false>>(in, out, n, s);
+        if (src == B2K_FMT_E5M2 && dst == B2K_FMT_F64) return launch_generic<Fp8ToF64<true>>(in, out, n, s);
+        if (src == B2K_FMT_E8M0 && dst == B2K_FMT_F64) return launch_generic<E8m0ToF64>(in, out, n, s);
+        if (src == B2K_FMT_E8M0 && dst == B2K_FMT_F16) return launch_generic<E8m0ToF16>(in, out, n, s);
+        if (src == B2K_FMT_F16 && dst == B2K_FMT_E4M3)
+            return sat ? launch_generic<F16ToFp8<false, true>>(in, out, n, s)
+                       : launch_generic<F16ToFp8<false, false>>(in, out, n, s);
+        if (src == B2K_FMT_F16 && dst == B2K_FMT_E5M2)
+            return sat ? launch_generic<F16ToFp8<true, true>>(in, out, n, s)
+                       : launch_generic<F16ToFp8<true, false>>(in, out, n, s);
+    }
+    if (src == B2K_FMT_F16 && dst == B2K_FMT_E8M0 && e8_mode) {
+        if (rounding == B2K_ROUND_POS_INF)
+            return sat ? launch_generic<F16ToE8m0<true, true>>(in, out, n, s)
+                       : launch_generic<F16ToE8m0<true, false>>(in, out, n, s);
+        return sat ? launch_generic<F16ToE8m0<false, true>>(in, out, n, s)
+                   : launch_generic<F16ToE8m0<false, false>>(in, out, n, s);
+    }
+    return B2K_ERR_UNSUPPORTED;
+}
+#undef B2K_FOR_WIDE_INT
+#undef B2K_FOR_ANY_INT
+
 }  // namespace
 
 extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void *out_dev,
@@ -573,8 +863,9 @@ extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const v
     cudaStream_t s = b2k::as_stream(stream);
     const bool sat = saturate != 0;
     // the nearest-even pairs of b2k_cast
-    if (rounding == B2K_ROUND_NEAREST && src <= B2K_FMT_E5M2 && dst <= B2K_FMT_E5M2 &&
-        !(src == B2K_FMT_BF16 && dst >= B2K_FMT_E4M3))
+    if (rounding == B2K_ROUND_NEAREST &&
+        ((src == B2K_FMT_F32 && dst >= B2K_FMT_BF16 && dst <= B2K_FMT_E5M2) ||
+         (dst == B2K_FMT_F32 && src >= B2K_FMT_BF16 && src <= B2K_FMT_E5M2)))
         return b2k_cast(src, dst, saturate, in_dev, out_dev, n, stream);
     if (src == B2K_FMT_F32 && dst == B2K_FMT_BF16) {
         if (rounding == B2K_ROUND_ZERO) return launch_generic<F32ToBf16Mode<1>>(in_dev, out_dev, n, s);
@@ -623,6 +914,10 @@ extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const v
         if (src == B2K_FMT_E8M0 && dst == B2K_FMT_F32) return launch_generic<E8m0ToF32>(in_dev, out_dev, n, s);
         if (src == B2K_FMT_F32 && dst == B2K_FMT_F16) return launch_generic<F32ToF16>(in_dev, out_dev, n, s);
         if (src == B2K_FMT_F16 && dst == B2K_FMT_F32) return launch_generic<F16ToF32>(in_dev, out_dev, n, s);
+    }
+    {
+        const int rc = cast_value_types(src, dst, sat, rounding, in_dev, out_dev, n, s);
+        if (rc != B2K_ERR_UNSUPPORTED) return rc;
     }
     return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_cast_ex: no conversion from format %d to %d with rounding %d", src,
                      dst, rounding);

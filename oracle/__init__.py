@@ -30,6 +30,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 xoroshiro128p_dtype = np.dtype([("s0", np.uint64), ("s1", np.uint64)], align=True)
 
 F32, BF16, E4M3, E5M2, F64, F16, E8M0 = 0, 1, 2, 3, 4, 5, 6
+I8, I16, I32, I64, U8, U16, U32, U64, BOOL = 7, 8, 9, 10, 11, 12, 13, 14, 15
 RN, RZ, RU, RD = 0, 1, 2, 3   # cudaRoundMode order: nearest, zero, +inf, -inf
 OPS = {"add": 0, "mul": 1, "max": 2, "min": 3}
 
@@ -159,6 +160,11 @@ def ref_headers() -> ctypes.CDLL:
     L.ref_bulk_fp8_to_f32.argtypes = [vp, vp, i64, i32, i32]
     L.ref_bulk_f32_to_bf16.argtypes = [vp, vp, i64, i32]
     L.ref_bulk_bf16_to_f32.argtypes = [vp, vp, i64, i32]
+    L.ref_bulk_value_from.argtypes = [i32, i32, vp, vp, i64, i32]
+    L.ref_bulk_value_to.argtypes = [i32, i32, vp, vp, i64, i32]
+    L.ref_bulk_f16_to_fp8.argtypes = [vp, vp, i64, i32, i32, i32]
+    L.ref_bulk_int_to_bf16_rn.argtypes = [i32, vp, vp, i64]
+    L.ref_bulk_bf16_to_int_rz.argtypes = [i32, vp, vp, i64]
     return L
 
 
@@ -220,7 +226,9 @@ def next_u64(state_pair):
 
 # ---------------------------------------------------------------- casts
 _CODE_DTYPE = {F32: np.float32, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8, F64: np.float64,
-               F16: np.float16, E8M0: np.uint8}
+               F16: np.float16, E8M0: np.uint8, I8: np.int8, I16: np.int16, I32: np.int32, I64: np.int64,
+               U8: np.uint8, U16: np.uint16, U32: np.uint32, U64: np.uint64, BOOL: np.uint8}
+INT_FORMATS = (I8, I16, I32, I64, U8, U16, U32, U64)
 
 
 def cast(x: np.ndarray, src: int, dst: int, sat: int = 1) -> np.ndarray:
@@ -270,6 +278,168 @@ def ref_cast(x: np.ndarray, src: int, dst: int, sat: int = 1, threads: int = 0, 
         R.ref_bulk_f64_to_e8m0(_ptr(x), _ptr(out), x.size, sat, mode, threads)
     else:
         raise ValueError(f"unsupported cast {src}->{dst}")
+    return out
+
+
+# ---------------------------------------------------------------- fp8 value types, bf16 <-> integers
+def fp8_values(fmt: int) -> np.ndarray:
+    """The 256 values of a one-byte format as float64 (NaN where the code is one):
+    E4M3 has no infinities and one NaN per sign (0x7F / 0xFF), E5M2 is IEEE-like,
+    E8M0 is 2**(code-127) with 0xFF the NaN (cuda_fp8.hpp:473-523, :817-851)."""
+    code = np.arange(256)
+    if fmt == E8M0:
+        v = np.ldexp(1.0, code - 127)
+        v[255] = np.nan
+        return v
+    mbits = 3 if fmt == E4M3 else 2
+    bias = 7 if fmt == E4M3 else 15
+    sign = np.where(code & 0x80, -1.0, 1.0)
+    e = (code & 0x7F) >> mbits
+    m = (code & ((1 << mbits) - 1)).astype(np.float64) / (1 << mbits)
+    v = np.where(e == 0, np.ldexp(m, 1 - bias), np.ldexp(1.0 + m, e - bias))
+    if fmt == E4M3:
+        v = np.where((code & 0x7F) == 0x7F, np.nan, v)
+    else:
+        v = np.where(e == 31, np.where(m == 0, np.inf, np.nan), v)
+    return sign * v
+
+
+def _float_to_int(v: np.ndarray, dst: int, mode: int = RZ) -> np.ndarray:
+    """Float64 values to an integer type the way a cvt does it: rounded in the given
+    direction, clamped to the ends of the range; a NaN gives 0 in a result of up to
+    32 bits and 0x8000000000000000 in one of 64 (cuda_fp8.hpp:1065-1263,
+    cuda_bf16.hpp:653-678)."""
+    dtype = np.dtype(_CODE_DTYPE[dst])
+    info = np.iinfo(dtype)
+    rounded = {RN: np.rint, RZ: np.trunc, RU: np.ceil, RD: np.floor}[mode](v)
+    nan = np.isnan(v)
+    top = rounded >= float(info.max)       # float(max) is max+1 for the 64-bit types: still the right cut
+    bottom = rounded <= float(info.min)
+    safe = np.where(nan | top | bottom, 0.0, rounded)
+    out = safe.astype(dtype)
+    out[top] = info.max
+    out[bottom] = info.min
+    out[nan] = (dtype.type(info.min) if dtype.kind == "i" else dtype.type(1 << 63)) if dtype.itemsize == 8 else 0
+    return out
+
+
+def value_to(codes: np.ndarray, fmt: int, dst: int) -> np.ndarray:
+    """Conversion operators of fp8_e4m3 / fp8_e5m2 / fp8_e8m0 (cuda_fp8.hpp:1031-1263,
+    :1644-1876, :2260-2494): to f16 / bf16 (raw bits) / f32 / f64, to the integer types
+    (toward zero, saturating, NaN as above) and to bool (any non-zero code; always true
+    for E8M0)."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    table = fp8_values(fmt)
+    if dst == BOOL:
+        flags = np.ones(256, np.uint8) if fmt == E8M0 else ((np.arange(256) & 0x7F) != 0).astype(np.uint8)
+        return flags[codes]
+    if dst in INT_FORMATS:
+        return _float_to_int(table, dst)[codes]
+    if dst == F64:
+        return table[codes]
+    if dst == F32:
+        return table.astype(np.float32)[codes]
+    if dst == F16:
+        with np.errstate(over="ignore"):
+            return table.astype(np.float16)[codes]   # E8M0: to nearest, beyond 2**15 infinity
+    if dst == BF16:
+        return (table.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)[codes]   # every value fits
+    raise ValueError(f"unsupported conversion {fmt}->{dst}")
+
+
+def value_from(x: np.ndarray, src: int, fmt: int) -> np.ndarray:
+    """Constructors of the fp8 value types (cuda_fp8.hpp:918-1023, :1531-1636, :2118-2215).
+    E4M3 / E5M2: saturating, to nearest even; an integer is rounded to float32 first.
+    E8M0: saturating, up to the next power of two; for an integer that is
+    ceil(log2(|v|))."""
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    if fmt in (E4M3, E5M2):
+        if src in INT_FORMATS:
+            return cast(x.astype(np.float32), F32, fmt, 1)
+        if src == F16:
+            return cast(x.astype(np.float32), F32, fmt, 1)
+        return cast_ex(x, src, fmt, 1, RN) if src in (F64, BF16) else cast(x, src, fmt, 1)
+    if src in INT_FORMATS:
+        zero = int(cast_ex(np.zeros(1, np.float32), F32, E8M0, 1, RU)[0])
+        flat = [int(v) for v in x.reshape(-1)]
+        codes = [zero if v == 0 else 127 + (abs(v) - 1).bit_length() for v in flat]
+        return np.array(codes, dtype=np.uint8).reshape(x.shape)
+    if src == F16:
+        return cast_ex(x.astype(np.float32), F32, E8M0, 1, RU)
+    return cast_ex(x, src, E8M0, 1, RU)
+
+
+def int_to_bf16(x: np.ndarray, src: int, mode: int = RN) -> np.ndarray:
+    """An integer rounded to bfloat16 (8 significant bits) in one step, in the
+    direction asked for: nearest even, toward zero, toward +inf, toward -inf
+    (cuda_bf16.hpp:714-738, :807-837 and the 16- and 64-bit siblings)."""
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    out = np.empty(x.size, dtype=np.uint16)
+    for i, v in enumerate(int(t) for t in x.reshape(-1)):
+        neg, mag = v < 0, abs(v)
+        if mag == 0:
+            out[i] = 0
+            continue
+        k = mag.bit_length()
+        if k <= 8:
+            q = mag << (8 - k)
+        else:
+            shift = k - 8
+            q, rem = mag >> shift, mag & ((1 << shift) - 1)
+            half = 1 << (shift - 1)
+            up = (rem > half or (rem == half and (q & 1))) if mode == RN else \
+                 False if mode == RZ else (rem != 0 and neg == (mode == RD))
+            q += int(up)
+            if q == 256:
+                q, k = 128, k + 1
+        out[i] = (int(neg) << 15) | ((126 + k) << 7) | (q & 0x7F)
+    return out.reshape(x.shape)
+
+
+def bf16_to_int(bits: np.ndarray, dst: int, mode: int = RZ) -> np.ndarray:
+    """bfloat16 (raw bits) to an integer type: rounded in the direction asked for,
+    saturating, NaN to 0 (0x8000000000000000 for 64 bits) (cuda_bf16.hpp:641-712 and
+    siblings)."""
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    with np.errstate(invalid="ignore"):     # signalling NaN patterns are converted like the others
+        values = (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    return _float_to_int(values, dst, mode)
+
+
+def ref_value_from(x: np.ndarray, src: int, fmt: int, threads: int = 0) -> np.ndarray:
+    """Constructors of the value types through the reference's own header (host path)."""
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    out = np.empty(x.shape, dtype=np.uint8)
+    ref_headers().ref_bulk_value_from(src, fmt, _ptr(x), _ptr(out), x.size, threads)
+    return out
+
+
+def ref_value_to(codes: np.ndarray, fmt: int, dst: int, threads: int = 0) -> np.ndarray:
+    """Conversion operators of the value types through the reference's own header."""
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    out = np.empty(codes.shape, dtype=_CODE_DTYPE[dst] if dst != F16 else np.uint16)
+    ref_headers().ref_bulk_value_to(fmt, dst, _ptr(codes), _ptr(out), codes.size, threads)
+    return out.view(np.float16) if dst == F16 else out
+
+
+def ref_f16_to_fp8(x: np.ndarray, fmt: int, sat: int = 1, threads: int = 0) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    out = np.empty(x.shape, dtype=np.uint8)
+    ref_headers().ref_bulk_f16_to_fp8(_ptr(x), _ptr(out), x.size, sat, fmt - 2, threads)
+    return out
+
+
+def ref_int_to_bf16_rn(x: np.ndarray, src: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=_CODE_DTYPE[src])
+    out = np.empty(x.shape, dtype=np.uint16)
+    ref_headers().ref_bulk_int_to_bf16_rn(src, _ptr(x), _ptr(out), x.size)
+    return out
+
+
+def ref_bf16_to_int_rz(bits: np.ndarray, dst: int) -> np.ndarray:
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    out = np.empty(bits.shape, dtype=_CODE_DTYPE[dst])
+    ref_headers().ref_bulk_bf16_to_int_rz(dst, _ptr(bits), _ptr(out), bits.size)
     return out
 
 

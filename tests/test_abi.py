@@ -102,6 +102,15 @@ def test_argument_errors_are_reported_on_host():
     assert L.b2k_cast_ex(_lib.FMT_F64, _lib.FMT_E4M3, 1, _lib.ROUND_NEAREST, 1028, 2048, 16, None) == _lib.ERR_ALIGNMENT
     assert L.b2k_cast_ex(_lib.FMT_F64, _lib.FMT_E8M0, 1, _lib.ROUND_NEAREST, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
     assert L.b2k_cast_ex(_lib.FMT_BF16, _lib.FMT_E5M2, 0, _lib.ROUND_NEAREST, None, None, 0, None) == 0
+    # integer sides: the constructors saturate and round to nearest (E8M0: up); the operators truncate
+    assert L.b2k_cast_ex(_lib.FMT_I32, _lib.FMT_E4M3, 0, _lib.ROUND_NEAREST, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_I32, _lib.FMT_E8M0, 1, _lib.ROUND_ZERO, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_E5M2, _lib.FMT_U16, 1, _lib.ROUND_NEAREST, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_BF16, _lib.FMT_I8, 1, _lib.ROUND_POS_INF, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_U8, _lib.FMT_BF16, 1, _lib.ROUND_NEAREST, 1024, 2048, 16, None) == _lib.ERR_UNSUPPORTED
+    assert L.b2k_cast_ex(_lib.FMT_I64, _lib.FMT_BF16, 1, _lib.ROUND_MIN_INF, 1028, 2048, 16, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_cast_ex(_lib.FMT_E8M0, _lib.FMT_U64, 1, _lib.ROUND_ZERO, 1024, 2052, 16, None) == _lib.ERR_ALIGNMENT
+    assert L.b2k_cast_ex(_lib.FMT_I16, _lib.FMT_E5M2, 1, _lib.ROUND_NEAREST, None, None, 0, None) == 0
     # empty work is a no-op that needs no device
     assert L.b2k_cast(_lib.FMT_F32, _lib.FMT_BF16, 1, None, None, 0, None) == 0
     assert L.b2k_transpose2d(None, None, 0, 4, 16, 4, 0, 4, 4, None) == 0
