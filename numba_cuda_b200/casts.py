@@ -274,25 +274,27 @@ def _packed(x, fmt, lanes):
     if x.ndim < 1 or x.shape[-1] != lanes:
         raise ValueError(f"the last axis must hold the {lanes} lanes")
     codes = _construct(x if not host_scalar else np.ascontiguousarray(x), fmt)
-    packed = codes.view(np.uint16 if lanes == 2 else np.uint32).reshape(x.shape[:-1])
-    if host_scalar and x.ndim == 1:
-        return packed.copy_to_host().reshape(())[()]
-    return packed
+    packed = codes.view(np.uint16 if lanes == 2 else np.uint32)
+    if x.ndim == 1:                      # one pair / quadruple: a scalar
+        return packed.copy_to_host()[0]
+    return packed.reshape(x.shape[:-1])
 
 
 def _unpacked(packed, fmt, lanes, dtype):
     """``float2(fp8x2)`` / ``float4(fp8x4)`` and the half / bfloat16 forms: the lanes
     come back on a new last axis."""
     want = np.uint16 if lanes == 2 else np.uint32
-    host_scalar = not isinstance(packed, DeviceNDArray)
-    if host_scalar:
-        packed = np.ascontiguousarray(np.asarray(packed, dtype=want))
+    scalar = not isinstance(packed, DeviceNDArray) and np.ndim(packed) == 0
+    if not isinstance(packed, DeviceNDArray):
+        packed = np.ascontiguousarray(np.asarray(packed, dtype=want))   # a scalar becomes one item
     elif packed.dtype != want:
         raise TypeError(f"packed codes must be {np.dtype(want)}")
-    dev, _ = auto_device(packed.reshape(-1) if packed.ndim == 0 else packed)
+    dev, _ = auto_device(packed)
+    if not dev.flags["C_CONTIGUOUS"]:
+        raise ValueError("packed codes must be C-contiguous")
     codes = dev.view(np.uint8)
-    out = _convert(codes, fmt, dtype).reshape(tuple(packed.shape) + (lanes,))
-    return out.copy_to_host() if host_scalar and packed.ndim == 0 else out
+    out = _convert(codes, fmt, dtype)
+    return out.copy_to_host() if scalar else out.reshape(tuple(packed.shape) + (lanes,))
 
 
 def fp8x2_e4m3(x):
