@@ -111,6 +111,27 @@ __device__ __forceinline__ T user_op(T a_, T b_) {
 #define THREADS 512
 #define VEC (16 / (int)sizeof(T))
 
+// one 128-bit load, read once: no L1 allocation.  (The 256-bit form needs a newer PTX
+// version than every run-time compiler in the field accepts, and 32 bytes per lane as
+// two 128-bit loads would touch every sector twice.)
+struct alignas(16) Vec16 { unsigned int w[4]; };
+__device__ __forceinline__ Vec16 load_vec(const Vec16 *p) {
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+                 : "l"(p));
+    return v;
+}
+// the vector folded on its own, left to right
+__device__ __forceinline__ T fold_vec(const Vec16 &raw) {
+    union { Vec16 q; T e[VEC]; } u;
+    u.q = raw;
+    T t = u.e[0];
+#pragma unroll
+    for (int k = 1; k < VEC; ++k) t = user_op(t, u.e[k]);
+    return t;
+}
+
 struct Partial { T v; bool has; };
 
 __device__ __forceinline__ void fold(Partial &p, T x) {
@@ -161,7 +182,7 @@ b2k_user_reduce(const T *__restrict__ x, long long n, T init, T *__restrict__ ou
     const unsigned long long addr = (unsigned long long)x;
     long long head = (long long)(((16u - (addr & 15u)) & 15u) / sizeof(T));
     if (head > n) head = n;
-    const uint4 *xv = (const uint4 *)(x + head);
+    const Vec16 *xv = (const Vec16 *)(x + head);
     const long long nvec = (n - head) / VEC;
     const long long tail_begin = head + nvec * VEC;
     // contiguous span of vectors for this block
@@ -171,16 +192,22 @@ b2k_user_reduce(const T *__restrict__ x, long long n, T init, T *__restrict__ ou
 
     Partial acc{T(), false};
     if (blockIdx.x == 0 && threadIdx.x < head) fold(acc, x[threadIdx.x]);
-#pragma unroll 4
-    for (long long v = vlo + threadIdx.x; v < vhi; v += THREADS) {
-        const uint4 raw = __ldg(xv + v);
-        union { uint4 q; T e[VEC]; } u;
-        u.q = raw;
-        T t = u.e[0];   // fold the vector on its own first: one flag test per vector
+    // A batch of loads is issued before any of its vectors is used, and the vectors fold as
+    // independent chains: a user function of tens of instructions per element otherwise
+    // leaves each warp with one load in flight, and the SM's warps cannot cover DRAM
+    // latency between them.
+    long long v = vlo + threadIdx.x;
+    for (; v + (B2K_BATCH - 1) * THREADS < vhi; v += B2K_BATCH * THREADS) {
+        Vec16 r[B2K_BATCH];
+        T t[B2K_BATCH];
 #pragma unroll
-        for (int k = 1; k < VEC; ++k) t = user_op(t, u.e[k]);
-        fold(acc, t);
+        for (int k = 0; k < B2K_BATCH; ++k) r[k] = load_vec(xv + v + k * THREADS);
+#pragma unroll
+        for (int k = 0; k < B2K_BATCH; ++k) t[k] = fold_vec(r[k]);
+#pragma unroll
+        for (int k = 0; k < B2K_BATCH; ++k) fold(acc, t[k]);
     }
+    for (; v < vhi; v += THREADS) fold(acc, fold_vec(load_vec(xv + v)));
     if (blockIdx.x == gridDim.x - 1) {
         const long long t = tail_begin + threadIdx.x;
         if (t < n) fold(acc, x[t]);
@@ -250,6 +277,7 @@ struct Driver {
     CUresult (*get_function)(CUfunction *, CUmodule, const char *) = nullptr;
     CUresult (*launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                        void **, void **) = nullptr;
+    CUresult (*occupancy)(int *, CUfunction, int, size_t) = nullptr;
     bool ok = false;
 };
 
@@ -267,7 +295,8 @@ Driver &driver() {
         d.module_load = reinterpret_cast<decltype(d.module_load)>(get("cuModuleLoadData"));
         d.get_function = reinterpret_cast<decltype(d.get_function)>(get("cuModuleGetFunction"));
         d.launch = reinterpret_cast<decltype(d.launch)>(get("cuLaunchKernel"));
-        d.ok = d.module_load && d.get_function && d.launch;
+        d.occupancy = reinterpret_cast<decltype(d.occupancy)>(get("cuOccupancyMaxActiveBlocksPerMultiprocessor"));
+        d.ok = d.module_load && d.get_function && d.launch && d.occupancy;
     });
     return d;
 }
@@ -291,9 +320,14 @@ bool type_info(int dtype, TypeInfo *out) {
 }
 
 std::mutex g_cache_mutex;
-std::map<std::string, CUfunction> g_cache;  // key: device / dtype / expression
+struct Compiled {
+    CUfunction fn = nullptr;
+    int blocks_per_sm = 1;   // resident CTAs of 512 threads, from the kernel's register count
+};
+std::map<std::string, Compiled> g_cache;  // key: device / dtype / expression
 
-int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, CUfunction *fn) {
+int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, Compiled *out) {
+    CUfunction *fn = &out->fn;
     Nvrtc &rt = nvrtc();
     if (!rt.ok) return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: libnvrtc could not be loaded");
     Driver &drv = driver();
@@ -306,9 +340,10 @@ int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, CUfun
     const std::string dw = std::string("-DB2K_W=") + ti.w;
     const std::string dl = std::string("-DB2K_ILIT(x)=") + ti.ilit;
     const std::string de = "-DB2K_EXPR=" + expr;
+    const std::string db = "-DB2K_BATCH=" + std::to_string(B2K_ENV_INT("B2K_USER_REDUCE_BATCH", 4));
     const char *opts[] = {"--gpu-architecture=sm_100a", "-std=c++17", "-default-device", dt.c_str(), dw.c_str(),
-                          dl.c_str(), de.c_str()};
-    const nvrtcResult rc = rt.compile(prog, 7, opts);
+                          dl.c_str(), de.c_str(), db.c_str()};
+    const nvrtcResult rc = rt.compile(prog, 8, opts);
     if (rc != NVRTC_SUCCESS) {
         size_t len = 0;
         rt.log_size(prog, &len);
@@ -328,6 +363,11 @@ int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, CUfun
         return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: cuModuleLoadData failed");
     if (drv.get_function(fn, mod, "b2k_user_reduce") != CUDA_SUCCESS)
         return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_reduce_expr: kernel not found in the compiled module");
+    // the grid is one wave of resident CTAs: the user's expression decides the register
+    // count, and with it how many CTAs of 512 threads an SM holds
+    int resident = 0;
+    if (drv.occupancy(&resident, *fn, 512, 0) != CUDA_SUCCESS || resident < 1) resident = 1;
+    out->blocks_per_sm = resident > 4 ? 4 : resident;
     (void)dtype;
     return B2K_OK;
 }
@@ -350,26 +390,27 @@ extern "C" int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, i
     int device = 0;
     cudaGetDevice(&device);
     const std::string key = std::to_string(device) + "/" + std::to_string(dtype) + "/" + expr;
-    CUfunction fn = nullptr;
+    Compiled kernel;
     {
         std::lock_guard<std::mutex> lock(g_cache_mutex);
         auto it = g_cache.find(key);
         if (it == g_cache.end()) {
-            const int rc = compile_kernel(expr, dtype, ti, &fn);
+            const int rc = compile_kernel(expr, dtype, ti, &kernel);
             if (rc != B2K_OK) return rc;
-            g_cache.emplace(key, fn);
+            g_cache.emplace(key, kernel);
         } else {
-            fn = it->second;
+            kernel = it->second;
         }
     }
+    CUfunction fn = kernel.fn;
     // one contiguous span of vectors per block, at least one vector each
     const int64_t vec = 16 / static_cast<int64_t>(ti.size);
     const int64_t nvec = n / vec;
     // the head (elements before the first 16-byte boundary) shortens the vector count by at most one
     const int64_t head = ((16 - (reinterpret_cast<uintptr_t>(x_dev) & 15)) & 15) / static_cast<int64_t>(ti.size);
     const int64_t nvec_dev = (n - (head < n ? head : n)) / vec;
-    int64_t grid = nvec_dev / (512 * 8);
-    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * 4;
+    int64_t grid = nvec_dev / (512 * 8);   // at least 64 KB per block
+    const int64_t cap = static_cast<int64_t>(b2k::sm_count()) * kernel.blocks_per_sm;
     if (grid > cap) grid = cap;
     if (grid < 1) grid = 1;
     long long per = (nvec_dev + grid - 1) / grid;
