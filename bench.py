@@ -189,7 +189,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-paths", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--only", default=None,
-                    help="run a single path (profiling aid): c1,c2,c3a,c3b,c4,c5,n2,refgpu")
+                    help="run a single path (profiling aid): c1,user,c2,c3a,c3b,c4,c5,n2,refgpu")
     ap.add_argument("--scale", type=int, default=0, help="shrink the --only workload by 2^scale (profiling aid)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -770,7 +770,10 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
                       iters, warm)
         res["reduce_sum_f64_2p28"] = _roof(n2 * 8, ms, peak)
         del x, y
+
+    if want("user"):
         # a user function outside the op table: traced, compiled at run time around the same reduce skeleton
+        scratch = torch.zeros(int(L.b2k_reduce_scratch_bytes()), dtype=torch.uint8, device="cuda")
         n3 = 1 << (28 - scale)
         w = torch.randint(0, 1000003, (n3,), dtype=torch.int32, device="cuda")
         out32 = torch.zeros(1, dtype=torch.int32, device="cuda")
