@@ -377,10 +377,11 @@ def create_sharded_xoroshiro128p_states(n_total, seed, subsequence_start=0, stre
 
 
 # ------------------------------------------------------------------ casts
-def sharded_cast(src_local, src_format, dst_format, out=None, saturate=1, stream=0):
-    """Cast this rank's contiguous shard (no communication)."""
+def sharded_cast(src_local, src_format, dst_format, out=None, saturate=1, stream=0, rounding=0):
+    """Cast this rank's contiguous shard (no communication); ``rounding`` as in
+    ``casts.cast`` (the directed modes, the integer sides)."""
     from .casts import cast
-    return cast(src_local, src_format, dst_format, out=out, saturate=saturate, stream=stream)
+    return cast(src_local, src_format, dst_format, out=out, saturate=saturate, stream=stream, rounding=rounding)
 
 
 __all__ = ["PeerMailboxes", "ShardedReduceAxis", "gather_partial_rows", "fold_gathered", "shard_bounds", "op_identity", "host_fold", "combine_partials", "ShardedReduce",
