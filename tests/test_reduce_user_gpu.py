@@ -124,3 +124,26 @@ def test_unsigned_items_follow_the_integer_rule():
     assert cuda.reduce(fn)(u) == u.max()
     s = u.astype(np.int64).astype(np.int32)                      # signed items: a - b > 0 only when a > b
     assert cuda.reduce(lambda a, b: a if a - b > 0 else b)(s) == s.max()
+
+
+def test_operands_that_leave_the_32_bit_range_in_small_items():
+    """Items of up to 32 bits take the 32-bit division sequence only while the operands
+    fit; a sum of two int32 may not.  The result must not depend on which sequence ran."""
+    rng = np.random.default_rng(13)
+    # half of all pair sums overflow int32
+    wide = rng.integers(-2 ** 31, 2 ** 31, size=100003, dtype=np.int64).astype(np.int32)
+    fn = lambda a, b: (a + b) % 1000003                    # noqa: E731
+    assert cuda.reduce(fn)(wide, init=7) == (int(wide.astype(np.int64).sum()) + 7) % 1000003
+    # a single overflowing pair in an otherwise small array, at every position of a vector
+    for pos in range(0, 9):
+        x = rng.integers(0, 1000, size=4099).astype(np.int32)
+        x[2048 + pos] = 2 ** 31 - 1
+        x[2049 + pos] = 2 ** 31 - 5
+        assert cuda.reduce(fn)(x) == int(x.astype(np.int64).sum()) % 1000003, pos
+    m8 = rng.integers(1, 100, size=5000).astype(np.uint8)
+    assert cuda.reduce(lambda a, b: (a + b) % 101)(m8) == int(m8.astype(np.int64).sum()) % 101
+    # a divisor of -1 that comes from the data (the case the 32-bit instructions cannot take)
+    d = rng.integers(1, 50, size=2000).astype(np.int16)
+    d[::7] = -1
+    keep = lambda a, b: (a % b) * 0 + max(a, b)            # noqa: E731
+    assert cuda.reduce(keep)(d, init=-5) == d.max()
