@@ -372,6 +372,15 @@ int launch(const void *x, int64_t n, const void *init_host, void *out, void *scr
     const bool pdl = B2K_ENV_INT("B2K_REDUCE_PDL", 1) != 0;
     cfg.numAttrs = pdl ? 1 : 0;
     const int input_ready = (pdl && (flags & B2K_REDUCE_INPUT_READY)) ? 1 : 0;
+    // Pipelined launches leave one CTA slot of the GPU free: the last block of the
+    // previous reduction is still folding its partials (and, across GPUs, waiting for
+    // its peers) while this kernel's CTAs start.  With every slot claimed, one CTA of
+    // this kernel would start only when that block is gone and, its chunks being fixed,
+    // finish that much later than the rest.
+    if (input_ready && grid == max_grid && grid > 1 && B2K_ENV_INT("B2K_REDUCE_SPARE_SLOT", 1) != 0) {
+        grid -= 1;
+        cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    }
     cudaError_t err;
     if (link) {
         err = cudaLaunchKernelEx(&cfg, reduce_kernel<T, Op, kThreads, kUnroll, true>, static_cast<const T *>(x), n,
