@@ -192,7 +192,7 @@ class Reduce:
             self._cache[key] = op
         return op
 
-    def __call__(self, arr, size=None, res=None, init=0, stream=0, _fold_init=True):
+    def __call__(self, arr, size=None, res=None, init=0, stream=0, _fold_init=True, *, input_ready=False):
         """Performs a full reduction.
 
         :param arr: A host or device array (1-D).
@@ -201,6 +201,10 @@ class Reduce:
                     element and nothing is copied back to the host.
         :param init: Initial value; it is always folded into the result.
         :param stream: Optional CUDA stream (0 = default stream).
+        :param input_ready: (not in the reference) promise that ``arr`` is not written by
+                    the kernel that precedes this call on ``stream``: a run of reductions
+                    with ``res`` given then overlap, each reading its input while the one
+                    before finishes.  Table ops on device arrays only; ignored otherwise.
         :return: ``None`` if ``res`` is given, else a NumPy scalar of ``arr.dtype``.
         """
         # reduction.py:217-228
@@ -213,9 +217,9 @@ class Reduce:
             return init
 
         op = self._compile(arr.dtype)
-        darr, _ = auto_device(arr, stream=stream)
+        darr, staged = auto_device(arr, stream=stream)
         if darr.strides[0] != darr.dtype.itemsize:
-            darr = _gather_contiguous(darr, stream)
+            darr, staged = _gather_contiguous(darr, stream), True
 
         scratch, slot, scratch_bytes, landing = _Scratch.get(stream)
         if res is not None:
@@ -235,9 +239,13 @@ class Reduce:
                 init_host.ctypes.data if _fold_init else None,
                 out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
         else:
-            _lib.check(_lib.lib().b2k_reduce(
+            # a host array was copied by this call, a strided one gathered: both are written
+            # by the work just before the kernel, so the promise cannot hold for them
+            ready = bool(input_ready) and not staged
+            _lib.check(_lib.lib().b2k_reduce_ex(
                 op, _DTYPE_CODES[np.dtype(arr.dtype)], darr._ptr, darr.size, init_host.ctypes.data,
-                out_ptr, scratch.data_ptr(), scratch_bytes, stream_ptr(stream)))
+                out_ptr, scratch.data_ptr(), scratch_bytes, _lib.REDUCE_INPUT_READY if ready else 0,
+                stream_ptr(stream)))
         if res is not None:
             return None
         # one item back through a page-locked landing buffer, ordered on the call's stream

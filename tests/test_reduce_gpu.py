@@ -249,3 +249,31 @@ def test_second_device_in_the_same_process():
             assert cuda.reduce(lambda x, y: x + y)(np.arange(100000, dtype=np.int64)) == 100000 * 99999 // 2
     finally:
         torch.cuda.set_device(0)
+
+
+def test_a_run_of_reductions_with_input_ready_overlaps_and_keeps_every_result():
+    """Reductions over arrays that were complete before the run started may overlap
+    (programmatic dependent launch); results, scratch and order stay those of the stream.
+    Also through the C ABI with both flag values, on sizes that use one CTA and a full grid."""
+    rng = np.random.default_rng(21)
+    arrays = [rng.integers(-2 ** 31, 2 ** 31, size=n, dtype=np.int64).astype(np.int32)
+              for n in (5, 4096, 100003, (1 << 22) + 7, 3, (1 << 21) + 1, 777, 1 << 20)]
+    dev = [cuda.to_device(a) for a in arrays]
+    res = [cuda.device_array(1, np.int32) for _ in arrays]
+    cuda.synchronize()
+    fold = cuda.reduce(lambda a, b: max(a, b))
+    for _ in range(3):                       # the same scratch serves every launch of the run
+        for d, r in zip(dev, res):
+            assert fold(d, res=r, init=-2 ** 31, input_ready=True) is None
+    for a, r in zip(arrays, res):
+        assert r.copy_to_host()[0] == a.max()
+    total = cuda.reduce(lambda a, b: a + b)
+    sums = [cuda.device_array(1, np.int32) for _ in arrays]
+    for d, r in zip(dev, sums):
+        total(d, res=r, input_ready=True)
+    for a, r in zip(arrays, sums):
+        assert r.copy_to_host()[0] == a.sum(dtype=np.int32)
+    # a host array is staged by the call itself: the promise is dropped, the result is the same
+    assert fold(arrays[3], init=-2 ** 31, input_ready=True) == arrays[3].max()
+    # a strided view is gathered first: same
+    assert fold(dev[3][::2], init=-2 ** 31, input_ready=True) == arrays[3][::2].max()
