@@ -1,6 +1,8 @@
-"""Bulk elementwise conversions f32 <-> bf16 / fp8 with the semantics of the
-reference's conversion intrinsics (numba/cuda/_internal/cuda_fp8.py:3341-3374,
-:1331-1351, :1610-1631; numba/cuda/bf16.py:204-210).
+"""Bulk elementwise conversions with the semantics of the reference's conversion
+intrinsics and value types: f32 / f64 / f16 / bf16 <-> fp8 (E4M3, E5M2, E8M0), the
+fp8 value types' constructors from and conversion operators to every numeric type,
+the packed fp8x2 / fp8x4 types, f32 / f64 <-> bf16 and bf16 <-> integers in the four
+rounding modes (numba/cuda/_internal/cuda_fp8.py:223-3654; numba/cuda/bf16.py:204-269).
 
 The reference has no bulk cast: a user writes an elementwise ``@cuda.jit``
 kernel over the scalar intrinsics.  ``cast`` is that kernel, precompiled.
