@@ -247,17 +247,33 @@ class ShardedReduce:
         self._local = Reduce(functor)
         self._peer = peer
 
-    def __call__(self, local_arr, init=0, stream=0, group=None):
+    def __call__(self, local_arr, init=0, stream=0, group=None, res=None, input_ready=False):
+        """The reduction of the whole array, on every rank.  With ``res`` (a device array
+        of the shard's dtype; fused combine only) the call only launches: the result lands
+        in ``res[0]`` in stream order, nothing is copied back and ``None`` is returned --
+        call ``peer.check()`` once the stream has been synchronised.  ``input_ready`` as
+        in ``Reduce.__call__``: a run of such launches over resident shards overlaps."""
         from .api import auto_device, device_array
         from .kernels.reduction import _DTYPE_CODES
         dtype = np.dtype(local_arr.dtype)
         op = self._local._compile(dtype)
+        if res is not None and (isinstance(op, str) or self._peer is None):
+            raise NotImplementedError("res= needs a table op and the fused combine (peer=PeerMailboxes())")
         if isinstance(op, str):
             return self._traced(local_arr, dtype, init, stream, group)
         if self._peer is not None:
-            darr, _ = auto_device(local_arr, stream=stream)
-            slot = device_array(1, dtype=dtype, stream=stream)
+            darr, staged = auto_device(local_arr, stream=stream)
+            if darr.ndim != 1 or (darr.size and darr.strides[0] != dtype.itemsize):
+                raise ValueError("the shard must be a contiguous 1-D array")
             init_host = np.array([init], dtype=dtype)
+            if res is not None:
+                dres, _ = auto_device(res, stream=stream)
+                if dres.dtype != dtype or dres.size < 1:
+                    raise TypeError("res must hold one item of the shard's dtype")
+                self._peer.reduce(op, _DTYPE_CODES[dtype], darr._ptr, darr.size, init_host, dres._ptr, stream,
+                                  input_ready=bool(input_ready) and not staged)
+                return None
+            slot = device_array(1, dtype=dtype, stream=stream)
             self._peer.reduce(op, _DTYPE_CODES[dtype], darr._ptr, darr.size, init_host, slot._ptr, stream)
             result = slot.copy_to_host()[0]
             self._peer.check()

@@ -300,6 +300,16 @@ def _rank_main(rank, world, port, errors):
                 for k in range(8)]
         assert got.tolist() == want
         assert 0 <= boxes.exchange_ns() < 50_000_000
+        # the same pipeline through the Python wrapper: launches only, results stay on the device
+        fused = sharded.ShardedReduce(lambda a, b: max(a, b), peer=boxes)
+        outs2 = cuda.device_array(8, dtype=np.int32)
+        for k, sh in enumerate(shards):
+            assert fused(sh, init=-2 ** 31, res=outs2[k:k + 1], input_ready=True) is None
+        got2 = outs2.copy_to_host()
+        boxes.check(agree=True)
+        assert got2.tolist() == want
+        with pytest.raises(NotImplementedError):
+            sharded.ShardedReduce(lambda a, b: max(a, b))(shards[0], res=outs2[:1])
         # a row-sharded matrix reduced along both axes
         full = np.random.default_rng(9).integers(-2 ** 31, 2 ** 31, size=(4099, 260), dtype=np.int32)
         lo, hi = sharded.shard_bounds(full.shape[0], world, rank)
