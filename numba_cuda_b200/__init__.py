@@ -24,4 +24,12 @@ from .kernels.reduction import Reduce
 
 reduce = Reduce
 
+
+def stats() -> dict:
+    """Counters of this process: kernels launched by the library so far, and whether
+    the C-ABI calls are wrapped in NVTX ranges (``B2K_NVTX=1``)."""
+    import os
+    return {"kernel_launches": _lib.launch_count(), "nvtx_ranges": os.environ.get("B2K_NVTX", "") not in ("", "0"),
+            "library": _lib.LIB_PATH}
+
 __version__ = "0.1.0"

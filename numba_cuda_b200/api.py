@@ -6,6 +6,8 @@ their callers need to hand arrays over (``to_device`` api.py:117,
 :100-113)."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 
@@ -153,7 +155,9 @@ def as_cuda_array(obj, sync=True) -> DeviceNDArray:
     if isinstance(obj, DeviceNDArray):
         return obj
     s = obj.__cuda_array_interface__.get("stream")
-    if sync and s:
+    # NUMBA_CUDA_ARRAY_INTERFACE_SYNC=0 switches the synchronisation off globally, as the
+    # reference's config.CUDA_ARRAY_INTERFACE_SYNC does (api.py:56-60, core/config.py:480)
+    if sync and s and os.environ.get("NUMBA_CUDA_ARRAY_INTERFACE_SYNC", "1") not in ("0", ""):
         if s in (1, 2):
             torch.cuda.default_stream().synchronize()
         else:

@@ -6,6 +6,8 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "b2k_internal.cuh"
 
 namespace b2k {
@@ -51,6 +53,15 @@ int env_read(const char *name) {
     const char *v = getenv(name);
     return (v && *v) ? atoi(v) : INT_MIN;
 }
+
+// NVTX 3 is header-only: the tools' injection library is looked up on the first call,
+// and without a tool attached the calls return at once.
+bool nvtx_enabled() {
+    static const bool on = env_read("B2K_NVTX") > 0;
+    return on;
+}
+void nvtx_push(const char *name) { nvtxRangePushA(name); }
+void nvtx_pop() { nvtxRangePop(); }
 
 }  // namespace b2k
 

@@ -703,12 +703,14 @@ int assign_impl(void *dst, const void *src, const void *value_host, int ndim, co
 
 extern "C" int b2k_assign(void *dst, const void *src, int ndim, const int64_t *shape, const int64_t *dst_strides,
                           const int64_t *src_strides, int64_t itemsize, void *stream) {
+    B2K_RANGE("b2k_assign");
     if (ndim > 0 && !src_strides) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_assign: null shape or strides");
     return assign_impl(dst, src, nullptr, ndim, shape, dst_strides, src_strides, itemsize, stream);
 }
 
 extern "C" int b2k_fill(void *dst, int ndim, const int64_t *shape, const int64_t *dst_strides, const void *value_host,
                         int64_t itemsize, void *stream) {
+    B2K_RANGE("b2k_fill");
     if (!value_host) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_fill: null value");
     if (itemsize < 1 || itemsize > 16)
         return b2k::fail(B2K_ERR_UNSUPPORTED, "b2k_fill: items of 1..16 bytes (got %lld)", static_cast<long long>(itemsize));

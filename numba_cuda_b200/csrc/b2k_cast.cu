@@ -837,6 +837,7 @@ int cast_value_types(int src, int dst, bool sat, int rounding, const void *in, v
 
 extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void *out_dev,
                         int64_t n, void *stream) {
+    B2K_RANGE("b2k_cast");
     if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast: negative length %lld", (long long)n);
     if (n > 0 && (!in_dev || !out_dev)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast: null pointer");
     cudaStream_t s = b2k::as_stream(stream);
@@ -856,6 +857,7 @@ extern "C" int b2k_cast(int src, int dst, int saturate, const void *in_dev, void
 
 extern "C" int b2k_cast_ex(int src, int dst, int saturate, int rounding, const void *in_dev, void *out_dev,
                            int64_t n, void *stream) {
+    B2K_RANGE("b2k_cast_ex");
     if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast_ex: negative length %lld", (long long)n);
     if (n > 0 && (!in_dev || !out_dev)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_cast_ex: null pointer");
     if (rounding < B2K_ROUND_NEAREST || rounding > B2K_ROUND_MIN_INF)

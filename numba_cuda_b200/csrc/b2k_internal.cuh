@@ -24,6 +24,24 @@ int sm_count();
 int env_read(const char *name);
 // Ordinal of the current device, or -1.
 int current_device();
+// An NVTX range around one C-ABI call, so that a timeline or an ncu capture can be
+// filtered by entry point.  Off unless B2K_NVTX=1 is in the environment (one cached
+// flag test per call otherwise).
+bool nvtx_enabled();
+void nvtx_push(const char *name);
+void nvtx_pop();
+struct Range {
+    const bool on;
+    explicit Range(const char *name) : on(nvtx_enabled()) {
+        if (on) nvtx_push(name);
+    }
+    ~Range() {
+        if (on) nvtx_pop();
+    }
+    Range(const Range &) = delete;
+    Range &operator=(const Range &) = delete;
+};
+#define B2K_RANGE(name) b2k::Range b2k_range__(name)
 
 // Set-up that has to happen once on EVERY device a process uses (function
 // attributes such as the dynamic shared-memory limit belong to a device, not to

@@ -467,11 +467,13 @@ static int reduce_impl(int op, int dtype, const void *x_dev, int64_t n, const vo
 
 int b2k_reduce(int op, int dtype, const void *x_dev, int64_t n, const void *init_host,
                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    B2K_RANGE("b2k_reduce");
     return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr, 0u);
 }
 
 int b2k_reduce_ex(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
                   void *scratch_dev, int64_t scratch_bytes, unsigned flags, void *stream) {
+    B2K_RANGE("b2k_reduce_ex");
     if (flags & ~static_cast<unsigned>(B2K_REDUCE_INPUT_READY))
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_ex: unknown flag bits 0x%x", flags);
     return reduce_impl(op, dtype, x_dev, n, init_host, out_dev, scratch_dev, scratch_bytes, stream, nullptr, flags);
@@ -520,6 +522,7 @@ int b2k_peer_mailbox_close(void *peer_mailbox_dev) {
 int b2k_reduce_peer(int op, int dtype, const void *x_dev, int64_t n, const void *init_host, void *out_dev,
                     void *scratch_dev, int64_t scratch_bytes, void *const *mailboxes, int world, int rank,
                     uint64_t epoch, uint64_t timeout_ns, void *status_dev, unsigned flags, void *stream) {
+    B2K_RANGE("b2k_reduce_peer");
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_peer: world %d / rank %d out of range (at most %d ranks)",
                          world, rank, kMaxPeers);

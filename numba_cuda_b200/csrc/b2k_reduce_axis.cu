@@ -655,6 +655,7 @@ static int reduce_axis_impl(const char *who, int op, int dtype, const void *x_de
 
 int b2k_reduce_axis(int op, int dtype, const void *x_dev, int64_t rows, int64_t cols, int64_t pitch_bytes, int axis,
                     const void *init_host, void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    B2K_RANGE("b2k_reduce_axis");
     return reduce_axis_impl("b2k_reduce_axis", op, dtype, x_dev, 1, rows, cols, pitch_bytes, 0, axis, init_host,
                             out_dev, scratch_dev, scratch_bytes, stream);
 }
@@ -673,6 +674,7 @@ int64_t b2k_reduce_cols_batched_scratch_bytes(int64_t batch, int64_t rows, int64
 int b2k_reduce_cols_batched(int op, int dtype, const void *x_dev, int64_t batch, int64_t rows, int64_t cols,
                             int64_t pitch_bytes, int64_t matrix_stride_bytes, const void *init_host, void *out_dev,
                             void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    B2K_RANGE("b2k_reduce_cols_batched");
     if (batch > 1 && matrix_stride_bytes < 0)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_cols_batched: negative matrix stride");
     return reduce_axis_impl("b2k_reduce_cols_batched", op, dtype, x_dev, batch, rows, cols, pitch_bytes,

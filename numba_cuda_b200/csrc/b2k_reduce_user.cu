@@ -376,6 +376,7 @@ int compile_kernel(const std::string &expr, int dtype, const TypeInfo &ti, Compi
 
 extern "C" int b2k_reduce_expr(const char *expr, int dtype, const void *x_dev, int64_t n, const void *init_host,
                                void *out_dev, void *scratch_dev, int64_t scratch_bytes, void *stream) {
+    B2K_RANGE("b2k_reduce_expr");
     TypeInfo ti;
     if (!type_info(dtype, &ti)) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: unknown dtype %d", dtype);
     if (!expr || !*expr) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_reduce_expr: empty expression");

@@ -92,6 +92,7 @@ int launch_items(const void *in, void *out, int64_t rows, int64_t cols, int64_t 
 extern "C" int b2k_transpose2d(const void *in_dev, void *out_dev, int64_t rows, int64_t cols,
                                int64_t in_stride0, int64_t in_stride1, int64_t out_stride0,
                                int64_t out_stride1, int64_t itemsize, void *stream) {
+    B2K_RANGE("b2k_transpose2d");
     if (rows < 0 || cols < 0 || itemsize <= 0)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_transpose2d: bad shape or item size");
     if (rows == 0 || cols == 0) return B2K_OK;

@@ -513,6 +513,7 @@ extern "C" {
 int64_t b2k_xoroshiro128p_tables_bytes(void) { return kTablesBytes; }
 
 int b2k_xoroshiro128p_build_tables(void *tables_dev, int64_t tables_bytes, void *stream) {
+    B2K_RANGE("b2k_xoroshiro128p_build_tables");
     if (!tables_dev || tables_bytes < kTablesBytes)
         return b2k::fail(B2K_ERR_SCRATCH, "b2k_xoroshiro128p_build_tables: %lld bytes required",
                          (long long)kTablesBytes);
@@ -527,6 +528,7 @@ int b2k_xoroshiro128p_build_tables(void *tables_dev, int64_t tables_bytes, void 
 
 int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t subsequence_start,
                            const void *tables_dev, int64_t tables_bytes, void *stream) {
+    B2K_RANGE("b2k_xoroshiro128p_init");
     if (n < 0) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_init: negative n");
     if (n == 0) return B2K_OK;
     if (!states_dev) return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_init: null states");
@@ -599,6 +601,7 @@ int b2k_xoroshiro128p_init(void *states_dev, int64_t n, uint64_t seed, uint64_t 
 
 int b2k_xoroshiro128p_fill(void *states_dev, int64_t n, int draw0, void *out0_dev, int64_t count0,
                            int draw1, void *out1_dev, int64_t count1, void *stream) {
+    B2K_RANGE("b2k_xoroshiro128p_fill");
     if (n < 0 || count0 < 0 || count1 < 0)
         return b2k::fail(B2K_ERR_INVALID_ARG, "b2k_xoroshiro128p_fill: negative size");
     if (n == 0 || (count0 == 0 && count1 == 0)) return B2K_OK;
