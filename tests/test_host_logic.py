@@ -1,5 +1,7 @@
 """Host-side logic of the drop-in: functor classification, indexing math,
 shard bounds, identities.  No GPU."""
+import os
+
 import numpy as np
 import pytest
 
@@ -254,3 +256,22 @@ def test_unsigned_items_widen_to_uint64_and_mix_as_int64():
     assert trace_functor(lambda a, b: -a + b, np.uint16) == "(((long long)(-(long long)a)) + ((long long)b))"
     # floats are untouched by the integer rule
     assert trace_functor(lambda a, b: a + b * 2, np.float32) == "(a + (b * B2K_ILIT(2LL)))"
+
+
+def test_stats_and_nvtx_switch_need_no_device():
+    """``cuda.stats()`` reads host-side counters only; with B2K_NVTX=1 an entry point that
+    has no work to launch still returns 0 (the range opens and closes around nothing)."""
+    import subprocess
+    import sys
+    import numba_cuda_b200 as cuda
+    s = cuda.stats()
+    assert set(s) == {"kernel_launches", "nvtx_ranges", "library"} and s["kernel_launches"] >= 0
+    code = ("from numba_cuda_b200 import _lib; L = _lib.lib(); "
+            "import numba_cuda_b200 as cuda; "
+            "assert L.b2k_cast(0, 1, 1, None, None, 0, None) == 0; "
+            "assert L.b2k_transpose2d(None, None, 0, 4, 16, 4, 0, 4, 4, None) == 0; "
+            "assert cuda.stats()['nvtx_ranges'] is True; print('ok')")
+    env = dict(os.environ, B2K_NVTX="1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-500:]
