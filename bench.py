@@ -787,6 +787,15 @@ def secondary_paths(cuda, L, torch, timed, peak, world, rank, sptr, only=None, s
             _roof(n3 * 4, ms, peak), expression=expr,
             spot_check=bool(int(out32.item()) == int(w.sum(dtype=torch.int64).item()) % 1000003),
             note="numba's typing: the sum and the remainder are 64-bit operations")
+        # a light user function (no division): the same skeleton is HBM-bound
+        expr2 = cuda.Reduce(lambda a, b: max(abs(a), abs(b)))._compile(np.dtype(np.int32))
+        assert isinstance(expr2, str)
+        ms, _ = timed(lambda: check(L.b2k_reduce_expr(expr2.encode(), _lib.I32, w.data_ptr(), n3, zero32.ctypes.data,
+                                                      out32.data_ptr(), scratch.data_ptr(), scratch.numel(), sptr)),
+                      iters, warm)
+        res["user_reduce_absmax_int32_2p28"] = dict(
+            _roof(n3 * 4, ms, peak), expression=expr2,
+            spot_check=bool(int(out32.item()) == int(w.abs().max().item())))
         del w
 
     for name, rows, cols, tdt, item in (("c3a_transpose_f32_32768x32768", 32768, 32768, torch.float32, 4),
