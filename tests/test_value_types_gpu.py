@@ -231,3 +231,27 @@ def test_modes_that_do_not_exist_are_refused():
     assert L.b2k_cast_ex(_lib.FMT_E4M3, _lib.FMT_I32, 1, _lib.ROUND_NEAREST, out._ptr, x._ptr, 64, None) == -2
     assert L.b2k_cast_ex(_lib.FMT_I32, _lib.FMT_U32, 1, 0, x._ptr, x._ptr, 64, None) == -2
     assert L.b2k_cast_ex(_lib.FMT_I8, _lib.FMT_BF16, 1, 0, out._ptr, x._ptr, 64, None) == -2
+
+
+def test_reference_bfloat16_integer_cases():
+    """The cases of the reference's own tests (numba_cuda/numba/cuda/tests/cudapy/
+    test_bfloat16.py:346-517): bit-cast round trip, 1.5 to every integer type in every
+    mode, 789 from every integer type in every mode."""
+    import ml_dtypes
+    one_and_a_half = np.int16(0x3FC0)
+    a = b16.int16_as_bfloat16(one_and_a_half)
+    assert a.dtype == ml_dtypes.bfloat16 and float(a) == 1.5
+    assert b16.bfloat16_as_int16(a) == one_and_a_half
+    assert b16.bfloat16_as_uint16(b16.uint16_as_bfloat16(np.uint16(0x3FC0))) == 0x3FC0
+    assert b16.bfloat16_to_int8_rz(a) == 1 and b16.bfloat16_to_uint8_rz(a) == 1
+    for name in ("int16", "uint16", "int32", "uint32", "int64", "uint64"):
+        got = [getattr(b16, f"bfloat16_to_{name}_{m}")(a) for m in ("rn", "rz", "rd", "ru")]
+        assert [int(v) for v in got] == [2, 1, 1, 2] and all(v.dtype == np.dtype(name) for v in got)
+        want = np.dtype(name).type(789).astype(ml_dtypes.bfloat16).view(np.int16)
+        for m in ("rn", "rz", "rd", "ru"):
+            bits = np.asarray(getattr(b16, f"{name}_to_bfloat16_{m}")(np.dtype(name).type(789))).view(np.int16)
+            assert abs(int(bits) - int(want)) < 2, (name, m)
+        # 789 = 0b1100010101 needs ten bits: 788 below, 792 above, 788 nearest
+        exact = {"rn": 788.0, "rz": 788.0, "rd": 788.0, "ru": 792.0}
+        for m, v in exact.items():
+            assert float(getattr(b16, f"{name}_to_bfloat16_{m}")(np.dtype(name).type(789))) == v
