@@ -255,3 +255,16 @@ def test_reference_bfloat16_integer_cases():
         exact = {"rn": 788.0, "rz": 788.0, "rd": 788.0, "ru": 792.0}
         for m, v in exact.items():
             assert float(getattr(b16, f"{name}_to_bfloat16_{m}")(np.dtype(name).type(789))) == v
+
+
+def test_reference_fp8_nan_and_round_trip_cases():
+    """numba_cuda/numba/cuda/tests/cudapy/test_fp8_bindings.py:162-177, :334-378: a NaN
+    constructs a NaN in every fp8 type and converts to a NaN in float16 / float32 /
+    float64; 4.0 survives the round trip through every type."""
+    nan = np.float32(np.nan)
+    for ctor, back in ((fp8_e5m2, fp8_e5m2_to), (fp8_e4m3, fp8_e4m3_to), (fp8_e8m0, fp8_e8m0_to)):
+        code = ctor(nan)
+        for t in (np.float16, np.float32, np.float64):
+            assert np.isnan(back(code, t)), (ctor.__name__, t)
+        assert back(ctor(np.float32(4.0)), np.float32) == 4.0
+    assert fp8_e5m2(nan) & 0x7F > 0x7C and fp8_e4m3(nan) & 0x7F == 0x7F and fp8_e8m0(nan) == 0xFF
